@@ -1,0 +1,537 @@
+// bfloat16 attention over the paged cache on the warp-level tensor-core path.
+//
+//   attention_prefill: flash-style causal grouped-query attention for a batch of
+//     prompts of unequal length.  One CTA per (64-query tile, query head,
+//     sequence); it walks the sequence's cache pages (64 keys each) up to the
+//     tile's last position with a streaming softmax in float.
+//   attention_decode: one query per sequence.  One CTA per (split, key/value
+//     head, sequence) serves the whole group of query heads that share the
+//     key/value head (rows of one 16-row MMA tile), streams its share of the
+//     pages through a four-stage cp.async ring and writes either the final
+//     output or a partial (max, sum, accumulator) that attention_combine merges
+//     in a fixed order.
+//
+// Scores are scaled after the dot product, masked by position (causal, optional
+// window), and exponentiated with exp2 on log2(e)-scaled values; max, sum and
+// the output accumulator are float (model/llama.go:1626-1660 for the formula).
+// Head sizes 16..128 in steps of 16 are served by the 16/32/64/128-wide variant
+// with zero-filled padding.
+#include "mma_helpers.cuh"
+#include <math.h>
+
+namespace {
+
+constexpr float kLog2e = 1.4426950408889634f;
+
+// ============================================================= prefill
+template <int DP>
+__global__ void __launch_bounds__(128)
+attention_prefill_kernel(const bf16* __restrict__ q, int ldq, bf16* __restrict__ out, int ldo,
+                         const bf16* __restrict__ kc, const bf16* __restrict__ vc, long long page_stride,
+                         const int* __restrict__ block_table, int table_stride,
+                         const int* __restrict__ cu_seqlens, const int* __restrict__ slots,
+                         const int* __restrict__ start_pos,
+                         int n_heads, int n_kv, int hd, float scale, int window) {
+    constexpr int CPR = DP / 8;                 // 16-byte chunks per row
+    constexpr int TILE_BYTES = 64 * DP * 2;
+    extern __shared__ __align__(128) unsigned char smem[];
+    const uint32_t sQ = smem_u32(smem);
+    const uint32_t sK = sQ + TILE_BYTES;        // two stages
+    const uint32_t sV = sK + 2 * TILE_BYTES;    // two stages
+
+    const int b = blockIdx.z, h = blockIdx.y;
+    const int tile = gridDim.x - 1 - blockIdx.x;          // longest tiles first
+    const int q_begin = cu_seqlens[b];
+    const int q_len = cu_seqlens[b + 1] - q_begin;
+    if (tile * 64 >= q_len) return;
+    const int start = start_pos[b];
+    const int kvh = h / (n_heads / n_kv);
+    const int* table = block_table + (size_t)slots[b] * table_stride;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t4 = lane & 3;
+
+    const int rows_here = min(64, q_len - tile * 64);
+    const int kv_total = start + q_len;                    // keys that exist after this step
+    const int k_max = start + tile * 64 + rows_here - 1;   // last key any row of the tile sees
+    int k_min = 0;
+    if (window > 0) k_min = max(0, start + tile * 64 - window + 1);
+    const int j_lo = k_min / kPageTokens, j_hi = k_max / kPageTokens;
+
+    // ---- stage the query tile
+    for (int id = tid; id < 64 * CPR; id += 128) {
+        const int r = id / CPR, c = id % CPR;
+        const bool ok = r < rows_here && c * 8 < hd;
+        const bf16* src = ok ? q + (size_t)(q_begin + tile * 64 + r) * ldq + h * hd + c * 8 : q;
+        cp_async16(sQ + swz_offset<DP>(r, c), src, ok ? 16 : 0);
+    }
+    auto load_kv = [&](int stage, int j) {
+        const size_t base = (size_t)table[j] * page_stride + (size_t)kvh * kPageTokens * hd;
+        for (int id = tid; id < 64 * CPR; id += 128) {
+            const int r = id / CPR, c = id % CPR;
+            const bool ok = (j * kPageTokens + r) < kv_total && c * 8 < hd;
+            const size_t off = ok ? base + (size_t)r * hd + c * 8 : 0;
+            cp_async16(sK + stage * TILE_BYTES + swz_offset<DP>(r, c), kc + off, ok ? 16 : 0);
+            cp_async16(sV + stage * TILE_BYTES + swz_offset<DP>(r, c), vc + off, ok ? 16 : 0);
+        }
+    };
+    load_kv(0, j_lo);
+    cp_async_commit();
+
+    uint32_t qf[DP / 16][4];
+    float o[DP / 8][4];
+#pragma unroll
+    for (int i = 0; i < DP / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+    float m_row[2] = {-INFINITY, -INFINITY};   // running max of scaled scores (log2 domain)
+    float l_row[2] = {0.f, 0.f};               // this thread's share of the running sum
+    const float sl2 = scale * kLog2e;
+    const int pos0 = start + tile * 64 + warp * 16 + g;    // position of row g; row g+8 is pos0+8
+
+    for (int j = j_lo, it = 0; j <= j_hi; ++j, ++it) {
+        const int stage = it & 1;
+        if (j + 1 <= j_hi) {
+            load_kv(stage ^ 1, j + 1);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        if (it == 0) {
+#pragma unroll
+            for (int kk = 0; kk < DP / 16; ++kk) {
+                const int r = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+                const int c = kk * 2 + (lane >> 4);
+                ldmatrix_x4(qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], sQ + swz_offset<DP>(r, c));
+            }
+        }
+        // ---- S = Q K^T for this warp's 16 rows and the page's 64 keys
+        float s[8][4];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
+        const uint32_t kbase = sK + stage * TILE_BYTES, vbase = sV + stage * TILE_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < DP / 16; ++kk) {
+#pragma unroll
+            for (int jj = 0; jj < 4; ++jj) {
+                uint32_t b0, b1, b2, b3;
+                const int r = jj * 16 + (lane & 7) + (lane >> 4) * 8;
+                const int c = kk * 2 + ((lane >> 3) & 1);
+                ldmatrix_x4(b0, b1, b2, b3, kbase + swz_offset<DP>(r, c));
+                mma_bf16_16816(s[jj * 2], qf[kk], b0, b1);
+                mma_bf16_16816(s[jj * 2 + 1], qf[kk], b2, b3);
+            }
+        }
+        // ---- mask, streaming softmax
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int key = j * kPageTokens + i * 8 + t4 * 2 + (e & 1);
+                const int pos = pos0 + (e >> 1) * 8;
+                const bool ok = key <= pos && (window <= 0 || key > pos - window);
+                const float v = ok ? s[i][e] * sl2 : -INFINITY;
+                s[i][e] = v;
+                mx[e >> 1] = fmaxf(mx[e >> 1], v);
+            }
+        }
+        float corr[2], m_use[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+            const float m_new = fmaxf(m_row[r], mx[r]);
+            m_use[r] = m_new == -INFINITY ? 0.f : m_new;
+            corr[r] = exp2f(m_row[r] - m_use[r]);
+            m_row[r] = m_new;
+            l_row[r] *= corr[r];
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float p = exp2f(s[i][e] - m_use[e >> 1]);
+                s[i][e] = p;
+                l_row[e >> 1] += p;
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < DP / 8; ++i) {
+            o[i][0] *= corr[0]; o[i][1] *= corr[0];
+            o[i][2] *= corr[1]; o[i][3] *= corr[1];
+        }
+        // ---- O += P V
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+            uint32_t pa[4];
+            pa[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+            pa[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+            pa[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+            pa[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+            for (int dd = 0; dd < DP / 16; ++dd) {
+                uint32_t b0, b1, b2, b3;
+                const int r = kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
+                const int c = dd * 2 + (lane >> 4);
+                ldmatrix_x4_trans(b0, b1, b2, b3, vbase + swz_offset<DP>(r, c));
+                mma_bf16_16816(o[dd * 2], pa, b0, b1);
+                mma_bf16_16816(o[dd * 2 + 1], pa, b2, b3);
+            }
+        }
+        __syncthreads();
+    }
+
+    // ---- normalise and store
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        l_row[r] += __shfl_xor_sync(0xffffffffu, l_row[r], 1);
+        l_row[r] += __shfl_xor_sync(0xffffffffu, l_row[r], 2);
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int row = warp * 16 + g + r * 8;
+        if (row >= rows_here) continue;
+        const float inv = l_row[r] > 0.f ? 1.0f / l_row[r] : 0.f;
+        bf16* dst = out + (size_t)(q_begin + tile * 64 + row) * ldo + h * hd;
+#pragma unroll
+        for (int i = 0; i < DP / 8; ++i) {
+            const int d = i * 8 + t4 * 2;
+            if (d < hd)
+                *reinterpret_cast<__nv_bfloat162*>(dst + d) =
+                    __floats2bfloat162_rn(o[i][r * 2] * inv, o[i][r * 2 + 1] * inv);
+        }
+    }
+}
+
+// ============================================================== decode
+constexpr int kDecodeStages = 4;
+
+// Partials: for each (sequence, query head, split): DP floats of unnormalised
+// output, then the running max (log2 domain) and the running sum.
+template <int DP>
+__global__ void __launch_bounds__(128)
+attention_decode_kernel(const bf16* __restrict__ q, int ldq, bf16* __restrict__ out, int ldo,
+                        const bf16* __restrict__ kc, const bf16* __restrict__ vc, long long page_stride,
+                        const int* __restrict__ block_table, int table_stride,
+                        const int* __restrict__ slots, const int* __restrict__ positions,
+                        int n_heads, int n_kv, int hd, float scale, int window,
+                        int n_splits, float* __restrict__ part_o, float* __restrict__ part_ml) {
+    constexpr int CPR = DP / 8;
+    constexpr int TILE_BYTES = 64 * DP * 2;
+    constexpr int STAGE_BYTES = 2 * TILE_BYTES;
+    extern __shared__ __align__(128) unsigned char smem[];
+    const uint32_t sQ = smem_u32(smem);                       // 16 x DP bf16
+    const uint32_t sKV = sQ + 16 * DP * 2;                    // kDecodeStages x (K page, V page)
+    float* merge = reinterpret_cast<float*>(smem + 16 * DP * 2);   // reused after the page loop
+
+    const int split = blockIdx.x, b = blockIdx.z;
+    const int group = n_heads / n_kv;
+    const int tiles_per_kv = (group + 15) / 16;
+    const int kvh = blockIdx.y / tiles_per_kv;
+    const int h0 = kvh * group + (blockIdx.y % tiles_per_kv) * 16;   // first query head of this CTA
+    const int rows = min(16, kvh * group + group - h0);              // query heads served here
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t4 = lane & 3;
+
+    const int pos = positions[b];
+    const int* table = block_table + (size_t)slots[b] * table_stride;
+    const int k_min = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int p_first = k_min / kPageTokens, p_last = pos / kPageTokens;
+    const int n_pages = p_last - p_first + 1;
+    const int per_split = (n_pages + n_splits - 1) / n_splits;
+    const int p_begin = p_first + split * per_split;
+    const int p_end = min(p_last + 1, p_begin + per_split);      // exclusive
+
+    // ---- queries of the group (rows beyond `rows` are zero)
+    for (int id = tid; id < 16 * CPR; id += 128) {
+        const int r = id / CPR, c = id % CPR;
+        const bool ok = r < rows && c * 8 < hd;
+        const bf16* src = ok ? q + (size_t)b * ldq + (h0 + r) * hd + c * 8 : q;
+        cp_async16(sQ + swz_offset<DP>(r, c), src, ok ? 16 : 0);
+    }
+    auto load_page = [&](int stage, int p) {
+        const size_t base = (size_t)table[p] * page_stride + (size_t)kvh * kPageTokens * hd;
+        const uint32_t dk = sKV + stage * STAGE_BYTES, dv = dk + TILE_BYTES;
+        for (int id = tid; id < 64 * CPR; id += 128) {
+            const int r = id / CPR, c = id % CPR;
+            const bool ok = (p * kPageTokens + r) <= pos && c * 8 < hd;
+            const size_t off = ok ? base + (size_t)r * hd + c * 8 : 0;
+            cp_async16(dk + swz_offset<DP>(r, c), kc + off, ok ? 16 : 0);
+            cp_async16(dv + swz_offset<DP>(r, c), vc + off, ok ? 16 : 0);
+        }
+    };
+#pragma unroll
+    for (int s = 0; s < kDecodeStages - 1; ++s) {
+        if (p_begin + s < p_end) load_page(s, p_begin + s);
+        cp_async_commit();
+    }
+
+    uint32_t qf[DP / 16][4];
+    float o[DP / 8][4];
+#pragma unroll
+    for (int i = 0; i < DP / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+    float m_row[2] = {-INFINITY, -INFINITY};
+    float l_row[2] = {0.f, 0.f};
+    const float sl2 = scale * kLog2e;
+
+    for (int p = p_begin, it = 0; p < p_end; ++p, ++it) {
+        cp_async_wait<kDecodeStages - 2>();
+        __syncthreads();
+        {
+            const int nxt = p + kDecodeStages - 1;
+            if (nxt < p_end) load_page((it + kDecodeStages - 1) % kDecodeStages, nxt);
+            cp_async_commit();
+        }
+        if (it == 0) {
+#pragma unroll
+            for (int kk = 0; kk < DP / 16; ++kk) {
+                const int r = (lane & 7) + ((lane >> 3) & 1) * 8;
+                const int c = kk * 2 + (lane >> 4);
+                ldmatrix_x4(qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], sQ + swz_offset<DP>(r, c));
+            }
+        }
+        const uint32_t kbase = sKV + (it % kDecodeStages) * STAGE_BYTES, vbase = kbase + TILE_BYTES;
+        // this warp's 16 keys of the page: S[16 heads x 16 keys]
+        float s[2][4];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
+#pragma unroll
+        for (int kk = 0; kk < DP / 16; ++kk) {
+            uint32_t b0, b1, b2, b3;
+            const int r = warp * 16 + (lane & 7) + (lane >> 4) * 8;
+            const int c = kk * 2 + ((lane >> 3) & 1);
+            ldmatrix_x4(b0, b1, b2, b3, kbase + swz_offset<DP>(r, c));
+            mma_bf16_16816(s[0], qf[kk], b0, b1);
+            mma_bf16_16816(s[1], qf[kk], b2, b3);
+        }
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int key = p * kPageTokens + warp * 16 + i * 8 + t4 * 2 + (e & 1);
+                const bool ok = key <= pos && key >= k_min;
+                const float v = ok ? s[i][e] * sl2 : -INFINITY;
+                s[i][e] = v;
+                mx[e >> 1] = fmaxf(mx[e >> 1], v);
+            }
+        }
+        float corr[2], m_use[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+            const float m_new = fmaxf(m_row[r], mx[r]);
+            m_use[r] = m_new == -INFINITY ? 0.f : m_new;
+            corr[r] = exp2f(m_row[r] - m_use[r]);
+            m_row[r] = m_new;
+            l_row[r] *= corr[r];
+        }
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float pv = exp2f(s[i][e] - m_use[e >> 1]);
+                s[i][e] = pv;
+                l_row[e >> 1] += pv;
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < DP / 8; ++i) {
+            o[i][0] *= corr[0]; o[i][1] *= corr[0];
+            o[i][2] *= corr[1]; o[i][3] *= corr[1];
+        }
+        uint32_t pa[4];
+        pa[0] = pack_bf16(s[0][0], s[0][1]);
+        pa[1] = pack_bf16(s[0][2], s[0][3]);
+        pa[2] = pack_bf16(s[1][0], s[1][1]);
+        pa[3] = pack_bf16(s[1][2], s[1][3]);
+#pragma unroll
+        for (int dd = 0; dd < DP / 16; ++dd) {
+            uint32_t b0, b1, b2, b3;
+            const int r = warp * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
+            const int c = dd * 2 + (lane >> 4);
+            ldmatrix_x4_trans(b0, b1, b2, b3, vbase + swz_offset<DP>(r, c));
+            mma_bf16_16816(o[dd * 2], pa, b0, b1);
+            mma_bf16_16816(o[dd * 2 + 1], pa, b2, b3);
+        }
+    }
+    cp_async_wait<0>();
+    __syncthreads();      // every warp is done with the ring: reuse it for the merge
+
+    // ---- merge the four warps (each saw a quarter of every page) in warp order
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        l_row[r] += __shfl_xor_sync(0xffffffffu, l_row[r], 1);
+        l_row[r] += __shfl_xor_sync(0xffffffffu, l_row[r], 2);
+    }
+    float* mo = merge;                      // [4 warps][16 rows][DP]
+    float* mm = merge + 4 * 16 * DP;        // [4][16] max
+    float* ml = mm + 64;                    // [4][16] sum
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int row = g + r * 8;
+        if (t4 == 0) { mm[warp * 16 + row] = m_row[r]; ml[warp * 16 + row] = l_row[r]; }
+#pragma unroll
+        for (int i = 0; i < DP / 8; ++i) {
+            const int d = i * 8 + t4 * 2;
+            mo[(warp * 16 + row) * DP + d] = o[i][r * 2];
+            mo[(warp * 16 + row) * DP + d + 1] = o[i][r * 2 + 1];
+        }
+    }
+    __syncthreads();
+    for (int idx = tid; idx < rows * DP; idx += 128) {
+        const int row = idx / DP, d = idx % DP;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) M = fmaxf(M, mm[w * 16 + row]);
+        const float Mu = M == -INFINITY ? 0.f : M;
+        float acc = 0.f, L = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float f = exp2f(mm[w * 16 + row] - Mu);
+            acc += f * mo[(w * 16 + row) * DP + d];
+            L += f * ml[w * 16 + row];
+        }
+        const int head = h0 + row;
+        if (n_splits == 1) {
+            if (d < hd) out[(size_t)b * ldo + head * hd + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+        } else {
+            const size_t pidx = ((size_t)b * n_heads + head) * n_splits + split;
+            part_o[pidx * DP + d] = acc;
+            if (d == 0) { part_ml[pidx * 2] = M; part_ml[pidx * 2 + 1] = L; }
+        }
+    }
+}
+
+template <int DP>
+__global__ void attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                         bf16* __restrict__ out, int ldo, int n_heads, int hd, int n_splits) {
+    const int bh = blockIdx.x;                 // sequence * n_heads + head
+    const int b = bh / n_heads, head = bh % n_heads;
+    const int d = threadIdx.x;
+    if (d >= hd) return;
+    float M = -INFINITY;
+    for (int s = 0; s < n_splits; ++s) M = fmaxf(M, part_ml[((size_t)bh * n_splits + s) * 2]);
+    const float Mu = M == -INFINITY ? 0.f : M;
+    float acc = 0.f, L = 0.f;
+    for (int s = 0; s < n_splits; ++s) {
+        const size_t pidx = (size_t)bh * n_splits + s;
+        const float f = exp2f(part_ml[pidx * 2] - Mu);
+        acc += f * part_o[pidx * DP + d];
+        L += f * part_ml[pidx * 2 + 1];
+    }
+    out[(size_t)b * ldo + head * hd + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+}
+
+int padded_head_dim(int hd) {
+    if (hd <= 0 || hd % 16 != 0 || hd > 128) return 0;
+    if (hd <= 16) return 16;
+    if (hd <= 32) return 32;
+    if (hd <= 64) return 64;
+    return 128;
+}
+
+template <int DP>
+int launch_prefill(const bf16* q, int ldq, bf16* out, int ldo, const bf16* kc, const bf16* vc,
+                   long long page_stride, const int* block_table, int table_stride,
+                   const int* cu_seqlens, const int* slots, const int* start_pos,
+                   int B, int max_q_len, int n_heads, int n_kv, int hd, float scale, int window,
+                   cudaStream_t stream) {
+    static bool configured = false;
+    const int smem = 5 * 64 * DP * 2;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<DP>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    dim3 grid((max_q_len + 63) / 64, n_heads, B);
+    attention_prefill_kernel<DP><<<grid, 128, smem, stream>>>(q, ldq, out, ldo, kc, vc, page_stride,
+        block_table, table_stride, cu_seqlens, slots, start_pos, n_heads, n_kv, hd, scale, window);
+    return launch_status();
+}
+
+template <int DP>
+int launch_decode(const bf16* q, int ldq, bf16* out, int ldo, const bf16* kc, const bf16* vc,
+                  long long page_stride, const int* block_table, int table_stride,
+                  const int* slots, const int* positions, int B, int n_heads, int n_kv, int hd,
+                  float scale, int window, int n_splits, float* part_o, float* part_ml,
+                  cudaStream_t stream) {
+    static bool configured = false;
+    const int ring = kDecodeStages * 2 * 64 * DP * 2;
+    const int merge = (4 * 16 * DP + 128) * 4;
+    const int smem = 16 * DP * 2 + (ring > merge ? ring : merge);
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<DP>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    const int group = n_heads / n_kv;
+    dim3 grid(n_splits, n_kv * ((group + 15) / 16), B);
+    attention_decode_kernel<DP><<<grid, 128, smem, stream>>>(q, ldq, out, ldo, kc, vc, page_stride,
+        block_table, table_stride, slots, positions, n_heads, n_kv, hd, scale, window,
+        n_splits, part_o, part_ml);
+    int st = launch_status();
+    if (st != 0 || n_splits == 1) return st;
+    attention_combine_kernel<DP><<<B * n_heads, DP, 0, stream>>>(part_o, part_ml, out, ldo, n_heads, hd, n_splits);
+    return launch_status();
+}
+}  // namespace
+
+// Head sizes the tiled bfloat16 kernels serve (others go to the one-warp-per-row kernel).
+GTG_API int gtg_attention_bf16_supports(int hd) { return padded_head_dim(hd) != 0; }
+
+// Floats of scratch a decode call needs: (part_o, part_ml) for `n_splits` > 1.
+GTG_API long long gtg_attention_decode_scratch_floats(int B, int n_heads, int hd, int n_splits) {
+    const int dp = padded_head_dim(hd);
+    if (dp == 0 || n_splits <= 1) return 0;
+    return (long long)B * n_heads * n_splits * (dp + 2);
+}
+
+GTG_API int gtg_attention_prefill_bf16(const void* q, int ldq, void* out, int ldo,
+                                       const void* kc, const void* vc, long long page_stride,
+                                       const int* block_table, int table_stride,
+                                       const int* cu_seqlens, const int* slots, const int* start_pos,
+                                       int B, int max_q_len, int n_heads, int n_kv, int hd,
+                                       float scale, int window, cudaStream_t stream) {
+    if (B <= 0 || max_q_len <= 0) return 0;
+    if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv != 0 || ldq % 8 != 0 || ldo % 2 != 0) return kErrBadArgument;
+    if (n_heads > 65535 || B > 65535) return kErrUnsupported;
+#define GTG_ARGS (const bf16*)q, ldq, (bf16*)out, ldo, (const bf16*)kc, (const bf16*)vc, page_stride, \
+        block_table, table_stride, cu_seqlens, slots, start_pos, B, max_q_len, n_heads, n_kv, hd, scale, window, stream
+    switch (padded_head_dim(hd)) {
+        case 16: return launch_prefill<16>(GTG_ARGS);
+        case 32: return launch_prefill<32>(GTG_ARGS);
+        case 64: return launch_prefill<64>(GTG_ARGS);
+        case 128: return launch_prefill<128>(GTG_ARGS);
+        default: return kErrUnsupported;
+    }
+#undef GTG_ARGS
+}
+
+GTG_API int gtg_attention_decode_bf16(const void* q, int ldq, void* out, int ldo,
+                                      const void* kc, const void* vc, long long page_stride,
+                                      const int* block_table, int table_stride,
+                                      const int* slots, const int* positions,
+                                      int B, int n_heads, int n_kv, int hd, float scale, int window,
+                                      int n_splits, float* scratch, cudaStream_t stream) {
+    if (B <= 0) return 0;
+    if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv != 0 || ldq % 8 != 0 || n_splits < 1) return kErrBadArgument;
+    const int dp = padded_head_dim(hd);
+    if (dp == 0 || B > 65535 || n_splits > 65535) return kErrUnsupported;
+    if (n_splits > 1 && scratch == nullptr) return kErrBadArgument;
+    float* part_o = scratch;
+    float* part_ml = scratch ? scratch + (size_t)B * n_heads * n_splits * dp : nullptr;
+#define GTG_ARGS (const bf16*)q, ldq, (bf16*)out, ldo, (const bf16*)kc, (const bf16*)vc, page_stride, \
+        block_table, table_stride, slots, positions, B, n_heads, n_kv, hd, scale, window, n_splits, part_o, part_ml, stream
+    switch (dp) {
+        case 16: return launch_decode<16>(GTG_ARGS);
+        case 32: return launch_decode<32>(GTG_ARGS);
+        case 64: return launch_decode<64>(GTG_ARGS);
+        case 128: return launch_decode<128>(GTG_ARGS);
+        default: return kErrUnsupported;
+    }
+#undef GTG_ARGS
+}

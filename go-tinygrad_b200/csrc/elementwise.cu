@@ -1,0 +1,225 @@
+// Bandwidth-bound kernels around the matrix products: embedding gather, the
+// residual add fused with RMSNorm, SwiGLU, the rotary table of a step and the
+// rotation of queries and keys fused with the write into the paged cache.
+// Each is templated on the activation type (float for the 32-bit path,
+// __nv_bfloat16 for the serving path); sums, the reciprocal root, the rotation
+// and the residual stream are float in both.
+#include "common.cuh"
+
+// ---------------------------------------------------------------- embedding
+// out[n,:] = table[tokens[n],:] widened to float (the residual stream).  No
+// scaling (model/inference_helpers.go:9-34).  Token ids are validated by the
+// host; an id outside the table is clamped so the kernel never reads outside.
+template <typename T>
+__global__ void embed_kernel(const int* __restrict__ tokens, const T* __restrict__ table,
+                             float* __restrict__ out, int H, int V) {
+    const int n = blockIdx.x;
+    int tok = tokens[n];
+    tok = tok < 0 ? 0 : (tok >= V ? V - 1 : tok);
+    const T* src = table + (size_t)tok * H;
+    float* dst = out + (size_t)n * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = to_f32<T>(src[i]);
+}
+
+GTG_API int gtg_embed(int dtype, const int* tokens, const void* table, float* out,
+                      int N, int H, int V, cudaStream_t stream) {
+    if (N <= 0) return 0;
+    const int threads = H >= 1024 ? 256 : 128;
+    if (dtype == 0) embed_kernel<float><<<N, threads, 0, stream>>>(tokens, (const float*)table, out, H, V);
+    else if (dtype == 1) embed_kernel<bf16><<<N, threads, 0, stream>>>(tokens, (const bf16*)table, out, H, V);
+    else return kErrBadArgument;
+    return launch_status();
+}
+
+// ------------------------------------------------- residual add + RMSNorm
+// x = residual[r,:] (+ pending[r,:]);  out[i,:] = weight * x * (1/sqrt(mean(x^2)+eps))
+// with r = rows ? rows[i] : i.  Without `rows` the sum is written back to the
+// residual stream.  eps is added to the mean inside the root, and the product
+// is (w*x)*s (backends/simd/vec.go:72-85).
+template <typename T>
+__global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __restrict__ pending,
+                                   const float* __restrict__ weight, float eps,
+                                   T* __restrict__ out, const int* __restrict__ rows, int H) {
+    extern __shared__ float smem[];
+    float* row = smem;          // H floats
+    float* scratch = smem + H;  // 33 floats
+    const int i_out = blockIdx.x;
+    const int r = rows ? rows[i_out] : i_out;
+    float* res = residual + (size_t)r * H;
+    const T* pen = pending ? pending + (size_t)r * H : nullptr;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float x = res[i];
+        if (pen) {
+            x += to_f32<T>(pen[i]);
+            if (!rows) res[i] = x;
+        }
+        row[i] = x;
+        ss += x * x;
+    }
+    const float total = block_sum(ss, scratch);
+    const float s = 1.0f / sqrtf(total / (float)H + eps);
+    T* o = out + (size_t)i_out * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x)
+        o[i] = from_f32<T>((weight[i] * row[i]) * s);
+}
+
+GTG_API int gtg_add_rmsnorm(int dtype, float* residual, const void* pending, const float* weight,
+                            float eps, void* out, const int* rows, int R, int H,
+                            cudaStream_t stream) {
+    if (R <= 0) return 0;
+    int threads = 32;
+    while (threads < 1024 && threads * 4 < H) threads *= 2;
+    const size_t smem = (size_t)(H + 33) * sizeof(float);
+    if (smem > 200 * 1024) return kErrUnsupported;
+    cudaError_t e;
+    if (dtype == 0) {
+        if (smem > 48 * 1024) {
+            e = cudaFuncSetAttribute(add_rmsnorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return (int)e;
+        }
+        add_rmsnorm_kernel<float><<<R, threads, smem, stream>>>(residual, (const float*)pending, weight, eps, (float*)out, rows, H);
+    } else if (dtype == 1) {
+        if (smem > 48 * 1024) {
+            e = cudaFuncSetAttribute(add_rmsnorm_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return (int)e;
+        }
+        add_rmsnorm_kernel<bf16><<<R, threads, smem, stream>>>(residual, (const bf16*)pending, weight, eps, (bf16*)out, rows, H);
+    } else return kErrBadArgument;
+    return launch_status();
+}
+
+// ------------------------------------------------------------------ SwiGLU
+// out[m,i] = silu(gu[m,i]) * gu[m,I+i],  silu(g) = g / (1 + exp(-g))
+// (backends/simd/vec.go:52-59).  `gu` holds the gate columns then the up columns.
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int M, int I) {
+    const size_t total = (size_t)M * I;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t m = idx / I;
+        const int i = (int)(idx - m * I);
+        const float g = to_f32<T>(gu[m * 2 * I + i]);
+        const float u = to_f32<T>(gu[m * 2 * I + I + i]);
+        const float s = g / (1.0f + expf(-g));
+        out[idx] = from_f32<T>(s * u);
+    }
+}
+
+GTG_API int gtg_swiglu(int dtype, const void* gu, void* out, int M, int I, cudaStream_t stream) {
+    if (M <= 0 || I <= 0) return 0;
+    const size_t total = (size_t)M * I;
+    int blocks = (int)((total + 255) / 256);
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (dtype == 0) swiglu_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gu, (float*)out, M, I);
+    else if (dtype == 1) swiglu_kernel<bf16><<<blocks, 256, 0, stream>>>((const bf16*)gu, (bf16*)out, M, I);
+    else return kErrBadArgument;
+    return launch_status();
+}
+
+// ------------------------------------------------------------ rotary table
+// cos_sin[n,i] = (cos, sin)(positions[n] * inv_freq[i]); the angle is a double
+// product and the functions are evaluated in double, then rounded to float
+// (model/llama.go:855-862).  Computed once per step for the step's tokens.
+__global__ void rope_table_kernel(const int* __restrict__ positions, const double* __restrict__ inv_freq,
+                                  float2* __restrict__ cos_sin, int N, int half) {
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= N * half) return;
+    const int n = idx / half, i = idx - n * half;
+    const double ang = (double)positions[n] * inv_freq[i];
+    double s, c;
+    sincos(ang, &s, &c);
+    cos_sin[idx] = make_float2((float)c, (float)s);
+}
+
+GTG_API int gtg_rope_table(const int* positions, const double* inv_freq, float* cos_sin,
+                           int N, int half, cudaStream_t stream) {
+    if (N <= 0 || half <= 0) return 0;
+    const int total = N * half;
+    rope_table_kernel<<<(total + 127) / 128, 128, 0, stream>>>(positions, inv_freq, (float2*)cos_sin, N, half);
+    return launch_status();
+}
+
+// ------------------------------------------- rotation + write into the cache
+// For token n with fused projections qkv[n] = [q heads | k heads | v heads]:
+// rotate q in place and k on its way into the cache, half-split pairs
+// (i, i+hd/2): a' = a*c - b*s, b' = a*s + b*c (model/llama.go:1556-1589); copy v
+// into the cache.  Keys are stored after rotation (model/llama.go:1253-1254).
+// With n_kv_store == 0 only the queries are rotated (a layer that reads another
+// layer's cache).  cos_sin == nullptr means no rotation.
+template <typename T>
+__global__ void rope_kv_store_kernel(T* __restrict__ qkv, int ld, const float2* __restrict__ cos_sin,
+                                     int n_heads, int n_kv_store, int hd,
+                                     T* __restrict__ kc, T* __restrict__ vc, long long page_stride,
+                                     const int* __restrict__ block_table, int table_stride,
+                                     const int* __restrict__ token_seq, const int* __restrict__ slots,
+                                     const int* __restrict__ positions) {
+    const int n = blockIdx.x;
+    const int half = hd >> 1;
+    const int pos = positions[n];
+    T* row = qkv + (size_t)n * ld;
+    size_t cache_off = 0;
+    if (n_kv_store > 0) {
+        const int slot = slots[token_seq[n]];
+        const int page = block_table[(size_t)slot * table_stride + pos / kPageTokens];
+        cache_off = (size_t)page * page_stride + (size_t)(pos % kPageTokens) * hd;
+    }
+    const int items = (n_heads + 2 * n_kv_store) * half;
+    for (int it = threadIdx.x; it < items; it += blockDim.x) {
+        const int head = it / half, i = it - head * half;
+        T* src = row + head * hd;
+        const float a = to_f32<T>(src[i]), b = to_f32<T>(src[i + half]);
+        if (head < n_heads + n_kv_store) {
+            float c = 1.f, s = 0.f;
+            if (cos_sin) { const float2 cs = cos_sin[(size_t)n * half + i]; c = cs.x; s = cs.y; }
+            const float ra = a * c - b * s, rb = a * s + b * c;
+            if (head < n_heads) {
+                src[i] = from_f32<T>(ra);
+                src[i + half] = from_f32<T>(rb);
+            } else {
+                T* dst = kc + cache_off + (size_t)(head - n_heads) * kPageTokens * hd;
+                dst[i] = from_f32<T>(ra);
+                dst[i + half] = from_f32<T>(rb);
+            }
+        } else {
+            T* dst = vc + cache_off + (size_t)(head - n_heads - n_kv_store) * kPageTokens * hd;
+            dst[i] = src[i];
+            dst[i + half] = src[i + half];
+        }
+    }
+}
+
+GTG_API int gtg_rope_kv_store(int dtype, void* qkv, int ld, const float* cos_sin,
+                              int n_heads, int n_kv_store, int hd,
+                              void* kc, void* vc, long long page_stride,
+                              const int* block_table, int table_stride,
+                              const int* token_seq, const int* slots, const int* positions,
+                              int N, cudaStream_t stream) {
+    if (N <= 0) return 0;
+    if (hd <= 0 || (hd & 1)) return kErrBadArgument;
+    const int items = (n_heads + 2 * n_kv_store) * (hd / 2);
+    int threads = 64;
+    while (threads < 512 && threads < items) threads *= 2;
+    if (dtype == 0)
+        rope_kv_store_kernel<float><<<N, threads, 0, stream>>>((float*)qkv, ld, (const float2*)cos_sin, n_heads, n_kv_store, hd,
+            (float*)kc, (float*)vc, page_stride, block_table, table_stride, token_seq, slots, positions);
+    else if (dtype == 1)
+        rope_kv_store_kernel<bf16><<<N, threads, 0, stream>>>((bf16*)qkv, ld, (const float2*)cos_sin, n_heads, n_kv_store, hd,
+            (bf16*)kc, (bf16*)vc, page_stride, block_table, table_stride, token_seq, slots, positions);
+    else return kErrBadArgument;
+    return launch_status();
+}
+
+// --------------------------------------------------- advance a decode batch
+// Between two decode steps that never leave the device: the sampled token
+// becomes the next input and every position moves on by one.
+__global__ void advance_kernel(int* tokens, int* positions, const int* sampled, int B) {
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b < B) { tokens[b] = sampled[b]; positions[b] += 1; }
+}
+
+GTG_API int gtg_advance(int* tokens, int* positions, const int* sampled, int B, cudaStream_t stream) {
+    if (B <= 0) return 0;
+    advance_kernel<<<(B + 127) / 128, 128, 0, stream>>>(tokens, positions, sampled, B);
+    return launch_status();
+}

@@ -1,0 +1,282 @@
+"""Tensor-level entry points of the hand-written kernels.
+
+Each function checks shapes, dtypes and layout on the host, then calls the C
+launcher of the compiled library on the current CUDA stream.  A size that a
+kernel does not take is refused here with a `KernelError` that says why; there
+is no other route for the same work (no library attention, no CPU path).
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_ulonglong, c_void_p
+from typing import Optional
+
+import torch
+
+from . import build
+
+PAGE_TOKENS = 64
+
+_P, _I, _L, _F, _U = c_void_p, c_int, c_longlong, c_float, c_ulonglong
+
+# library, symbol -> argument types (the stream is always last)
+_SIGNATURES = {
+    "gtg_embed": ("elementwise", [_I, _P, _P, _P, _I, _I, _I, _P]),
+    "gtg_add_rmsnorm": ("elementwise", [_I, _P, _P, _P, _F, _P, _P, _I, _I, _P]),
+    "gtg_swiglu": ("elementwise", [_I, _P, _P, _I, _I, _P]),
+    "gtg_rope_table": ("elementwise", [_P, _P, _P, _I, _I, _P]),
+    "gtg_rope_kv_store": ("elementwise", [_I, _P, _I, _P, _I, _I, _I, _P, _P, _L, _P, _I, _P, _P, _P, _I, _P]),
+    "gtg_advance": ("elementwise", [_P, _P, _P, _I, _P]),
+    "gtg_gemm_f32": ("gemm_f32", [_P, _I, _P, _I, _P, _I, _I, _I, _I, _P]),
+    "gtg_gemm_bf16_mma": ("gemm_bf16_mma", [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _P]),
+    "gtg_attention_simple": ("attention_simple", [_I, _P, _I, _P, _I, _P, _P, _L, _P, _I, _P, _P, _P,
+                                                  _I, _I, _I, _I, _F, _I, _P]),
+    "gtg_attention_bf16_supports": ("attention_bf16", [_I]),
+    "gtg_attention_decode_scratch_floats": ("attention_bf16", [_I, _I, _I, _I]),
+    "gtg_attention_prefill_bf16": ("attention_bf16", [_P, _I, _P, _I, _P, _P, _L, _P, _I, _P, _P, _P,
+                                                      _I, _I, _I, _I, _I, _F, _I, _P]),
+    "gtg_attention_decode_bf16": ("attention_bf16", [_P, _I, _P, _I, _P, _P, _L, _P, _I, _P, _P,
+                                                     _I, _I, _I, _I, _F, _I, _I, _P, _P]),
+    "gtg_argmax": ("sampling", [_P, _I, _I, _I, _P, _P]),
+    "gtg_sample_temperature": ("sampling", [_P, _I, _I, _I, _F, _U, _P, _P, _P, _P]),
+}
+_RESTYPES = {"gtg_attention_decode_scratch_floats": c_longlong}
+
+_FUNCS = {}
+
+
+class KernelError(RuntimeError):
+    """A kernel refused its arguments or its launch failed."""
+
+
+def _fn(symbol: str):
+    f = _FUNCS.get(symbol)
+    if f is None:
+        lib_name, argtypes = _SIGNATURES[symbol]
+        if not torch.cuda.is_available():
+            raise KernelError(f"{symbol}: no CUDA device; this library runs on the GPU only "
+                              f"and has no CPU path")
+        f = getattr(build.library(lib_name), symbol)
+        f.argtypes = argtypes
+        f.restype = _RESTYPES.get(symbol, c_int)
+        _FUNCS[symbol] = f
+    return f
+
+
+_CODES = {-1: "bad argument", -2: "size not supported by this kernel"}
+
+
+def _check(code: int, what: str) -> None:
+    if code != 0:
+        if code in _CODES:
+            raise KernelError(f"{what}: {_CODES[code]}")
+        raise KernelError(f"{what}: CUDA error {code} (cudaError_t)")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _dt(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return 0
+    if t.dtype == torch.bfloat16:
+        return 1
+    raise KernelError(f"dtype {t.dtype} is not supported (float32 or bfloat16)")
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _need(cond: bool, msg: str) -> None:
+    if not cond:
+        raise KernelError(msg)
+
+
+def _rows2d(t: torch.Tensor, name: str) -> None:
+    _need(t.dim() == 2 and t.stride(1) == 1, f"{name} must be 2-D with a unit inner stride, "
+                                             f"got shape {tuple(t.shape)} strides {t.stride()}")
+
+
+# ------------------------------------------------------------------ elementwise
+def embed(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> None:
+    """out[n,:] (float32) = table[tokens[n],:]."""
+    N, (V, H) = tokens.numel(), table.shape
+    _need(tokens.dtype == torch.int32 and tokens.is_contiguous(), "embed: tokens must be contiguous int32")
+    _need(table.is_contiguous() and out.is_contiguous() and out.dtype == torch.float32
+          and tuple(out.shape) == (N, H), "embed: out must be contiguous float32 [N, H]")
+    _check(_fn("gtg_embed")(_dt(table), _ptr(tokens), _ptr(table), _ptr(out), N, H, V, _stream()), "embed")
+
+
+def add_rmsnorm(residual: torch.Tensor, pending: Optional[torch.Tensor], weight: torch.Tensor,
+                eps: float, out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> None:
+    """residual (+= pending); out = rmsnorm(residual) * weight.  With `rows` only
+    those rows are read (nothing is written back) and out has len(rows) rows."""
+    H = residual.shape[1]
+    R = rows.numel() if rows is not None else residual.shape[0]
+    _need(residual.dtype == torch.float32 and residual.is_contiguous(), "add_rmsnorm: residual must be contiguous float32")
+    _need(weight.dtype == torch.float32 and weight.is_contiguous() and weight.numel() == H,
+          "add_rmsnorm: weight must be float32 [H]")
+    _need(out.is_contiguous() and tuple(out.shape) == (R, H), "add_rmsnorm: out must be contiguous [rows, H]")
+    if pending is not None:
+        _need(pending.dtype == out.dtype and pending.is_contiguous() and pending.shape == residual.shape,
+              "add_rmsnorm: pending must match the residual's shape and out's dtype")
+    if rows is not None:
+        _need(rows.dtype == torch.int32 and rows.is_contiguous(), "add_rmsnorm: rows must be contiguous int32")
+    _check(_fn("gtg_add_rmsnorm")(_dt(out), _ptr(residual), _ptr(pending), _ptr(weight), float(eps),
+                                  _ptr(out), _ptr(rows), R, H, _stream()), "add_rmsnorm")
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out[m,i] = silu(gate_up[m,i]) * gate_up[m,I+i]."""
+    M, two_i = gate_up.shape
+    _need(two_i % 2 == 0 and gate_up.is_contiguous() and out.is_contiguous()
+          and tuple(out.shape) == (M, two_i // 2) and out.dtype == gate_up.dtype,
+          "swiglu: gate_up [M, 2I] and out [M, I] must be contiguous and of one dtype")
+    _check(_fn("gtg_swiglu")(_dt(out), _ptr(gate_up), _ptr(out), M, two_i // 2, _stream()), "swiglu")
+
+
+def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, out: torch.Tensor) -> None:
+    """out[n,i] = (cos, sin)(positions[n] * inv_freq[i]), angle and functions in float64."""
+    N, half = positions.numel(), inv_freq.numel()
+    _need(positions.dtype == torch.int32 and positions.is_contiguous(), "rope_table: positions must be int32")
+    _need(inv_freq.dtype == torch.float64 and inv_freq.is_contiguous(), "rope_table: inv_freq must be float64")
+    _need(out.dtype == torch.float32 and out.is_contiguous() and tuple(out.shape) == (N, half, 2),
+          "rope_table: out must be float32 [N, half, 2]")
+    _check(_fn("gtg_rope_table")(_ptr(positions), _ptr(inv_freq), _ptr(out), N, half, _stream()), "rope_table")
+
+
+def rope_kv_store(qkv: torch.Tensor, cos_sin: Optional[torch.Tensor], n_heads: int, n_kv_store: int,
+                  head_dim: int, kv, token_seq: torch.Tensor, slots: torch.Tensor,
+                  positions: torch.Tensor) -> None:
+    """Rotate the query heads of qkv in place; rotate the key heads and copy the
+    value heads into the cache `kv` at each token's (slot, position).  With
+    n_kv_store == 0 only queries are rotated and `kv` may be None."""
+    _rows2d(qkv, "rope_kv_store: qkv")
+    N = qkv.shape[0]
+    _need(head_dim % 2 == 0, "rope_kv_store: head_dim must be even")
+    _need(qkv.shape[1] >= (n_heads + 2 * n_kv_store) * head_dim, "rope_kv_store: qkv is too narrow")
+    if cos_sin is not None:
+        _need(cos_sin.dtype == torch.float32 and cos_sin.is_contiguous()
+              and tuple(cos_sin.shape) == (N, head_dim // 2, 2), "rope_kv_store: cos_sin must be float32 [N, hd/2, 2]")
+    for name, t in (("token_seq", token_seq), ("slots", slots), ("positions", positions)):
+        _need(t.dtype == torch.int32 and t.is_contiguous(), f"rope_kv_store: {name} must be contiguous int32")
+    if n_kv_store > 0:
+        _need(kv is not None and kv.k.dtype == qkv.dtype and kv.head_dim == head_dim
+              and kv.n_kv_heads == n_kv_store, "rope_kv_store: cache entry does not match the heads to store")
+        args = (_ptr(kv.k), _ptr(kv.v), kv.page_stride, _ptr(kv.block_table), kv.table_stride)
+    else:
+        args = (None, None, 0, None, 0)
+    _check(_fn("gtg_rope_kv_store")(_dt(qkv), _ptr(qkv), qkv.stride(0), _ptr(cos_sin), n_heads, n_kv_store,
+                                    head_dim, *args, _ptr(token_seq), _ptr(slots), _ptr(positions),
+                                    N, _stream()), "rope_kv_store")
+
+
+def advance(tokens: torch.Tensor, positions: torch.Tensor, sampled: torch.Tensor) -> None:
+    """tokens <- sampled; positions += 1 (between decode steps that stay on the device)."""
+    B = tokens.numel()
+    _check(_fn("gtg_advance")(_ptr(tokens), _ptr(positions), _ptr(sampled), B, _stream()), "advance")
+
+
+# ---------------------------------------------------------------- matrix products
+def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out[M,N] = x[M,K] . w[N,K]^T.  float32 operands take the true 32-bit
+    kernel; bfloat16 operands accumulate in float and write bfloat16 or float32."""
+    _rows2d(x, "linear: x"); _rows2d(w, "linear: w"); _rows2d(out, "linear: out")
+    M, K = x.shape
+    N = w.shape[0]
+    _need(w.shape[1] == K and tuple(out.shape) == (M, N), f"linear: shapes {tuple(x.shape)} x {tuple(w.shape)} -> {tuple(out.shape)}")
+    if x.dtype == torch.float32:
+        _need(w.dtype == torch.float32 and out.dtype == torch.float32, "linear: float32 x needs float32 w and out")
+        _check(_fn("gtg_gemm_f32")(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0),
+                                   M, N, K, _stream()), "linear(float32)")
+        return
+    _need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16, "linear: operands must both be bfloat16 or both float32")
+    _need(out.dtype in (torch.bfloat16, torch.float32), "linear: out must be bfloat16 or float32")
+    _need(K % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0,
+          f"linear(bfloat16): the inner size {K} and the row strides must be multiples of 8")
+    _check(_fn("gtg_gemm_bf16_mma")(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0),
+                                    1 if out.dtype == torch.float32 else 0, M, N, K, _stream()),
+           "linear(bfloat16)")
+
+
+# ----------------------------------------------------------------------- attention
+def attention_bf16_supports(head_dim: int) -> bool:
+    return bool(_fn("gtg_attention_bf16_supports")(head_dim))
+
+
+def attention_simple(q: torch.Tensor, out: torch.Tensor, kv, token_seq, slots, positions,
+                     n_heads: int, scale: float, window: int = 0) -> None:
+    """One warp per (token, head): the float32 path's attention, for prompts and
+    decode steps alike."""
+    _rows2d(q, "attention: q"); _rows2d(out, "attention: out")
+    N = q.shape[0]
+    _need(kv.k.dtype == q.dtype == out.dtype, "attention: q, out and the cache must share a dtype")
+    _need(kv.head_dim <= 256, f"attention: head_dim {kv.head_dim} exceeds 256")
+    _check(_fn("gtg_attention_simple")(_dt(q), _ptr(q), q.stride(0), _ptr(out), out.stride(0),
+                                       _ptr(kv.k), _ptr(kv.v), kv.page_stride, _ptr(kv.block_table),
+                                       kv.table_stride, _ptr(token_seq), _ptr(slots), _ptr(positions),
+                                       N, n_heads, kv.n_kv_heads, kv.head_dim, float(scale), int(window),
+                                       _stream()), "attention_simple")
+
+
+def attention_prefill_bf16(q, out, kv, cu_seqlens, slots, start_pos, n_seqs: int, max_q_len: int,
+                           n_heads: int, scale: float, window: int = 0) -> None:
+    _rows2d(q, "attention: q"); _rows2d(out, "attention: out")
+    _need(q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and kv.k.dtype == torch.bfloat16,
+          "attention_prefill_bf16: bfloat16 only")
+    _need(attention_bf16_supports(kv.head_dim),
+          f"attention_prefill_bf16: head_dim {kv.head_dim} is not a multiple of 16 up to 128")
+    _check(_fn("gtg_attention_prefill_bf16")(_ptr(q), q.stride(0), _ptr(out), out.stride(0),
+                                             _ptr(kv.k), _ptr(kv.v), kv.page_stride, _ptr(kv.block_table),
+                                             kv.table_stride, _ptr(cu_seqlens), _ptr(slots), _ptr(start_pos),
+                                             n_seqs, max_q_len, n_heads, kv.n_kv_heads, kv.head_dim,
+                                             float(scale), int(window), _stream()), "attention_prefill_bf16")
+
+
+def attention_decode_scratch_floats(n_seqs: int, n_heads: int, head_dim: int, n_splits: int) -> int:
+    return int(_fn("gtg_attention_decode_scratch_floats")(n_seqs, n_heads, head_dim, n_splits))
+
+
+def attention_decode_bf16(q, out, kv, slots, positions, n_heads: int, scale: float, window: int,
+                          n_splits: int, scratch: Optional[torch.Tensor]) -> None:
+    _rows2d(q, "attention: q"); _rows2d(out, "attention: out")
+    B = q.shape[0]
+    _need(q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and kv.k.dtype == torch.bfloat16,
+          "attention_decode_bf16: bfloat16 only")
+    _need(attention_bf16_supports(kv.head_dim),
+          f"attention_decode_bf16: head_dim {kv.head_dim} is not a multiple of 16 up to 128")
+    if n_splits > 1:
+        need = attention_decode_scratch_floats(B, n_heads, kv.head_dim, n_splits)
+        _need(scratch is not None and scratch.dtype == torch.float32 and scratch.is_contiguous()
+              and scratch.numel() >= need, f"attention_decode_bf16: scratch needs {need} floats")
+    _check(_fn("gtg_attention_decode_bf16")(_ptr(q), q.stride(0), _ptr(out), out.stride(0),
+                                            _ptr(kv.k), _ptr(kv.v), kv.page_stride, _ptr(kv.block_table),
+                                            kv.table_stride, _ptr(slots), _ptr(positions), B, n_heads,
+                                            kv.n_kv_heads, kv.head_dim, float(scale), int(window),
+                                            int(n_splits), _ptr(scratch), _stream()), "attention_decode_bf16")
+
+
+# ------------------------------------------------------------------------ sampling
+def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
+    """out[r] = first index of the maximum of logits[r,:]."""
+    _rows2d(logits, "argmax: logits")
+    R, V = logits.shape
+    _need(logits.dtype == torch.float32 and out.dtype == torch.int32 and out.numel() >= R and out.is_contiguous(),
+          "argmax: logits float32, out int32 [R]")
+    _check(_fn("gtg_argmax")(_ptr(logits), logits.stride(0), R, V, _ptr(out), _stream()), "argmax")
+
+
+def sample_temperature(logits: torch.Tensor, temperature: float, seed: int, sequence_ids: torch.Tensor,
+                       steps: torch.Tensor, out: torch.Tensor) -> None:
+    """out[r] ~ softmax(logits[r,:] / temperature), drawn with the uniform that
+    (seed, sequence_ids[r], steps[r]) determine."""
+    _rows2d(logits, "sample: logits")
+    R, V = logits.shape
+    _need(temperature > 0, "sample_temperature: the temperature must be positive (0 means greedy: use argmax)")
+    for name, t in (("sequence_ids", sequence_ids), ("steps", steps), ("out", out)):
+        _need(t.dtype == torch.int32 and t.is_contiguous() and t.numel() >= R, f"sample: {name} must be int32 [R]")
+    _check(_fn("gtg_sample_temperature")(_ptr(logits), logits.stride(0), R, V, float(temperature),
+                                         int(seed) & (2**64 - 1), _ptr(sequence_ids), _ptr(steps),
+                                         _ptr(out), _stream()), "sample_temperature")

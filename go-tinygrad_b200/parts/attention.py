@@ -1,0 +1,107 @@
+"""Grouped-query attention with a position encoding on queries and keys.
+
+q, k, v = x Wq^T, x Wk^T, x Wv^T; rotate q and k; store k (after rotation) and
+v in the cache; per query head h, softmax((q_h . K_{h // group}) * scale) V,
+causal within the sequence, optionally over the last `window` keys only; then
+the output projection (model/llama.go:1111-1137 projections, :1230-1233
+rotation, :1253-1254 cache write, :1603-1661 attention, :1290-1297 output).
+
+Parameters: ``hidden_size``, ``n_heads``, ``n_kv_heads``, ``head_dim``,
+``window`` (None: all keys), ``scale`` (None: head_dim^-1/2), ``position`` (a
+position PartSpec), ``own_kv`` (False for a layer that has no key/value
+projections and reads another run's cache), and the tensor names ``q``, ``k``,
+``v``, ``o``.  The three projections are fused at load into one matrix
+[(n_heads + 2 n_kv_heads) * head_dim, hidden] so that one product serves them.
+"""
+from __future__ import annotations
+
+import math
+from typing import List, Mapping, Optional
+
+import torch
+
+from ..cache import CacheHandle, KVRequest, Request
+from ..kernels import ops
+from ..weights.binder import WeightSpec
+from .base import Mixer, Runtime, StepContext, build_part, register_part
+
+_TARGET_CTAS = 2 * 148      # decode attention: fill the SMs about twice over
+
+
+@register_part("mixer", "gqa_attention")
+class GQAttention(Mixer):
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.hidden = int(self.param("hidden_size"))
+        self.n_heads = int(self.param("n_heads"))
+        self.n_kv = int(self.param("n_kv_heads"))
+        self.head_dim = int(self.param("head_dim"))
+        if self.n_heads % self.n_kv:
+            raise ValueError(f"{self.n_heads} query heads cannot share {self.n_kv} key/value heads")
+        window = self.p.get("window")
+        self.window = int(window) if window else None
+        scale = self.p.get("scale")
+        self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(self.head_dim)
+        self.own_kv = bool(self.p.get("own_kv", True))
+        self.position = build_part("position", self.param("position"))
+        self.names = {k: str(self.param(k)) for k in (("q", "k", "v", "o") if self.own_kv else ("q", "o"))}
+        self.q_dim = self.n_heads * self.head_dim
+        self.kv_dim = self.n_kv * self.head_dim
+        self.w_qkv: Optional[torch.Tensor] = None
+        self.w_o: Optional[torch.Tensor] = None
+
+    def weight_specs(self) -> List[WeightSpec]:
+        specs = [WeightSpec(self.names["q"], (self.q_dim, self.hidden))]
+        if self.own_kv:
+            specs += [WeightSpec(self.names["k"], (self.kv_dim, self.hidden)),
+                      WeightSpec(self.names["v"], (self.kv_dim, self.hidden))]
+        specs.append(WeightSpec(self.names["o"], (self.hidden, self.q_dim)))
+        return specs + self.position.weight_specs()
+
+    def cache_requests(self) -> List[Request]:
+        return [KVRequest(self.n_kv, self.head_dim, self.window)] if self.own_kv else []
+
+    def load(self, tensors: Mapping[str, torch.Tensor], rt: Runtime) -> None:
+        parts = [tensors[self.names["q"]]]
+        if self.own_kv:
+            parts += [tensors[self.names["k"]], tensors[self.names["v"]]]
+        self.w_qkv = rt.matrix(torch.cat([p.to(rt.dtype) for p in parts], dim=0))
+        self.w_o = rt.matrix(tensors[self.names["o"]])
+        self.position.load(tensors, rt)
+
+    def _decode_splits(self, ctx: StepContext) -> int:
+        per_split_one = ctx.n_seqs * self.n_kv * ((self.n_heads // self.n_kv + 15) // 16)
+        return max(1, min(32, (_TARGET_CTAS + per_split_one - 1) // per_split_one))
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheHandle) -> torch.Tensor:
+        rt = ctx.rt
+        kv = cache.kv
+        if kv is None or kv.n_kv_heads != self.n_kv or kv.head_dim != self.head_dim:
+            raise ValueError("attention was given a cache entry that does not match its heads")
+        n = x.shape[0]
+        qkv = rt.empty(n, self.w_qkv.shape[0])
+        ops.linear(x, self.w_qkv, qkv)
+        store = self.n_kv if (cache.writes and self.own_kv) else 0
+        ops.rope_kv_store(qkv, self.position.rotation(ctx), self.n_heads, store, self.head_dim,
+                          kv, ctx.token_seq, ctx.slots, ctx.positions)
+        q = qkv[:, : self.q_dim]
+        mixed = rt.empty(n, self.q_dim)
+        window = self.window or 0
+        if rt.dtype == torch.bfloat16 and ops.attention_bf16_supports(self.head_dim):
+            if ctx.is_decode:
+                splits = self._decode_splits(ctx)
+                scratch = None
+                if splits > 1:
+                    scratch = rt.empty(ops.attention_decode_scratch_floats(
+                        n, self.n_heads, self.head_dim, splits), dtype=torch.float32)
+                ops.attention_decode_bf16(q, mixed, kv, ctx.slots, ctx.positions, self.n_heads,
+                                          self.scale, window, splits, scratch)
+            else:
+                ops.attention_prefill_bf16(q, mixed, kv, ctx.cu_seqlens, ctx.slots, ctx.start_pos,
+                                           ctx.n_seqs, ctx.max_q_len, self.n_heads, self.scale, window)
+        else:
+            ops.attention_simple(q, mixed, kv, ctx.token_seq, ctx.slots, ctx.positions,
+                                 self.n_heads, self.scale, window)
+        out = rt.empty(n, self.hidden)
+        ops.linear(mixed, self.w_o, out)
+        return out

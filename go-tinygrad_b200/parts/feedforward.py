@@ -1,0 +1,48 @@
+"""Dense gated feed-forward (SwiGLU): down(silu(gate(x)) * up(x)), silu(g) =
+g / (1 + exp(-g)) (model/llama.go:1361-1401, backends/simd/vec.go:52-59).
+
+Parameters: ``hidden_size``, ``intermediate_size`` and the tensor names
+``gate``, ``up``, ``down``.  Gate and up are fused at load into one matrix
+[2 * intermediate, hidden] (gate rows first) so that one product serves both.
+"""
+from __future__ import annotations
+
+from typing import List, Mapping, Optional
+
+import torch
+
+from ..kernels import ops
+from ..weights.binder import WeightSpec
+from .base import FeedForward, Runtime, StepContext, register_part
+
+
+@register_part("feed_forward", "swiglu")
+class SwiGLU(FeedForward):
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.hidden = int(self.param("hidden_size"))
+        self.inter = int(self.param("intermediate_size"))
+        self.names = {k: str(self.param(k)) for k in ("gate", "up", "down")}
+        self.w_gate_up: Optional[torch.Tensor] = None
+        self.w_down: Optional[torch.Tensor] = None
+
+    def weight_specs(self) -> List[WeightSpec]:
+        return [WeightSpec(self.names["gate"], (self.inter, self.hidden)),
+                WeightSpec(self.names["up"], (self.inter, self.hidden)),
+                WeightSpec(self.names["down"], (self.hidden, self.inter))]
+
+    def load(self, tensors: Mapping[str, torch.Tensor], rt: Runtime) -> None:
+        self.w_gate_up = rt.matrix(torch.cat([tensors[self.names["gate"]].to(rt.dtype),
+                                              tensors[self.names["up"]].to(rt.dtype)], dim=0))
+        self.w_down = rt.matrix(tensors[self.names["down"]])
+
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        rt = ctx.rt
+        n = x.shape[0]
+        gate_up = rt.empty(n, 2 * self.inter)
+        ops.linear(x, self.w_gate_up, gate_up)
+        act = rt.empty(n, self.inter)
+        ops.swiglu(gate_up, act)
+        out = rt.empty(n, self.hidden)
+        ops.linear(act, self.w_down, out)
+        return out

@@ -1,0 +1,98 @@
+"""The plan of a model: what its layers are made of and the order they run in.
+
+A plan is data.  An architecture's registry entry produces it from the typed
+configuration; the engine builds parts from it and runs the schedule.  No part
+knows which model it is in: a part sees only its own `PartSpec` (a kind, looked
+up in the part registries, and its sizes and constants as parameters).
+
+The reference does the opposite: one loop body with ``if ModelType == ...``
+branches (model/llama.go:1094-1455) and per-layer flags such as ``HasKV`` and
+``KVSourceLayer`` (model/llama.go:679-695, model/kv_staging.go:11-54) for layers
+that reuse another layer's cache.  Those needs are expressed here as schedule
+entries.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, List, Mapping, Optional, Tuple
+
+
+@dataclass(frozen=True)
+class PartSpec:
+    """`kind` names a registered part of its category; `params` are its sizes,
+    constants, weight names and nested PartSpecs (e.g. a mixer's position
+    encoding)."""
+    kind: str
+    params: Mapping[str, Any] = field(default_factory=dict)
+
+
+@dataclass(frozen=True)
+class LayerSpec:
+    """One layer: an arrangement (`block`) of a mixer and a feed-forward, each
+    behind its norm.  Every layer carries its own specs, so mixers and
+    feed-forwards may differ from layer to layer."""
+    block: PartSpec
+    mixer_norm: PartSpec
+    mixer: PartSpec
+    feed_forward_norm: PartSpec
+    feed_forward: PartSpec
+
+
+@dataclass(frozen=True)
+class ScheduleEntry:
+    """One run of a layer.  `cache` is the index of the schedule entry whose
+    cache storage this run uses: None means its own.  An entry that points at
+    another entry reads that entry's keys and values and writes none
+    (`writes_cache` is then False).  A layer may appear in several entries; each
+    entry that writes has storage of its own."""
+    layer: int
+    cache: Optional[int] = None
+
+    @property
+    def writes_cache(self) -> bool:
+        return self.cache is None
+
+
+@dataclass(frozen=True)
+class ModelPlan:
+    hidden_size: int
+    vocab_size: int
+    embedding: PartSpec
+    layers: Tuple[LayerSpec, ...]
+    schedule: Tuple[ScheduleEntry, ...]
+    final_norm: PartSpec
+    head: PartSpec
+    stop_tokens: Tuple[int, ...] = ()
+    max_position: Optional[int] = None
+
+    def check(self) -> None:
+        for i, e in enumerate(self.schedule):
+            if not 0 <= e.layer < len(self.layers):
+                raise ValueError(f"schedule entry {i} names layer {e.layer}; "
+                                 f"the plan has {len(self.layers)} layers")
+            if e.cache is not None:
+                if not 0 <= e.cache < i:
+                    raise ValueError(f"schedule entry {i} reads the cache of entry {e.cache}, "
+                                     f"which does not run before it")
+                if self.schedule[e.cache].cache is not None:
+                    raise ValueError(f"schedule entry {i} reads the cache of entry {e.cache}, "
+                                     f"which has no storage of its own")
+
+
+def default_schedule(n_layers: int) -> Tuple[ScheduleEntry, ...]:
+    return tuple(ScheduleEntry(layer=i) for i in range(n_layers))
+
+
+def plan_weight_specs(plan: ModelPlan) -> List[Any]:
+    """Every tensor the plan's parts declare, built without touching a device."""
+    from .base import build_part  # late import: base imports this module
+    specs = []
+    specs += build_part("embedding", plan.embedding).weight_specs()
+    for layer in plan.layers:
+        for category, spec in (("norm", layer.mixer_norm), ("mixer", layer.mixer),
+                               ("norm", layer.feed_forward_norm),
+                               ("feed_forward", layer.feed_forward)):
+            specs += build_part(category, spec).weight_specs()
+    specs += build_part("norm", plan.final_norm).weight_specs()
+    specs += build_part("head", plan.head).weight_specs()
+    return specs
