@@ -66,19 +66,28 @@ def _digest(source: str) -> str:
     return h.hexdigest()[:16]
 
 
+_BUILD_DIR: Optional[str] = None
+_BUILD_DIR_LOCK = threading.Lock()
+
+
 def build_dir() -> str:
-    in_tree = os.path.join(CSRC, "_build")
-    try:
-        os.makedirs(in_tree, exist_ok=True)
-        probe = os.path.join(in_tree, f".w{os.getpid()}")
-        with open(probe, "w"):
-            pass
-        os.remove(probe)
-        return in_tree
-    except OSError:
-        alt = os.path.join(tempfile.gettempdir(), f"go_tinygrad_b200_build_{os.getuid()}")
-        os.makedirs(alt, exist_ok=True)
-        return alt
+    """``csrc/_build`` inside the package if it can be written, else a per-user
+    folder under the system's temporary directory."""
+    global _BUILD_DIR
+    with _BUILD_DIR_LOCK:
+        if _BUILD_DIR is None:
+            in_tree = os.path.join(CSRC, "_build")
+            try:
+                os.makedirs(in_tree, exist_ok=True)
+                fd, probe = tempfile.mkstemp(prefix=".probe", dir=in_tree)
+                os.close(fd)
+                os.remove(probe)
+                _BUILD_DIR = in_tree
+            except OSError:
+                alt = os.path.join(tempfile.gettempdir(), f"go_tinygrad_b200_build_{os.getuid()}")
+                os.makedirs(alt, exist_ok=True)
+                _BUILD_DIR = alt
+        return _BUILD_DIR
 
 
 def _say(msg: str) -> None:

@@ -1,0 +1,383 @@
+"""Each kernel alone against a plain PyTorch float32 reference of the same
+operation, at sizes other than the engine tests use: widths and vocabularies
+that are no power of two, every head size in steps of 16, ragged batches, pages
+scattered over the cache, and inputs made so that a wrong key shows."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import go_tinygrad_b200  # noqa: F401
+from go_tinygrad_b200.cache import Cache, KVRequest
+from go_tinygrad_b200.kernels import ops
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype):
+    return dict(rtol=2e-5, atol=2e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
+
+
+def rnd(*shape, dtype=torch.float32, scale=1.0, seed=0):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(dtype).to(DEV)
+
+
+# ------------------------------------------------------------------ elementwise
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H,V,N", [(24, 37, 5), (2048, 1000, 33), (1000, 129, 7)])
+def test_embed(dtype, H, V, N):
+    table = rnd(V, H, dtype=dtype)
+    tokens = torch.randint(0, V, (N,), dtype=torch.int32, device=DEV)
+    tokens[0], tokens[-1] = V - 1, 0
+    out = torch.empty(N, H, dtype=torch.float32, device=DEV)
+    ops.embed(tokens, table, out)
+    assert torch.equal(out, table[tokens.long()].float())
+
+
+def ref_rmsnorm(x, w, eps):
+    return w * x * torch.rsqrt((x.double() ** 2).mean(-1, keepdim=True) + eps).float()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H,N,eps", [(24, 3, 1e-5), (2048, 19, 1e-6), (1000, 4, 1e-3), (13000, 2, 1e-5)])
+def test_add_rmsnorm(dtype, H, N, eps):
+    res = rnd(N, H, scale=3.0, seed=1)
+    pend = rnd(N, H, dtype=dtype, seed=2)
+    w = 1 + 0.1 * rnd(H, seed=3)
+    # with a pending update: the sum lands in the residual
+    r1 = res.clone()
+    out = torch.empty(N, H, dtype=dtype, device=DEV)
+    ops.add_rmsnorm(r1, pend, w, eps, out)
+    summed = res + pend.float()
+    torch.testing.assert_close(r1, summed, rtol=0, atol=0)
+    torch.testing.assert_close(out.float(), ref_rmsnorm(summed, w, eps).to(dtype).float(), **tol(dtype))
+    # without one: the residual is untouched
+    r2 = res.clone()
+    ops.add_rmsnorm(r2, None, w, eps, out)
+    assert torch.equal(r2, res)
+    torch.testing.assert_close(out.float(), ref_rmsnorm(res, w, eps).to(dtype).float(), **tol(dtype))
+    # selected rows: nothing is written back, rows may repeat
+    rows = torch.tensor([N - 1, 0, N - 1], dtype=torch.int32, device=DEV)
+    r3 = res.clone()
+    out3 = torch.empty(3, H, dtype=dtype, device=DEV)
+    ops.add_rmsnorm(r3, pend, w, eps, out3, rows)
+    assert torch.equal(r3, res)
+    torch.testing.assert_close(out3.float(), ref_rmsnorm(summed[rows.long()], w, eps).to(dtype).float(),
+                               **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("M,I", [(1, 8), (7, 264), (130, 1000)])
+def test_swiglu(dtype, M, I):
+    gu = rnd(M, 2 * I, dtype=dtype, scale=3.0)
+    out = torch.empty(M, I, dtype=dtype, device=DEV)
+    ops.swiglu(gu, out)
+    g, u = gu[:, :I].float(), gu[:, I:].float()
+    want = (g / (1 + torch.exp(-g)) * u).to(dtype).float()
+    torch.testing.assert_close(out.float(), want, **tol(dtype))
+
+
+def test_rope_table_is_float64_accurate():
+    half = 24
+    inv = torch.tensor([1.0 / math.pow(500000.0, 2 * i / (2 * half)) for i in range(half)],
+                       dtype=torch.float64, device=DEV)
+    pos = torch.tensor([0, 1, 63, 64, 8191, 131071, 1 << 24], dtype=torch.int32, device=DEV)
+    out = torch.empty(pos.numel(), half, 2, dtype=torch.float32, device=DEV)
+    ops.rope_table(pos, inv, out)
+    ang = pos.double().cpu()[:, None] * inv.cpu()[None, :]
+    want = torch.stack([torch.cos(ang), torch.sin(ang)], dim=-1).float()
+    # float rounding of a correctly computed value only: an angle formed in float32
+    # would be off by up to 1e-3 at these positions
+    torch.testing.assert_close(out.cpu(), want, rtol=0, atol=2e-7)
+
+
+def make_cache(n_kv, hd, dtype, n_pages=40, n_entries=2, window=None):
+    """A cache with one group whose pages are handed out in a scrambled order, so
+    that a kernel that ignored the block table would read the wrong memory."""
+    cache = Cache([[KVRequest(n_kv, hd, window)] for _ in range(n_entries)], [None] * n_entries,
+                  max_tokens=n_pages * 64, max_slots=8, dtype=dtype, device=DEV)
+    pool = cache.groups[0].pool
+    rng = np.random.default_rng(5)
+    pool._free = [int(p) for p in rng.permutation(n_pages)]
+    return cache
+
+
+def fill_sequence(cache, entry, slot, k, v):
+    """Write k, v [T, n_kv, hd] as the first T tokens of `slot` (test-side scatter)."""
+    T = k.shape[0]
+    cache.reserve(slot, T)
+    cache.flush_tables()
+    view = cache.handles[entry].kv
+    t = torch.arange(T)
+    pages = cache.groups[0].table_host[slot][t // 64].long().to(DEV)
+    view.k[pages, :, (t % 64).to(DEV), :] = k
+    view.v[pages, :, (t % 64).to(DEV), :] = v
+    cache._length[slot] = T
+
+
+def read_sequence(cache, entry, slot, T):
+    view = cache.handles[entry].kv
+    t = torch.arange(T)
+    pages = cache.groups[0].table_host[slot][t // 64].long().to(DEV)
+    k = view.k[pages, :, (t % 64).to(DEV), :]
+    v = view.v[pages, :, (t % 64).to(DEV), :]
+    return k, v
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("n_heads,n_kv,hd", [(4, 2, 16), (3, 1, 48), (8, 8, 64), (5, 5, 112)])
+def test_rope_kv_store(dtype, n_heads, n_kv, hd):
+    cache = make_cache(n_kv, hd, dtype)
+    slots = [cache.open_sequence() for _ in range(3)]
+    starts, lens = [0, 61, 130], [5, 9, 3]       # runs that cross page borders
+    for s, st in zip(slots, starts):
+        cache.reserve(s, st + 70)
+        cache._length[s] = st
+    cache.flush_tables()
+    N = sum(lens)
+    width = (n_heads + 2 * n_kv) * hd + 8          # a row stride wider than the data
+    buf = rnd(N, width, dtype=dtype, seed=7)
+    qkv = buf[:, : (n_heads + 2 * n_kv) * hd]
+    before = qkv.clone()
+    positions = torch.tensor([st + j for st, n in zip(starts, lens) for j in range(n)], dtype=torch.int32, device=DEV)
+    token_seq = torch.tensor([b for b, n in enumerate(lens) for _ in range(n)], dtype=torch.int32, device=DEV)
+    slot_t = torch.tensor(slots, dtype=torch.int32, device=DEV)
+    half = hd // 2
+    inv = torch.tensor([1.0 / math.pow(10000.0, 2 * i / hd) for i in range(half)], dtype=torch.float64, device=DEV)
+    cs = torch.empty(N, half, 2, dtype=torch.float32, device=DEV)
+    ops.rope_table(positions, inv, cs)
+    ops.rope_kv_store(qkv, cs, n_heads, n_kv, hd, cache.handles[1].kv, token_seq, slot_t, positions)
+
+    def rot(x, nh):
+        x = x.float().reshape(N, nh, hd)
+        a, b = x[..., :half], x[..., half:]
+        c, s = cs[:, None, :, 0], cs[:, None, :, 1]
+        return torch.cat([a * c - b * s, a * s + b * c], dim=-1).to(dtype)
+    want_q = rot(before[:, : n_heads * hd], n_heads).reshape(N, -1)
+    want_k = rot(before[:, n_heads * hd: (n_heads + n_kv) * hd], n_kv)
+    want_v = before[:, (n_heads + n_kv) * hd:].reshape(N, n_kv, hd)
+    torch.testing.assert_close(qkv[:, : n_heads * hd].float(), want_q.float(), **tol(dtype))
+    assert torch.equal(qkv[:, n_heads * hd:], before[:, n_heads * hd:])      # k, v columns untouched
+    assert torch.equal(buf[:, -8:], rnd(N, width, dtype=dtype, seed=7)[:, -8:])
+    o = 0
+    for s, st, n in zip(slots, starts, lens):
+        k, v = read_sequence(cache, 1, s, st + n)
+        torch.testing.assert_close(k[st:].float(), want_k[o:o + n].float(), **tol(dtype))
+        assert torch.equal(v[st:], want_v[o:o + n])
+        assert float(k[:st].abs().sum()) == 0.0            # nothing written before the run
+        o += n
+    assert float(cache.handles[0].kv.k.abs().sum()) == 0.0  # the other entry is untouched
+
+
+# -------------------------------------------------------------- matrix products
+@pytest.mark.parametrize("M,N,K", [(1, 17, 8), (5, 96, 264), (64, 391, 96), (130, 130, 40),
+                                   (257, 1000, 2048), (3, 2048, 8192)])
+def test_linear_float32(M, N, K):
+    x, w = rnd(M, K, seed=1), rnd(N, K, seed=2)
+    out = torch.empty(M, N, dtype=torch.float32, device=DEV)
+    ops.linear(x, w, out)
+    want = (x.double() @ w.double().T).float()
+    torch.testing.assert_close(out, want, rtol=1e-5, atol=1e-4 * math.sqrt(K / 64))
+
+
+def test_linear_float32_does_not_depend_on_the_batch():
+    """A row's result is bitwise the same alone, in a small batch, in a large one."""
+    K, N = 264, 391
+    x, w = rnd(200, K, seed=1), rnd(N, K, seed=2)
+    full = torch.empty(200, N, dtype=torch.float32, device=DEV)
+    ops.linear(x, w, full)
+    for rows in ([0], [63, 64], list(range(100, 177))):
+        sub = x[rows].contiguous()
+        out = torch.empty(len(rows), N, dtype=torch.float32, device=DEV)
+        ops.linear(sub, w, out)
+        assert torch.equal(out, full[rows])
+
+
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("M,N,K", [(1, 17, 8), (5, 96, 264), (64, 391, 96), (130, 130, 40),
+                                   (257, 1000, 2048), (3, 2048, 8192), (8, 6144, 2048),
+                                   (300, 144, 96)])
+def test_linear_bfloat16(out_dtype, M, N, K):
+    x, w = rnd(M, K, dtype=torch.bfloat16, seed=1), rnd(N, K, dtype=torch.bfloat16, seed=2)
+    out = torch.empty(M, N, dtype=out_dtype, device=DEV)
+    ops.linear(x, w, out)
+    want = (x.double() @ w.double().T).float()
+    if out_dtype == torch.bfloat16:
+        torch.testing.assert_close(out.float(), want.to(torch.bfloat16).float(), rtol=1.6e-2, atol=1e-2 * math.sqrt(K / 64))
+    else:
+        torch.testing.assert_close(out, want, rtol=1e-4, atol=2e-3 * math.sqrt(K / 64))
+
+
+def test_linear_strided_operands():
+    """Inputs and outputs that are column slices of wider buffers."""
+    xb, w = rnd(9, 300, dtype=torch.bfloat16), rnd(50, 96, dtype=torch.bfloat16, seed=3)
+    x = xb[:, 8:104]
+    outb = torch.zeros(9, 80, dtype=torch.bfloat16, device=DEV)
+    ops.linear(x, w, outb[:, 10:60])
+    want = (x.double() @ w.double().T).float().to(torch.bfloat16).float()
+    torch.testing.assert_close(outb[:, 10:60].float(), want, rtol=1.6e-2, atol=1e-2)
+    assert float(outb[:, :10].abs().sum()) == 0 and float(outb[:, 60:].abs().sum()) == 0
+
+
+def test_linear_refuses_unaligned_inner_size():
+    x, w = rnd(4, 12, dtype=torch.bfloat16), rnd(5, 12, dtype=torch.bfloat16)
+    with pytest.raises(ops.KernelError, match="multiples of 8"):
+        ops.linear(x, w, torch.empty(4, 5, dtype=torch.bfloat16, device=DEV))
+
+
+# ------------------------------------------------------------------- attention
+def ref_attention(q, k, v, n_heads, n_kv, hd, pos_q, scale, window):
+    """q [n, n_heads*hd] at positions pos_q over keys k, v [T, n_kv, hd] (float64)."""
+    g = n_heads // n_kv
+    kv_of_head = torch.arange(n_heads, device=q.device) // g
+    out = torch.zeros(q.shape[0], n_heads, hd, dtype=torch.float64, device=q.device)
+    qh = q.double().view(-1, n_heads, hd)
+    for i, p in enumerate(pos_q):
+        lo = max(0, p - window + 1) if window else 0
+        kk = k[lo:p + 1].double()[:, kv_of_head]          # [keys, heads, hd]
+        vv = v[lo:p + 1].double()[:, kv_of_head]
+        w = torch.softmax(torch.einsum("thd,hd->ht", kk, qh[i]) * scale, dim=1)
+        out[i] = torch.einsum("ht,thd->hd", w, vv)
+    return out.view(q.shape[0], -1).float()
+
+
+ATT_SHAPES = [(4, 2, 16), (3, 1, 48), (8, 8, 64), (6, 2, 128), (2, 1, 80), (20, 1, 32)]
+
+
+def attention_case(dtype, n_heads, n_kv, hd, lens_before, lens_new, window, seed=0):
+    """Sequences with `lens_before` tokens in the cache get `lens_new` more; returns
+    what the kernels need and the reference output for the new tokens.  One far
+    key of each sequence is made to dominate some queries."""
+    cache = make_cache(n_kv, hd, dtype, n_pages=64)
+    B = len(lens_before)
+    slots = [cache.open_sequence() for _ in range(B)]
+    if B > 1:                      # slots out of order
+        slots = slots[::-1]
+    scale = 1.0 / math.sqrt(hd)
+    qs, wants, pos_all, tok_seq = [], [], [], []
+    for b, (t0, n) in enumerate(zip(lens_before, lens_new)):
+        T = t0 + n
+        k = rnd(T, n_kv, hd, dtype=dtype, seed=seed + 10 * b + 1)
+        v = rnd(T, n_kv, hd, dtype=dtype, seed=seed + 10 * b + 2)
+        q = rnd(n, n_heads * hd, dtype=dtype, seed=seed + 10 * b + 3)
+        far = min(3, T - 1)        # a key far from the end ...
+        k[far] *= 4.0
+        q[-1] = (k[far].float().repeat_interleave(n_heads // n_kv, dim=0).view(-1) * 1.5).to(dtype)
+        fill_sequence(cache, 0, slots[b], k, v)
+        pos = list(range(t0, T))
+        wants.append(ref_attention(q, k, v, n_heads, n_kv, hd, pos, scale, window))
+        qs.append(q)
+        pos_all += pos
+        tok_seq += [b] * n
+    q = torch.cat(qs)
+    want = torch.cat(wants)
+    meta = dict(
+        positions=torch.tensor(pos_all, dtype=torch.int32, device=DEV),
+        token_seq=torch.tensor(tok_seq, dtype=torch.int32, device=DEV),
+        slots=torch.tensor(slots, dtype=torch.int32, device=DEV),
+        cu=torch.tensor(np.concatenate([[0], np.cumsum(lens_new)]), dtype=torch.int32, device=DEV),
+        start=torch.tensor(lens_before, dtype=torch.int32, device=DEV),
+    )
+    return cache, q, want, meta, scale
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("n_heads,n_kv,hd", ATT_SHAPES + [(2, 2, 256)])
+@pytest.mark.parametrize("window", [0, 37])
+def test_attention_simple(dtype, n_heads, n_kv, hd, window):
+    cache, q, want, m, scale = attention_case(dtype, n_heads, n_kv, hd, [0, 130, 63], [70, 1, 5], window)
+    out = torch.empty_like(q)
+    ops.attention_simple(q, out, cache.handles[0].kv, m["token_seq"], m["slots"], m["positions"],
+                         n_heads, scale, window)
+    torch.testing.assert_close(out.float(), want, **(dict(rtol=1e-4, atol=1e-5) if dtype == torch.float32
+                                                     else dict(rtol=2e-2, atol=2e-2)))
+
+
+@pytest.mark.parametrize("n_heads,n_kv,hd", ATT_SHAPES)
+@pytest.mark.parametrize("window", [0, 37, 64])
+@pytest.mark.parametrize("lens_before,lens_new", [([0], [1]), ([0, 0, 0], [5, 129, 64]),
+                                                  ([10, 64, 100], [70, 1, 200]), ([0], [300])])
+def test_attention_prefill_bf16(n_heads, n_kv, hd, window, lens_before, lens_new):
+    cache, q, want, m, scale = attention_case(torch.bfloat16, n_heads, n_kv, hd, lens_before, lens_new, window)
+    qbuf = torch.zeros(q.shape[0], q.shape[1] + 16, dtype=torch.bfloat16, device=DEV)   # strided q
+    qbuf[:, : q.shape[1]] = q
+    out = torch.full_like(q, float("nan"))
+    ops.attention_prefill_bf16(qbuf[:, : q.shape[1]], out, cache.handles[0].kv, m["cu"], m["slots"],
+                               m["start"], len(lens_new), max(lens_new), n_heads, scale, window)
+    torch.testing.assert_close(out.float(), want, rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("n_heads,n_kv,hd", ATT_SHAPES)
+@pytest.mark.parametrize("window", [0, 37])
+@pytest.mark.parametrize("splits", [1, 2, 5])
+def test_attention_decode_bf16(n_heads, n_kv, hd, window, splits):
+    lens_before = [0, 63, 64, 700, 129]
+    cache, q, want, m, scale = attention_case(torch.bfloat16, n_heads, n_kv, hd, lens_before,
+                                              [1] * len(lens_before), window)
+    out = torch.full_like(q, float("nan"))
+    scratch = None
+    if splits > 1:
+        n = ops.attention_decode_scratch_floats(len(lens_before), n_heads, hd, splits)
+        scratch = torch.full((n,), float("nan"), dtype=torch.float32, device=DEV)
+    ops.attention_decode_bf16(q, out, cache.handles[0].kv, m["slots"], m["positions"], n_heads, scale,
+                              window, splits, scratch)
+    torch.testing.assert_close(out.float(), want, rtol=2e-2, atol=2e-2)
+
+
+def test_attention_refuses_head_sizes_it_cannot_serve():
+    assert not ops.attention_bf16_supports(40)
+    assert not ops.attention_bf16_supports(144)
+    assert ops.attention_bf16_supports(112)
+
+
+# -------------------------------------------------------------------- sampling
+@pytest.mark.parametrize("R,V", [(1, 5), (7, 391), (3, 49152), (2, 128257)])
+def test_argmax_first_maximum(R, V):
+    logits = rnd(R, V, seed=4)
+    logits[0, V - 1] = 50.0
+    if R > 1:
+        logits[1, 3] = 60.0
+        logits[1, V // 2] = 60.0          # a tie: the lower index wins
+    out = torch.zeros(R, dtype=torch.int32, device=DEV)
+    ops.argmax(logits, out)
+    want = [int(np.argmax(row)) for row in logits.cpu().numpy()]   # numpy: first maximum
+    assert out.tolist() == want
+    if R > 1:
+        assert out[1].item() == 3
+
+
+def test_sample_temperature_matches_inverse_cdf():
+    import plain_llama
+    R, V, T, seed = 64, 391, 0.8, 7
+    logits = rnd(R, V, scale=2.0, seed=9)
+    seq = torch.arange(R, dtype=torch.int32, device=DEV) % 5
+    steps = torch.arange(R, dtype=torch.int32, device=DEV) // 5
+    out = torch.zeros(R, dtype=torch.int32, device=DEV)
+    ops.sample_temperature(logits, T, seed, seq, steps, out)
+    lg = logits.cpu().numpy()
+    for r in range(R):
+        u = plain_llama.uniform(seed, int(seq[r]), int(steps[r]))
+        cdf = np.cumsum(plain_llama.temperature_probs(lg[r], T))
+        t = int(out[r])
+        below = cdf[t - 1] if t > 0 else 0.0
+        assert below - 1e-5 <= u <= cdf[t] + 1e-5, (r, t, u, below, cdf[t])
+    # the same (seed, sequence, step) gives the same token whatever else is in the batch
+    out2 = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops.sample_temperature(logits[17:18], T, seed, seq[17:18].contiguous(), steps[17:18].contiguous(), out2)
+    assert out2.item() == out[17].item()
+
+
+def test_sample_temperature_follows_the_distribution():
+    V, T = 50, 1.3
+    logits = rnd(1, V, scale=1.5, seed=11).repeat(4000, 1).contiguous()
+    seq = torch.zeros(4000, dtype=torch.int32, device=DEV)
+    steps = torch.arange(4000, dtype=torch.int32, device=DEV)
+    out = torch.zeros(4000, dtype=torch.int32, device=DEV)
+    ops.sample_temperature(logits, T, 123, seq, steps, out)
+    p = torch.softmax(logits[0].double() / T, 0).cpu().numpy()
+    freq = np.bincount(out.cpu().numpy(), minlength=V) / 4000.0
+    assert np.abs(freq - p).max() < 4 * np.sqrt(p.max() / 4000.0) + 1e-3
