@@ -1,0 +1,273 @@
+#!/usr/bin/env python3
+"""Measurement of the library's headline metric on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl own|reference]
+
+A "step" is one decode step of the batch.  The default run has the layer sizes
+of SmolLM2-1.7B (random weights, bfloat16), a batch of 8 and sequences that end
+at a context of 8192 tokens.  It prints ONE JSON line:
+
+  value      decoded tokens a second, device time of K replayed decode steps
+             (the sampled tokens feed the next step on the device)
+  e2e        the same through the public entry point DecodeBatch.step_host:
+             every step uploads the tokens it feeds from pinned host memory and
+             downloads the tokens it sampled
+  prefill    one prompt of 2,048 tokens through step(): tokens a second, and the
+             step's flops / time / the bfloat16 matrix peak
+  roofline   the decode step against HBM: bytes it has to read (every weight
+             once, the cache of the live sequences) / its time / the copy peak
+  points     decode tokens a second at batch 1 and 64 (same context)
+
+Peaks come from MEASURED_PEAKS.json beside this file if present, else from the
+fallback figures of an earlier measurement on the same pool.  Inputs are larger
+than L2 (3.4 GB of weights and 1.6 GB of cache per sequence against 126 MB), so
+no flush is needed between steps.  For --gpus N > 1 it prints a line that says
+so and exits with 2: this library runs on one GPU.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+SMOLLM2_1P7B = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "num_hidden_layers": 24, "hidden_size": 2048, "num_attention_heads": 32,
+    "num_key_value_heads": 32, "head_dim": 64, "intermediate_size": 8192, "vocab_size": 49152,
+    "rope_theta": 130000.0, "rope_scaling": None, "rms_norm_eps": 1e-5,
+    "tie_word_embeddings": True, "max_position_embeddings": 8192,
+}
+FULL_LAYERS = SMOLLM2_1P7B["num_hidden_layers"]
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            with open(path) as f:
+                raw = json.load(f)
+            return {"hbm_gbs": float(raw["hbm_gbs"]), "bf16_tflops": float(raw["bf16_tflops"]),
+                    "source": "measured"}
+        except (OSError, ValueError, KeyError):
+            pass
+    return dict(FALLBACK_PEAKS)
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons, sampled while the timed region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+    NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+
+    def __init__(self):
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        for line in out.splitlines():
+            cells = [c.strip() for c in line.split(",")]
+            if len(cells) < 6:
+                continue
+            try:
+                sm.append(float(cells[0])); mx.append(float(cells[1]))
+            except ValueError:
+                continue
+            for name, cell in zip(self.NAMES, cells[2:6]):
+                if cell.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def decode_bytes(cfg, n_layers, batch, context):
+    """Bytes a decode step has to read: every weight it uses once (bfloat16) and
+    the keys and values of the live sequences."""
+    H, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    q = cfg["num_attention_heads"] * cfg["head_dim"]
+    kv = cfg["num_key_value_heads"] * cfg["head_dim"]
+    per_layer = (q + 2 * kv) * H + H * q + 3 * H * I + 2 * H
+    weights = 2 * (n_layers * per_layer + V * H + H)
+    cache = batch * context * n_layers * 2 * kv * 2
+    return weights + cache, weights, cache
+
+
+def prefill_flops(cfg, n_layers, T):
+    H, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    nh, hd = cfg["num_attention_heads"], cfg["head_dim"]
+    q, kv = nh * hd, cfg["num_key_value_heads"] * hd
+    gemm = 2 * T * ((q + 2 * kv) * H + H * q + 3 * H * I)
+    attn = 2 * T * T * hd * nh          # causal: half of QK^T and half of PV
+    return n_layers * (gemm + attn) + 2 * V * H
+
+
+def run_own(args):
+    import torch
+    import go_tinygrad_b200 as lib
+    from go_tinygrad_b200.engine import StepEntry, step
+    from go_tinygrad_b200.engine.decode import DecodeBatch
+    from go_tinygrad_b200.kernels import ops
+
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    cfg = dict(SMOLLM2_1P7B, num_hidden_layers=args.layers)
+    pk = peaks()
+    model = lib.Model.random(cfg, seed=0, dtype="bfloat16", device=dev, std=0.02)
+    context, vocab = args.context, cfg["vocab_size"]
+    biggest = max([args.batch] + ([1, 64] if args.points else []))
+    cache = model.new_cache(max_tokens=biggest * context + 64 * 40, max_slots=biggest + 1)
+    for grp in cache.groups:                       # synthetic keys and values of unit scale
+        grp.storage.normal_(0.0, 1.0)
+    gen = torch.Generator().manual_seed(0)
+
+    def decode_run(batch, steps, warmup, host):
+        """Tokens a second of `steps` decode steps that end at `context` tokens."""
+        slots = [cache.open_sequence() for _ in range(batch)]
+        total = warmup + steps
+        for s in slots:
+            cache.reserve(s, context)
+            cache.advance(s, context - total)
+        cache.flush_tables()
+        db = DecodeBatch(model, cache, slots, list(range(batch)), lib.Sampler(0.0, 0))
+        tokens = torch.randint(0, vocab, (batch,), generator=gen).tolist()
+        sampler = ClockSampler()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        launches_before = ops.launch_count()
+        if host:
+            out = db.step_host(tokens, [0] * batch)      # eager: loads and configures kernels
+            per_step = ops.launch_count() - launches_before
+            for i in range(1, warmup):
+                out = db.step_host(out, [i] * batch)
+            torch.cuda.synchronize()
+            sampler.start()
+            start.record()
+            for i in range(steps):
+                out = db.step_host(out, [warmup + i] * batch)
+            stop.record()
+        else:
+            db.set_state(tokens, [0] * batch)
+            db._launch()                                 # eager: loads and configures kernels
+            per_step = ops.launch_count() - launches_before
+            for _ in range(warmup - 1):
+                db.step_device()
+            torch.cuda.synchronize()
+            sampler.start()
+            start.record()
+            for _ in range(steps):
+                db.step_device()
+            stop.record()
+        torch.cuda.synchronize()
+        clocks = sampler.stop()
+        ms = start.elapsed_time(stop) / steps
+        for s in slots:
+            cache.close_sequence(s)
+        return batch / (ms * 1e-3), ms, clocks, per_step + 1      # +1: the kernel that feeds tokens back
+
+    value, ms, clocks, launches = decode_run(args.batch, args.steps, args.warmup, host=False)
+    e2e_value, e2e_ms, _, _ = decode_run(args.batch, args.steps, args.warmup, host=True)
+    points = {}
+    if args.points:
+        for b in (1, 64):
+            points[f"decode_b{b}"] = round(decode_run(b, max(3, args.steps // 2), args.warmup, host=False)[0], 1)
+
+    # prefill of one 2,048-token prompt through the step function
+    T = 2048
+    prompt = torch.randint(0, vocab, (T,), generator=gen).tolist()
+    times = []
+    for i in range(3 + 3):
+        slot = cache.open_sequence()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        step(model, cache, [StepEntry(slot, prompt, [T - 1])])
+        b.record()
+        torch.cuda.synchronize()
+        if i >= 3:
+            times.append(a.elapsed_time(b))
+        cache.close_sequence(slot)
+    pre_ms = statistics.median(times)
+    flops = prefill_flops(cfg, args.layers, T)
+
+    total_bytes, w_bytes, kv_bytes = decode_bytes(cfg, args.layers, args.batch, context)
+    achieved = total_bytes / (ms * 1e-3) / 1e9
+    line = {
+        "metric": "decode tok/s at batch 8, context 8192 (SmolLM2-1.7B shape)",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {
+            "model": "SmolLM2-1.7B shape, random weights", "layers": args.layers,
+            "layers_of_model": FULL_LAYERS, "hidden": cfg["hidden_size"],
+            "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
+            "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"],
+            "vocab": cfg["vocab_size"], "rope_theta": cfg["rope_theta"], "tied_head": True,
+            "global_batch": args.batch, "seq_len": context, "context": context,
+            "prefill_tokens": T, "parallelism": "single GPU", "l2": "inputs larger than L2",
+            "peaks": pk["source"], "graph": "decode step replayed as a CUDA graph",
+        },
+        "clocks": clocks,
+        "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),
+                "h2d_bytes_per_step": 3 * 4 * args.batch, "d2h_bytes_per_step": 4 * args.batch},
+        "gpu_launches": launches * args.steps,
+        "prefill": {"value": round(T / (pre_ms * 1e-3), 1), "tokens": T, "ms": round(pre_ms, 3),
+                    "frac": round(flops / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"],
+                     "unit": "GB/s", "frac": round(achieved / pk["hbm_gbs"], 4),
+                     "weight_gb": round(w_bytes / 1e9, 3), "cache_gb": round(kv_bytes / 1e9, 3)},
+        "points": points,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="own", choices=["own", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=SMOLLM2_1P7B["max_position_embeddings"])
+    ap.add_argument("--layers", type=int, default=FULL_LAYERS,
+                    help="fewer layers than the model has, where memory or time needs it")
+    ap.add_argument("--no-points", dest="points", action="store_false",
+                    help="skip the batch-1 and batch-64 decode points")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "the reference is a Go program (go.mod, purego); no Go toolchain is installed "
+                          "and pip cannot build it, so it cannot be run here"}))
+        return 0
+    if args.gpus != 1:
+        print(json.dumps({"error": f"--gpus {args.gpus}: this library runs on one GPU; "
+                                   f"there is no multi-GPU path to measure", "n_gpus": args.gpus}))
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+    return run_own(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

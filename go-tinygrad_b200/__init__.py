@@ -8,7 +8,10 @@ module of that name beside it loads this package).
 from . import config, weights, cache, parts, models  # noqa: F401  (models registers architectures)
 from .config import ConfigError, LlamaConfig, read_model_config, registered_architectures
 from .engine import Model, StepEntry, StepError, step
+from .engine.generate import GenerationResult, generate
+from .sampling import Sampler
 from .weights import WeightError, write_random_model
 
 __all__ = ["ConfigError", "LlamaConfig", "read_model_config", "registered_architectures", "Model",
-           "StepEntry", "StepError", "step", "WeightError", "write_random_model"]
+           "StepEntry", "StepError", "step", "WeightError", "write_random_model", "GenerationResult",
+           "generate", "Sampler"]

@@ -212,14 +212,16 @@ GTG_API int gtg_rope_kv_store(int dtype, void* qkv, int ld, const float* cos_sin
 
 // --------------------------------------------------- advance a decode batch
 // Between two decode steps that never leave the device: the sampled token
-// becomes the next input and every position moves on by one.
-__global__ void advance_kernel(int* tokens, int* positions, const int* sampled, int B) {
+// becomes the next input, every position moves on by one and so does every
+// sequence's count of generated tokens (which keys its next random draw).
+__global__ void advance_kernel(int* tokens, int* positions, int* steps, const int* sampled, int B) {
     const int b = blockIdx.x * blockDim.x + threadIdx.x;
-    if (b < B) { tokens[b] = sampled[b]; positions[b] += 1; }
+    if (b < B) { tokens[b] = sampled[b]; positions[b] += 1; steps[b] += 1; }
 }
 
-GTG_API int gtg_advance(int* tokens, int* positions, const int* sampled, int B, cudaStream_t stream) {
+GTG_API int gtg_advance(int* tokens, int* positions, int* steps, const int* sampled, int B,
+                        cudaStream_t stream) {
     if (B <= 0) return 0;
-    advance_kernel<<<(B + 127) / 128, 128, 0, stream>>>(tokens, positions, sampled, B);
+    advance_kernel<<<(B + 127) / 128, 128, 0, stream>>>(tokens, positions, steps, sampled, B);
     return launch_status();
 }

@@ -1,0 +1,118 @@
+"""A fixed set of sequences decoding together: one token each per step, with
+the step captured once as a CUDA graph and replayed.
+
+The decode step of a batch is launch-bound (a few hundred small kernels), so it
+is recorded once -- embedding, every layer from the cache, final norm, head and
+the choice of the next token -- and replayed from buffers at fixed addresses:
+tokens, positions, the count of tokens each sequence has generated (it keys the
+random draw) and the sampled tokens.  Two ways to drive it:
+
+  * `step_host(tokens)`: the host uploads the tokens to feed, runs the step and
+    downloads the sampled tokens (what the generation loop does);
+  * `step_device()`: the sampled tokens become the next input on the device and
+    nothing crosses the bus (a kernel moves them; for timing the step itself).
+
+The first run of a batch executes eagerly (it loads and configures kernels,
+which a capture must not do), the second is captured.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence
+
+import torch
+
+from ..cache import Cache
+from ..kernels import ops
+from ..parts.base import StepContext
+from ..sampling import Sampler
+from .model import Model
+from .step import logits_at, run_layers
+
+
+class DecodeBatch:
+    def __init__(self, model: Model, cache: Cache, slots: Sequence[int], requests: Sequence[int],
+                 sampler: Sampler, use_graph: bool = True):
+        self.model, self.cache, self.sampler = model, cache, sampler
+        self.slots = list(slots)
+        B = self.B = len(self.slots)
+        dev = model.rt.device
+        # one device buffer, views at fixed addresses
+        #   tokens | positions | steps | token_seq | cu_seqlens | slots | requests | rows
+        self.meta = torch.zeros(8 * B + 1, dtype=torch.int32, device=dev)
+        cut = lambda a, n: self.meta[a:a + n]
+        self.tokens, self.positions, self.steps = cut(0, B), cut(B, B), cut(2 * B, B)
+        self.token_seq, self.cu = cut(3 * B, B), cut(4 * B, B + 1)
+        self.slot_ids, self.requests, self.rows = cut(5 * B + 1, B), cut(6 * B + 1, B), cut(7 * B + 1, B)
+        ar = torch.arange(B + 1, dtype=torch.int32)
+        fixed = torch.cat([ar[:B], ar, torch.tensor(self.slots, dtype=torch.int32),
+                           torch.tensor(list(requests), dtype=torch.int32), ar[:B]])
+        self.meta[3 * B:].copy_(fixed.to(dev))
+        self.sampled = torch.zeros(B, dtype=torch.int32, device=dev)
+        pin = dev.type == "cuda"
+        self.h_in = torch.zeros(3 * B, dtype=torch.int32, pin_memory=pin)
+        self.h_out = torch.zeros(B, dtype=torch.int32, pin_memory=pin)
+        self.logits: Optional[torch.Tensor] = None
+        self.use_graph = use_graph and dev.type == "cuda"
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self._runs = 0
+
+    # ------------------------------------------------------------------ state
+    def set_state(self, tokens: Sequence[int], steps: Sequence[int]) -> None:
+        """Tokens to feed next and how many tokens each sequence has generated;
+        positions are the sequences' lengths in the cache."""
+        B = self.B
+        self.h_in[:B] = torch.tensor(list(tokens), dtype=torch.int32)
+        self.h_in[B:2 * B] = torch.tensor([self.cache.length(s) for s in self.slots], dtype=torch.int32)
+        self.h_in[2 * B:] = torch.tensor(list(steps), dtype=torch.int32)
+        self.meta[:3 * B].copy_(self.h_in, non_blocking=True)
+
+    def _context(self) -> StepContext:
+        return StepContext(rt=self.model.rt, n_tokens=self.B, n_seqs=self.B, tokens=self.tokens,
+                           positions=self.positions, token_seq=self.token_seq, cu_seqlens=self.cu,
+                           slots=self.slot_ids, start_pos=self.positions, max_q_len=1,
+                           max_kv_len=0, is_decode=True)
+
+    def _forward(self) -> None:
+        ctx = self._context()
+        stream = run_layers(self.model, self.cache, ctx)
+        self.logits = logits_at(self.model, stream, ctx, self.rows)
+        self.sampler.pick(self.logits, self.requests, self.steps, out=self.sampled)
+
+    def _launch(self) -> None:
+        """Run the step for the state now on the device; grows every sequence by one."""
+        self.cache.reserve_many([(s, self.cache.length(s) + 1) for s in self.slots])
+        self.cache.flush_tables()
+        if not self.use_graph:
+            self._forward()
+        elif self.graph is not None:
+            self.graph.replay()
+        elif self._runs == 0:
+            self._forward()
+        else:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                self._forward()
+            self.graph = graph
+            graph.replay()
+        self._runs += 1
+        for s in self.slots:
+            self.cache.advance(s, 1)
+
+    # ------------------------------------------------------------------ driving
+    def step_host(self, tokens: Sequence[int], steps: Sequence[int]) -> List[int]:
+        self.set_state(tokens, steps)
+        self._launch()
+        self.h_out.copy_(self.sampled, non_blocking=True)
+        torch.cuda.current_stream().synchronize() if self.model.rt.device.type == "cuda" else None
+        return self.h_out.tolist()
+
+    def step_device(self) -> None:
+        """Feed back the tokens just sampled; no host synchronisation."""
+        ops.advance(self.tokens, self.positions, self.steps, self.sampled)
+        self._launch()
+
+    def reserve_ahead(self, n_steps: int) -> None:
+        """Take the pages `n_steps` more steps will need now, so that the steps
+        themselves touch no block table."""
+        self.cache.reserve_many([(s, self.cache.length(s) + n_steps) for s in self.slots])
+        self.cache.flush_tables()

@@ -20,6 +20,7 @@ import torch
 
 from ..cache import Cache
 from ..sampling import Sampler
+from .decode import DecodeBatch
 from .model import Model
 from .schedule import SequenceProgress, live, plan_batches
 from .step import StepEntry, step
@@ -41,12 +42,14 @@ def _pick(sampler: Sampler, logits: torch.Tensor, seqs: Sequence[SequenceProgres
 def generate(model: Model, prompts: Sequence[Sequence[int]],
              max_new_tokens: Union[int, Sequence[int]] = 50, *, temperature: float = 0.0,
              seed: int = 0, stop: Optional[Sequence[int]] = None, cache: Optional[Cache] = None,
-             max_batch: Optional[int] = None, max_tokens: Optional[int] = None
-             ) -> List[GenerationResult]:
+             max_batch: Optional[int] = None, max_tokens: Optional[int] = None,
+             use_graph: bool = True) -> List[GenerationResult]:
     """Generate for every prompt (lists of token ids).  `stop` defaults to the
     model's own end tokens (config.json's eos_token_id).  With no `cache` one
     is made that holds `max_tokens` tokens (default: what the largest batch
-    needs, up to `max_batch` requests at a time, default 64)."""
+    needs, up to `max_batch` requests at a time, default 64).  Decode steps of a
+    batch whose membership does not change are replayed as a CUDA graph unless
+    `use_graph` is False."""
     n = len(prompts)
     limits = [int(max_new_tokens)] * n if isinstance(max_new_tokens, int) else [int(m) for m in max_new_tokens]
     if len(limits) != n:
@@ -79,6 +82,7 @@ def generate(model: Model, prompts: Sequence[Sequence[int]],
                 logits = step(model, cache, entries)
                 for s, tok in zip(running, _pick(sampler, logits, running)):
                     s.accept(tok)
+            decode, members = None, None
             while True:
                 for s in running:
                     if s.finished and s.request in slots:
@@ -86,9 +90,13 @@ def generate(model: Model, prompts: Sequence[Sequence[int]],
                 running = live(running)
                 if not running:
                     break
-                entries = [StepEntry(slots[s.request], [s.tokens[-1]], [0]) for s in running]
-                logits = step(model, cache, entries)
-                for s, tok in zip(running, _pick(sampler, logits, running)):
+                now = tuple(s.request for s in running)
+                if now != members:          # the batch shrank: a new fixed set of sequences
+                    decode = DecodeBatch(model, cache, [slots[r] for r in now], now, sampler,
+                                         use_graph=use_graph)
+                    members = now
+                picked = decode.step_host([s.tokens[-1] for s in running], [len(s.tokens) for s in running])
+                for s, tok in zip(running, picked):
                     s.accept(tok)
         finally:
             for slot in slots.values():

@@ -90,15 +90,16 @@ class Model:
     def random(cls, config_json: Any, seed: int = 0, dtype: Union[str, torch.dtype] = "bfloat16",
                device: Union[str, torch.device] = "cuda", std: Optional[float] = None,
                norm_std: float = 0.0) -> "Model":
-        """A model with random weights drawn in memory (the same values that
-        `write_random_model` writes to a folder for this configuration and seed)."""
+        """A model with random weights drawn on the device, without a folder
+        (for measurements at sizes one would not write to disk)."""
         if hasattr(config_json, "to_json"):
             config_json = config_json.to_json()
         arch = find_architecture(config_json)
         config = arch.read_config(config_json)
         dt = compute_dtype(dtype)
         model = cls(arch.plan(config), Runtime(torch.device(device), dt), config)
-        return model.load_tensors(random_tensors(model.weight_specs(), seed, std, norm_std, dt))
+        return model.load_tensors(random_tensors(model.weight_specs(), seed, std, norm_std, dt,
+                                                 device=str(model.rt.device)))
 
     # ------------------------------------------------------------------ cache
     def new_cache(self, max_tokens: int, max_slots: Optional[int] = None) -> Cache:
@@ -115,6 +116,11 @@ class Model:
                 shared.append(entry.cache)
         return Cache(requests, shared, max_tokens=max_tokens, max_slots=max_slots,
                      max_position=self.plan.max_position, dtype=self.rt.dtype, device=self.rt.device)
+
+    def generate(self, prompts, max_new_tokens=50, **options):
+        """Generate for a list of prompts (token ids); see engine/generate.py."""
+        from .generate import generate
+        return generate(self, prompts, max_new_tokens, **options)
 
     def weight_bytes(self) -> int:
         """Bytes of device memory the parts' weights hold (shared tables once)."""

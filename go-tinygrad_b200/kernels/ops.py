@@ -26,7 +26,7 @@ _SIGNATURES = {
     "gtg_swiglu": ("elementwise", [_I, _P, _P, _I, _I, _P]),
     "gtg_rope_table": ("elementwise", [_P, _P, _P, _I, _I, _P]),
     "gtg_rope_kv_store": ("elementwise", [_I, _P, _I, _P, _I, _I, _I, _P, _P, _L, _P, _I, _P, _P, _P, _I, _P]),
-    "gtg_advance": ("elementwise", [_P, _P, _P, _I, _P]),
+    "gtg_advance": ("elementwise", [_P, _P, _P, _P, _I, _P]),
     "gtg_gemm_f32": ("gemm_f32", [_P, _I, _P, _I, _P, _I, _I, _I, _I, _P]),
     "gtg_gemm_bf16_mma": ("gemm_bf16_mma", [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _P]),
     "gtg_attention_simple": ("attention_simple", [_I, _P, _I, _P, _I, _P, _P, _L, _P, _I, _P, _P, _P,
@@ -66,7 +66,18 @@ def _fn(symbol: str):
 _CODES = {-1: "bad argument", -2: "size not supported by this kernel"}
 
 
+_launches = 0
+
+
+def launch_count() -> int:
+    """How many kernel launchers of this library have been called so far (a
+    launcher that is recorded into a CUDA graph counts once, when recorded)."""
+    return _launches
+
+
 def _check(code: int, what: str) -> None:
+    global _launches
+    _launches += 1
     if code != 0:
         if code in _CODES:
             raise KernelError(f"{what}: {_CODES[code]}")
@@ -173,10 +184,13 @@ def rope_kv_store(qkv: torch.Tensor, cos_sin: Optional[torch.Tensor], n_heads: i
                                     N, _stream()), "rope_kv_store")
 
 
-def advance(tokens: torch.Tensor, positions: torch.Tensor, sampled: torch.Tensor) -> None:
-    """tokens <- sampled; positions += 1 (between decode steps that stay on the device)."""
+def advance(tokens: torch.Tensor, positions: torch.Tensor, steps: torch.Tensor,
+            sampled: torch.Tensor) -> None:
+    """tokens <- sampled; positions += 1; steps += 1 (between decode steps that stay on the device)."""
     B = tokens.numel()
-    _check(_fn("gtg_advance")(_ptr(tokens), _ptr(positions), _ptr(sampled), B, _stream()), "advance")
+    for name, t in (("tokens", tokens), ("positions", positions), ("steps", steps), ("sampled", sampled)):
+        _need(t.dtype == torch.int32 and t.is_contiguous() and t.numel() >= B, f"advance: {name} must be int32 [B]")
+    _check(_fn("gtg_advance")(_ptr(tokens), _ptr(positions), _ptr(steps), _ptr(sampled), B, _stream()), "advance")
 
 
 # ---------------------------------------------------------------- matrix products

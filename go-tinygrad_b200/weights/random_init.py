@@ -29,19 +29,18 @@ def _tensor_seed(seed: int, name: str) -> int:
 
 
 def random_tensors(specs, seed: int, std: Optional[float], norm_std: float,
-                   store_dtype: torch.dtype) -> Mapping[str, torch.Tensor]:
+                   store_dtype: torch.dtype, device: str = "cpu") -> Mapping[str, torch.Tensor]:
+    """Random values for every required spec.  Drawn on `device`: the host's and
+    a GPU's generators give different (equally valid) values for one seed."""
     out = {}
     for s in check_specs(specs):
         if s.optional:
             continue
-        g = torch.Generator(device="cpu")
+        g = torch.Generator(device=device)
         g.manual_seed(_tensor_seed(seed, s.name))
-        if s.role == "vector":
-            t = s.mean + norm_std * torch.randn(s.shape, generator=g, dtype=torch.float32)
-        else:
-            t = s.mean + (s.std if std is None else std) * torch.randn(
-                s.shape, generator=g, dtype=torch.float32)
-        out[s.name] = t.to(store_dtype)
+        scale = norm_std if s.role == "vector" else (s.std if std is None else std)
+        t = torch.randn(s.shape, generator=g, dtype=torch.float32, device=device)
+        out[s.name] = (s.mean + scale * t).to(store_dtype)
     return out
 
 

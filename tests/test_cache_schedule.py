@@ -1,0 +1,178 @@
+"""The cache's bookkeeping and the generation loop's decisions (no GPU)."""
+import random
+
+import pytest
+import torch
+
+import go_tinygrad_b200  # noqa: F401
+from go_tinygrad_b200.cache import (Cache, CacheFull, CacheMisuse, KVRequest, PagePool, SlotTable,
+                                    StateRequest)
+from go_tinygrad_b200.engine.schedule import (RequestTooLarge, SequenceProgress, live,
+                                              plan_batches)
+
+
+def test_slot_table_never_loses_or_doubles_a_slot():
+    table = SlotTable(5)
+    rng = random.Random(0)
+    held = set()
+    for _ in range(2000):
+        if held and (rng.random() < 0.5 or len(held) == 5):
+            s = rng.choice(sorted(held))
+            table.free(s)
+            held.discard(s)
+        else:
+            s = table.alloc()
+            assert s not in held and 0 <= s < 5
+            held.add(s)
+        assert set(table.held()) == held and table.n_free == 5 - len(held)
+    for s in sorted(held):
+        table.free(s)
+    assert table.n_free == 5
+    with pytest.raises(CacheMisuse, match="not held"):
+        table.free(0)
+    with pytest.raises(CacheMisuse):
+        table.free(7)
+    got = [table.alloc() for _ in range(5)]
+    assert sorted(got) == [0, 1, 2, 3, 4]
+    with pytest.raises(CacheFull):
+        table.alloc()
+
+
+def test_page_pool_accounts_for_every_page():
+    pool = PagePool(6)
+    a = pool.alloc(2, slot=0)
+    b = pool.alloc(3, slot=1)
+    assert len(set(a) | set(b)) == 5 and pool.n_free == 1
+    with pytest.raises(CacheFull):
+        pool.alloc(2, slot=2)
+    assert pool.n_free == 1                               # a refused request takes nothing
+    with pytest.raises(CacheMisuse, match="belongs to"):
+        pool.free(a, slot=1)
+    pool.free(a, slot=0)
+    with pytest.raises(CacheMisuse):
+        pool.free(a, slot=0)                              # freed twice
+    assert pool.owned_by(1) == sorted(b) and pool.n_free == 3
+
+
+def make_cache(max_tokens=64 * 6, max_slots=3):
+    requests = [[KVRequest(2, 16)], [KVRequest(2, 16)], [KVRequest(1, 32, window=128)],
+                [StateRequest("h", (4,))], []]
+    return Cache(requests, [None, None, None, None, 1], max_tokens=max_tokens, max_slots=max_slots,
+                 dtype=torch.float32, device="cpu")
+
+
+def test_groups_have_storage_of_their_own():
+    cache = make_cache()
+    assert len(cache.groups) == 2                         # all-keys layers and the windowed layer
+    full, win = cache.groups
+    assert full.storage.shape == (2, 6, 2, 2, 64, 16) and win.storage.shape == (1, 6, 2, 1, 64, 32)
+    assert cache.handles[0].kv.k.data_ptr() != cache.handles[1].kv.k.data_ptr()
+    assert cache.handles[2].kv.window == 128 and cache.handles[0].kv.window is None
+    assert cache.handles[3].kv is None and cache.handles[3].state("h").shape == (3, 4)
+    shared = cache.handles[4]                             # reads entry 1's keys, writes none
+    assert not shared.writes and shared.kv.k.data_ptr() == cache.handles[1].kv.k.data_ptr()
+    assert cache.handles[1].writes
+
+
+def test_sequences_take_and_return_pages():
+    cache = make_cache()
+    a, b = cache.open_sequence(), cache.open_sequence()
+    cache.reserve(a, 65)
+    cache.reserve(b, 64)
+    assert cache.free_pages() == [3, 3] and cache.tokens_held() == 192
+    cache.advance(a, 65)
+    cache.advance(b, 10)
+    assert (cache.length(a), cache.length(b)) == (65, 10)
+    with pytest.raises(CacheMisuse, match="without reserved pages"):
+        cache.advance(b, 60)
+    # block tables: the pages a sequence got, in order, distinct across sequences and groups' own
+    for grp in cache.groups:
+        pa, pb = grp.pages_of[a], grp.pages_of[b]
+        assert grp.table_host[a, :2].tolist() == pa and grp.table_host[b, :1].tolist() == pb
+        assert not set(pa) & set(pb)
+    with pytest.raises(CacheFull, match="full"):
+        cache.reserve_many([(a, 65 + 128), (b, 64 + 128)])
+    assert cache.free_pages() == [3, 3]                   # all or nothing
+    cache.truncate(a, 3)
+    assert cache.length(a) == 3 and cache.free_pages() == [3, 3]
+    with pytest.raises(CacheMisuse):
+        cache.truncate(a, 4)
+    cache.close_sequence(a)
+    assert cache.free_pages() == [5, 5] and cache.open_slots() == [b]
+    with pytest.raises(CacheMisuse, match="not open"):
+        cache.close_sequence(a)
+    with pytest.raises(CacheMisuse):
+        cache.reserve(a, 1)
+    cache.close_sequence(b)
+    assert cache.free_pages() == [6, 6] and cache.open_slots() == [] and cache.tokens_held() == 0
+
+
+def test_slots_are_used_again_and_state_starts_at_zero():
+    cache = make_cache()
+    seen = set()
+    for round_ in range(4):
+        slots = [cache.open_sequence() for _ in range(3)]
+        with pytest.raises(CacheFull, match="slots"):
+            cache.open_sequence()
+        for s in slots:
+            assert float(cache.handles[3].state("h")[s].abs().sum()) == 0.0
+            cache.handles[3].state("h")[s] += 1.0 + round_     # a mixer leaves state behind
+            cache.reserve(s, 100)
+            cache.advance(s, 100)
+            seen.add(s)
+        for s in slots:
+            cache.close_sequence(s)
+    assert seen == {0, 1, 2} and cache.free_pages() == [6, 6]
+
+
+def test_a_sequence_cannot_outgrow_the_table():
+    cache = Cache([[KVRequest(1, 16)]], [None], max_tokens=64 * 10, max_slots=2, max_position=200,
+                  dtype=torch.float32, device="cpu")
+    assert cache.pages_per_seq == 4
+    s = cache.open_sequence()
+    cache.reserve(s, 256)
+    with pytest.raises(CacheFull, match="longest"):
+        cache.reserve(s, 257)
+
+
+# ----------------------------------------------------------------- the loop's decisions
+def test_batches_fit_the_cache_and_keep_order():
+    lengths = [5, 70, 17, 1, 64, 130, 3]
+    new = [9, 3, 20, 12, 1, 6, 33]
+    batches = plan_batches(lengths, new, max_tokens=64 * 5, max_batch=4)
+    assert [i for b in batches for i in b] == list(range(7))
+    for b in batches:
+        assert len(b) <= 4
+        assert sum((lengths[i] + new[i] - 1 + 63) // 64 * 64 for i in b) <= 64 * 5
+    assert plan_batches([10, 10, 10], [5, 5, 5], max_tokens=64 * 8, max_batch=2) == [[0, 1], [2]]
+    assert plan_batches([64], [1], max_tokens=64, max_batch=1) == [[0]]      # the last token is not fed back
+    with pytest.raises(RequestTooLarge, match="cache holds"):
+        plan_batches([100], [100], max_tokens=128, max_batch=4)
+    with pytest.raises(RequestTooLarge, match="longest"):
+        plan_batches([300], [1], max_tokens=1024, max_batch=4, max_sequence=256)
+    assert plan_batches([250], [100], max_tokens=256, max_batch=4, max_sequence=256) == [[0]]
+    with pytest.raises(ValueError, match="empty"):
+        plan_batches([0], [1], max_tokens=64, max_batch=1)
+
+
+def test_a_sequence_ends_on_stop_length_or_capacity():
+    s = SequenceProgress(0, prompt_length=4, max_new_tokens=3, stop={9})
+    s.start()
+    s.accept(5)
+    assert not s.finished
+    s.accept(9)
+    assert s.finish_reason == "stop" and s.tokens == [5, 9]      # the stop token is kept
+    with pytest.raises(RuntimeError):
+        s.accept(1)
+    t = SequenceProgress(1, 4, 2, {9})
+    t.start(); t.accept(1); t.accept(2)
+    assert t.finish_reason == "length"
+    z = SequenceProgress(2, 4, 0, set())
+    z.start()
+    assert z.finished and z.tokens == []
+    c = SequenceProgress(3, prompt_length=6, max_new_tokens=10, stop=set(), max_sequence=8)
+    c.start(); c.accept(1); c.accept(2)
+    assert not c.finished                                   # 8 tokens fit positions 0..7
+    c.accept(3)
+    assert c.finish_reason == "capacity" and len(c.tokens) == 3
+    assert live([s, t, z, c, SequenceProgress(4, 1, 1, set())])[0].request == 4

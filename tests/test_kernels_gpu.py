@@ -214,7 +214,7 @@ def test_linear_bfloat16(out_dtype, M, N, K):
 
 def test_linear_strided_operands():
     """Inputs and outputs that are column slices of wider buffers."""
-    xb, w = rnd(9, 300, dtype=torch.bfloat16), rnd(50, 96, dtype=torch.bfloat16, seed=3)
+    xb, w = rnd(9, 304, dtype=torch.bfloat16), rnd(50, 96, dtype=torch.bfloat16, seed=3)
     x = xb[:, 8:104]
     outb = torch.zeros(9, 80, dtype=torch.bfloat16, device=DEV)
     ops.linear(x, w, outb[:, 10:60])

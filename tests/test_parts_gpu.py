@@ -1,0 +1,298 @@
+"""Each part alone against the plain implementation's function for it, and the
+generality of the assembly: a toy mixer with state of its own, defined here, is
+registered, built and stepped without touching the library; a layer runs twice
+in one schedule; a layer reads another layer's cache."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import go_tinygrad_b200 as lib
+import plain_llama as plain
+from go_tinygrad_b200.cache import Cache, StateRequest
+from go_tinygrad_b200.config import Architecture, LlamaConfig, register_architecture, unregister_architecture
+from go_tinygrad_b200.engine import Model, StepEntry, step
+from go_tinygrad_b200.models.llama import llama_plan
+from go_tinygrad_b200.parts import (LayerSpec, Mixer, ModelPlan, PartSpec, ResidualStream, Runtime,
+                                    ScheduleEntry, StepContext, build_part, register_part,
+                                    unregister_part)
+from go_tinygrad_b200.weights import TensorSource, WeightSpec
+from conftest import TINY, assert_close, make_prompts
+
+pytestmark = pytest.mark.gpu
+DEV = torch.device("cuda" if torch.cuda.is_available() and torch.cuda.device_count() else "cpu")
+
+
+def context(rt, seq_lens, starts, slots, tokens=None):
+    """A StepContext for sequences that bring `seq_lens` tokens after `starts`."""
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    n = sum(seq_lens)
+    return StepContext(
+        rt=rt, n_tokens=n, n_seqs=len(seq_lens),
+        tokens=i32(tokens if tokens is not None else [0] * n),
+        positions=i32([s + j for s, l in zip(starts, seq_lens) for j in range(l)]),
+        token_seq=i32([b for b, l in enumerate(seq_lens) for _ in range(l)]),
+        cu_seqlens=i32(np.concatenate([[0], np.cumsum(seq_lens)]).tolist()),
+        slots=i32(slots), start_pos=i32(starts), max_q_len=max(seq_lens),
+        max_kv_len=max(s + l for s, l in zip(starts, seq_lens)), is_decode=all(l == 1 for l in seq_lens))
+
+
+def tensors_of(folder):
+    with TensorSource(folder) as src:
+        return {n: src.tensor(n) for n in src.names()}
+
+
+def tol(dtype):
+    return dict(rtol=1e-4, atol=1e-5) if dtype == torch.float32 else dict(rtol=3e-2, atol=3e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_parts_alone(model_folders, plain_models, name, dtype):
+    cfg, w = plain_models[name]
+    raw = tensors_of(model_folders[name])
+    plan = llama_plan(LlamaConfig.from_json(TINY[name]))
+    rt = Runtime(DEV, dtype)
+    H, V = cfg["hidden_size"], cfg["vocab_size"]
+    lens, tokens = [70, 9], make_prompts(name, [79], seed=41)[0]
+    ctx = context(rt, lens, [0, 0], [1, 0], tokens)
+    rng = np.random.default_rng(0)
+    x_np = rng.standard_normal((79, H)).astype(np.float32)
+    x_act = torch.tensor(x_np, device=DEV).to(dtype)              # an activation in the compute dtype
+    x_ref = x_act.float().cpu().numpy()
+
+    # embedding
+    emb = build_part("embedding", plan.embedding); emb.load(raw, rt)
+    stream = emb.forward(ctx)
+    np.testing.assert_array_equal(stream.residual.cpu().numpy(), plain.embed(w["model.embed_tokens.weight"], tokens))
+
+    # norm: the pending update is added in float32, then normalised
+    layer = plan.layers[1]
+    norm = build_part("norm", layer.mixer_norm); norm.load(raw, rt)
+    res = torch.tensor(x_np, device=DEV)
+    st = ResidualStream(res.clone(), x_act.clone())
+    got = norm.forward(st, ctx)
+    summed = x_np + x_ref
+    assert st.pending is None
+    np.testing.assert_allclose(st.residual.cpu().numpy(), summed, rtol=0, atol=0)
+    want = plain.rms_norm(summed, w["model.layers.1.input_layernorm.weight"], cfg["rms_norm_eps"])
+    torch.testing.assert_close(got.float().cpu(), torch.tensor(want).to(dtype).float(), **tol(dtype))
+
+    # position encoding: the angles of the step's tokens
+    pos = build_part("position", layer.mixer.params["position"]); pos.load(raw, rt)
+    table = pos.rotation(ctx).cpu().numpy()
+    inv = plain.rope_inv_freq(cfg)
+    positions = list(range(70)) + list(range(9))
+    ang = np.array(positions, dtype=np.float64)[:, None] * inv[None, :]
+    np.testing.assert_allclose(table[..., 0], np.cos(ang).astype(np.float32), rtol=0, atol=1e-7)
+    np.testing.assert_allclose(table[..., 1], np.sin(ang).astype(np.float32), rtol=0, atol=1e-7)
+    assert pos.rotation(ctx) is pos.rotation(ctx)                 # computed once per step
+
+    # mixer: attention over a cache of its own, two sequences in one step
+    mixer = build_part("mixer", layer.mixer); mixer.load(raw, rt)
+    cache = Cache([mixer.cache_requests()], [None], max_tokens=64 * 4, max_slots=2, dtype=dtype, device=DEV)
+    for _ in range(2):
+        cache.open_sequence()
+    cache.reserve_many([(1, 70), (0, 9)]); cache.flush_tables()
+    got = mixer.forward(x_act, ctx, cache.handles[0]).float().cpu().numpy()
+    want = np.concatenate([plain.attention_block(x_ref[:70], list(range(70)), "model.layers.1.", cfg, inv, w),
+                           plain.attention_block(x_ref[70:], list(range(9)), "model.layers.1.", cfg, inv, w)])
+    scale = np.abs(want).max()
+    limit = 1e-4 if dtype == torch.float32 else 4e-2
+    assert np.abs(got - want).max() <= limit * max(1.0, scale)
+
+    # feed-forward
+    ff = build_part("feed_forward", layer.feed_forward); ff.load(raw, rt)
+    got = ff.forward(x_act, ctx).float().cpu().numpy()
+    p = "model.layers.1.mlp."
+    want = plain.swiglu_mlp(x_ref, w[p + "gate_proj.weight"], w[p + "up_proj.weight"], w[p + "down_proj.weight"])
+    assert np.abs(got - want).max() <= limit * max(1.0, np.abs(want).max())
+
+    # block: the whole layer; its second update stays pending
+    block = build_part("block", layer.block)
+    block.assemble(norm, mixer, build_part("norm", layer.feed_forward_norm), ff)
+    block.ff_norm.load(raw, rt)
+    cache2 = Cache([mixer.cache_requests()], [None], max_tokens=64 * 4, max_slots=2, dtype=dtype, device=DEV)
+    for _ in range(2):
+        cache2.open_sequence()
+    cache2.reserve_many([(1, 70), (0, 9)]); cache2.flush_tables()
+    st = ResidualStream(torch.tensor(x_np, device=DEV))
+    block.forward(st, context(rt, lens, [0, 0], [1, 0], tokens), cache2.handles[0])
+    got = (st.residual + st.pending.float()).cpu().numpy()
+    want = np.concatenate([plain.decoder_layer(x_np[:70], list(range(70)), 1, cfg, inv, w),
+                           plain.decoder_layer(x_np[70:], list(range(9)), 1, cfg, inv, w)])
+    assert np.abs(got - want).max() <= limit * max(1.0, np.abs(want).max())
+
+    # head on chosen rows
+    head = build_part("head", plan.head); head.load(raw, rt)
+    fnorm = build_part("norm", plan.final_norm); fnorm.load(raw, rt)
+    rows = torch.tensor([78, 0, 69], dtype=torch.int32, device=DEV)
+    st = ResidualStream(torch.tensor(x_np, device=DEV))
+    got = head.forward(fnorm.forward(st, ctx, rows=rows), ctx).cpu().numpy()
+    want = plain.lm_head(x_np[[78, 0, 69]], cfg, w)
+    assert got.shape == (3, V) and np.abs(got - want).max() <= limit * max(1.0, np.abs(want).max())
+
+
+# ------------------------------------------------------------------ a toy mixer with state
+class DecayMixer(Mixer):
+    """h_t = a * h_{t-1} + (1 - a) * x_t per channel, y_t = W h_t.  Its state h is a
+    record of fixed size per sequence, kept in the cache beside the keys and values
+    of other layers.  Written with plain torch: it is a test's toy, not a kernel."""
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.size = int(self.param("hidden_size"))
+        self.decay_name, self.out_name = self.param("decay"), self.param("out")
+
+    def weight_specs(self):
+        return [WeightSpec(self.decay_name, (self.size,), role="vector", mean=0.0),
+                WeightSpec(self.out_name, (self.size, self.size))]
+
+    def cache_requests(self):
+        return [StateRequest("h", (self.size,), "float32")]
+
+    def load(self, tensors, rt):
+        self.a = torch.sigmoid(rt.vector(tensors[self.decay_name]))
+        self.w = rt.matrix(tensors[self.out_name])
+
+    def forward(self, x, ctx, cache):
+        state = cache.state("h")
+        cu, slots = ctx.cu_seqlens.tolist(), ctx.slots.tolist()
+        hs = torch.empty(x.shape, dtype=torch.float32, device=x.device)
+        for b, slot in enumerate(slots):
+            h = state[slot].clone()
+            for t in range(cu[b], cu[b + 1]):
+                h = self.a * h + (1 - self.a) * x[t].float()
+                hs[t] = h
+            state[slot] = h
+        return (hs.to(x.dtype).float() @ self.w.float().T).to(x.dtype)
+
+
+def toy_plan(cfg):
+    """Llama's plan with the mixer of every odd layer replaced by the toy."""
+    base = llama_plan(cfg)
+    layers = []
+    for i, layer in enumerate(base.layers):
+        if i % 2 == 1:
+            layer = LayerSpec(layer.block, layer.mixer_norm,
+                              PartSpec("decay", {"hidden_size": cfg.hidden_size,
+                                                 "decay": f"model.layers.{i}.decay.a",
+                                                 "out": f"model.layers.{i}.decay.out.weight"}),
+                              layer.feed_forward_norm, layer.feed_forward)
+        layers.append(layer)
+    return ModelPlan(base.hidden_size, base.vocab_size, base.embedding, tuple(layers), base.schedule,
+                     base.final_norm, base.head, base.stop_tokens, base.max_position)
+
+
+def plain_toy_forward(cfg, w, tokens):
+    positions = list(range(len(tokens)))
+    inv = plain.rope_inv_freq(cfg)
+    x = plain.embed(w["model.embed_tokens.weight"], tokens)
+    for i in range(cfg["num_hidden_layers"]):
+        if i % 2 == 0:
+            x = plain.decoder_layer(x, positions, i, cfg, inv, w)
+            continue
+        p = f"model.layers.{i}."
+        n = plain.rms_norm(x, w[p + "input_layernorm.weight"], cfg["rms_norm_eps"])
+        a = 1.0 / (1.0 + np.exp(-w[p + "decay.a"].astype(np.float32)))
+        h = np.zeros(cfg["hidden_size"], dtype=np.float32)
+        hs = np.zeros_like(n)
+        for t in range(len(tokens)):
+            h = a * h + (1 - a) * n[t]
+            hs[t] = h
+        x = x + plain.linear(hs, w[p + "decay.out.weight"])
+        n2 = plain.rms_norm(x, w[p + "post_attention_layernorm.weight"], cfg["rms_norm_eps"])
+        x = x + plain.swiglu_mlp(n2, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"],
+                                 w[p + "mlp.down_proj.weight"])
+    return plain.lm_head(x, cfg, w)
+
+
+def test_a_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path):
+    register_part("mixer", "decay")(DecayMixer)
+    arch = register_architecture(Architecture(("ToyDecayForCausalLM",), LlamaConfig.from_json, toy_plan))
+    try:
+        raw = dict(TINY["B"], architectures=["ToyDecayForCausalLM"], model_type="toy_decay")
+        folder = str(tmp_path / "toy")
+        lib.write_random_model(folder, raw, seed=5, dtype="float32", std=0.1, norm_std=0.05)
+        cfg, w = plain.read_model(folder)
+        model = Model.load(folder, dtype="float32", device="cuda")
+        assert type(model.blocks[1].mixer) is DecayMixer
+        cache = model.new_cache(max_tokens=64 * 4, max_slots=2)
+        assert len(cache.groups) == 1 and cache.groups[0].storage.shape[0] == 2     # layers 0 and 2 hold keys
+        p, q = make_prompts("B", [50, 20], seed=42)
+        want_p, want_q = plain_toy_forward(cfg, w, p), plain_toy_forward(cfg, w, q)
+        for round_ in range(2):                     # the second round reuses slots whose state is stale
+            sp, sq = cache.open_sequence(), cache.open_sequence()
+            got = step(model, cache, [StepEntry(sp, p[:30], list(range(30))), StepEntry(sq, q, list(range(20)))])
+            got = got.cpu().numpy()
+            assert_close(got[:30], want_p[:30], "float32", "toy whole")
+            assert_close(got[30:], want_q, "float32", "toy second sequence")
+            cache.close_sequence(sq)
+            rest = [step(model, cache, [StepEntry(sp, [p[t]], [0])]).cpu().numpy() for t in range(30, 50)]
+            assert_close(np.concatenate(rest), want_p[30:], "float32", "toy one by one")
+            cache.close_sequence(sp)
+    finally:
+        unregister_architecture(arch)
+        unregister_part("mixer", "decay")
+
+
+# ------------------------------------------------------- the order of layers is data
+def test_a_layer_named_twice_and_a_layer_that_reads_another_cache(model_folders, plain_models, tmp_path):
+    name = "A"
+    cfg, w = plain_models[name]
+    base = llama_plan(LlamaConfig.from_json(TINY[name]))
+
+    # layer 0 runs twice: each run has keys and values of its own
+    twice = ModelPlan(base.hidden_size, base.vocab_size, base.embedding, base.layers,
+                      (ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(0)),
+                      base.final_norm, base.head, base.stop_tokens, base.max_position)
+    model = Model(twice, Runtime(DEV, torch.float32)).load_tensors(tensors_of(model_folders[name]))
+    cache = model.new_cache(max_tokens=64 * 2)
+    assert cache.groups[0].storage.shape[0] == 3
+    (p,) = make_prompts(name, [40], seed=43)
+    want = plain.forward(cfg, w, p, layer_order=[0, 1, 0])
+    s = cache.open_sequence()
+    got = [step(model, cache, [StepEntry(s, p[:25], list(range(25)))]).cpu().numpy()]
+    got += [step(model, cache, [StepEntry(s, [p[t]], [0])]).cpu().numpy() for t in range(25, 40)]
+    assert_close(np.concatenate(got), want, "float32", "layer named twice")
+
+    # a third run: layer 1's queries over the keys and values that run 0 stored
+    l1 = base.layers[1]
+    reader = LayerSpec(l1.block, l1.mixer_norm,
+                       PartSpec("gqa_attention", dict(l1.mixer.params, own_kv=False)),
+                       l1.feed_forward_norm, l1.feed_forward)
+    shared = ModelPlan(base.hidden_size, base.vocab_size, base.embedding, (base.layers[0], reader),
+                       (ScheduleEntry(0), ScheduleEntry(1, cache=0)),
+                       base.final_norm, base.head, base.stop_tokens, base.max_position)
+    shared.check()
+    raw = {k: v for k, v in tensors_of(model_folders[name]).items()
+           if k not in ("model.layers.1.self_attn.k_proj.weight", "model.layers.1.self_attn.v_proj.weight")}
+    model = Model(shared, Runtime(DEV, torch.float32)).load_tensors(raw)
+    assert "model.layers.1.self_attn.k_proj.weight" not in {s.name for s in model.weight_specs()}
+    cache = model.new_cache(max_tokens=64 * 2)
+    assert cache.groups[0].storage.shape[0] == 1                 # one store, read by both runs
+
+    positions = list(range(40))
+    inv = plain.rope_inv_freq(cfg)
+    nh, nkv, hd, eps = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"], cfg["rms_norm_eps"]
+    x = plain.embed(w["model.embed_tokens.weight"], p)
+    n0 = plain.rms_norm(x, w["model.layers.0.input_layernorm.weight"], eps)
+    k0 = plain.rope(plain.linear(n0, w["model.layers.0.self_attn.k_proj.weight"]), positions, inv, nkv, hd)
+    v0 = plain.linear(n0, w["model.layers.0.self_attn.v_proj.weight"])
+    x = plain.decoder_layer(x, positions, 0, cfg, inv, w)
+    n1 = plain.rms_norm(x, w["model.layers.1.input_layernorm.weight"], eps)
+    q1 = plain.rope(plain.linear(n1, w["model.layers.1.self_attn.q_proj.weight"]), positions, inv, nh, hd)
+    x = x + plain.linear(plain.causal_gqa_attention(q1, k0, v0, nh, nkv, hd), w["model.layers.1.self_attn.o_proj.weight"])
+    n2 = plain.rms_norm(x, w["model.layers.1.post_attention_layernorm.weight"], eps)
+    x = x + plain.swiglu_mlp(n2, w["model.layers.1.mlp.gate_proj.weight"], w["model.layers.1.mlp.up_proj.weight"],
+                             w["model.layers.1.mlp.down_proj.weight"])
+    want = plain.lm_head(x, cfg, w)
+    s = cache.open_sequence()
+    got = [step(model, cache, [StepEntry(s, p[:25], list(range(25)))]).cpu().numpy()]
+    got += [step(model, cache, [StepEntry(s, [p[t]], [0])]).cpu().numpy() for t in range(25, 40)]
+    assert_close(np.concatenate(got), want, "float32", "layer that reads another layer's cache")
+
+    with pytest.raises(ValueError, match="does not run before"):
+        ModelPlan(base.hidden_size, base.vocab_size, base.embedding, base.layers,
+                  (ScheduleEntry(0, cache=1), ScheduleEntry(1)), base.final_norm, base.head).check()
