@@ -34,7 +34,10 @@ LIBRARIES: Dict[str, str] = {
     "sampling": "sampling.cu",
     "gemm_bf16_mma": "gemm_bf16_mma.cu",
     "attention_bf16": "attention_bf16.cu",
+    "attention_decode_static": "attention_decode_static.cu",
 }
+# sources a library's file includes textually (they count for staleness)
+INCLUDED_SOURCES: Dict[str, List[str]] = {"attention_decode_static.cu": ["attention_bf16.cu"]}
 
 
 class KernelBuildError(RuntimeError):
@@ -59,7 +62,7 @@ def _headers() -> List[str]:
 def _digest(source: str) -> str:
     h = hashlib.sha256()
     h.update(" ".join(NVCC_FLAGS).encode())
-    for name in [source] + _headers():
+    for name in [source] + INCLUDED_SOURCES.get(source, []) + _headers():
         h.update(name.encode())
         with open(os.path.join(CSRC, name), "rb") as f:
             h.update(f.read())
