@@ -123,6 +123,26 @@ def prefill_flops(cfg, n_layers, T):
     return n_layers * (gemm + attn) + 2 * V * H
 
 
+def prefill_only(args, model, cache, vocab, gen):
+    """For profilers: `warmup` + `steps` prefills of one 2,048-token prompt."""
+    import torch
+    from go_tinygrad_b200.engine import StepEntry, step
+    prompt = torch.randint(0, vocab, (2048,), generator=gen).tolist()
+    times = []
+    for i in range(args.warmup + args.steps):
+        slot = cache.open_sequence()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        step(model, cache, [StepEntry(slot, prompt, [2047])])
+        b.record()
+        torch.cuda.synchronize()
+        if i >= args.warmup:
+            times.append(a.elapsed_time(b))
+        cache.close_sequence(slot)
+    print(json.dumps({"only": "prefill", "ms": round(statistics.median(times), 3)}))
+    return 0
+
+
 def run_own(args):
     import torch
     import go_tinygrad_b200 as lib
@@ -136,6 +156,8 @@ def run_own(args):
     pk = peaks()
     model = lib.Model.random(cfg, seed=0, dtype="bfloat16", device=dev, std=0.02)
     context, vocab = args.context, cfg["vocab_size"]
+    if args.only != "all":
+        args.points = False
     biggest = max([args.batch] + ([1, 64] if args.points else []))
     cache = model.new_cache(max_tokens=biggest * context + 64 * 40, max_slots=biggest + 1)
     for grp in cache.groups:                       # synthetic keys and values of unit scale
@@ -150,7 +172,8 @@ def run_own(args):
             cache.reserve(s, context)
             cache.advance(s, context - total)
         cache.flush_tables()
-        db = DecodeBatch(model, cache, slots, list(range(batch)), lib.Sampler(0.0, 0))
+        db = DecodeBatch(model, cache, slots, list(range(batch)), lib.Sampler(0.0, 0),
+                         use_graph=not args.eager)
         tokens = torch.randint(0, vocab, (batch,), generator=gen).tolist()
         sampler = ClockSampler()
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -185,6 +208,13 @@ def run_own(args):
             cache.close_sequence(s)
         return batch / (ms * 1e-3), ms, clocks, per_step + 1      # +1: the kernel that feeds tokens back
 
+    if args.only == "decode":          # for profilers: the decode steps and nothing else
+        value, ms, _, launches = decode_run(args.batch, args.steps, args.warmup, host=False)
+        print(json.dumps({"only": "decode", "value": round(value, 1), "ms_per_step": round(ms, 4),
+                          "launches_per_step": launches, "eager": args.eager}))
+        return 0
+    if args.only == "prefill":
+        return prefill_only(args, model, cache, vocab, gen)
     value, ms, clocks, launches = decode_run(args.batch, args.steps, args.warmup, host=False)
     e2e_value, e2e_ms, _, _ = decode_run(args.batch, args.steps, args.warmup, host=True)
     points = {}
@@ -254,6 +284,10 @@ def main():
                     help="fewer layers than the model has, where memory or time needs it")
     ap.add_argument("--no-points", dest="points", action="store_false",
                     help="skip the batch-1 and batch-64 decode points")
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
+                    help="run one part only and print a short line (for profilers)")
+    ap.add_argument("--eager", action="store_true",
+                    help="launch the decode step kernel by kernel instead of replaying a graph")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":

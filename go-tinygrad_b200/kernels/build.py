@@ -33,6 +33,7 @@ LIBRARIES: Dict[str, str] = {
     "attention_simple": "attention_simple.cu",
     "sampling": "sampling.cu",
     "gemm_bf16_mma": "gemm_bf16_mma.cu",
+    "gemm_bf16_skinny": "gemm_bf16_skinny.cu",
     "attention_bf16": "attention_bf16.cu",
     "attention_decode_static": "attention_decode_static.cu",
 }

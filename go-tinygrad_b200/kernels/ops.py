@@ -29,6 +29,7 @@ _SIGNATURES = {
     "gtg_advance": ("elementwise", [_P, _P, _P, _P, _I, _P]),
     "gtg_gemm_f32": ("gemm_f32", [_P, _I, _P, _I, _P, _I, _I, _I, _I, _P]),
     "gtg_gemm_bf16_mma": ("gemm_bf16_mma", [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _P]),
+    "gtg_gemm_bf16_skinny": ("gemm_bf16_skinny", [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _P]),
     "gtg_attention_simple": ("attention_simple", [_I, _P, _I, _P, _I, _P, _P, _L, _P, _I, _P, _P, _P,
                                                   _I, _I, _I, _I, _F, _I, _P]),
     "gtg_attention_bf16_supports": ("attention_bf16", [_I]),
@@ -194,9 +195,14 @@ def advance(tokens: torch.Tensor, positions: torch.Tensor, steps: torch.Tensor,
 
 
 # ---------------------------------------------------------------- matrix products
-def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+SKINNY_MAX_ROWS = 64
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, kind: str = "auto") -> None:
     """out[M,N] = x[M,K] . w[N,K]^T.  float32 operands take the true 32-bit
-    kernel; bfloat16 operands accumulate in float and write bfloat16 or float32."""
+    kernel; bfloat16 operands accumulate in float and write bfloat16 or float32.
+    `kind` picks the bfloat16 kernel: "auto" (by the number of rows), "skinny"
+    (weight streaming, up to 64 rows) or "tiled"."""
     _rows2d(x, "linear: x"); _rows2d(w, "linear: w"); _rows2d(out, "linear: out")
     M, K = x.shape
     N = w.shape[0]
@@ -210,9 +216,12 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
     _need(out.dtype in (torch.bfloat16, torch.float32), "linear: out must be bfloat16 or float32")
     _need(K % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0,
           f"linear(bfloat16): the inner size {K} and the row strides must be multiples of 8")
-    _check(_fn("gtg_gemm_bf16_mma")(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0),
-                                    1 if out.dtype == torch.float32 else 0, M, N, K, _stream()),
-           "linear(bfloat16)")
+    # few rows (a decode step): stream the weights once; many rows: tiled product
+    symbol = "gtg_gemm_bf16_skinny" if M <= SKINNY_MAX_ROWS and kind != "tiled" else "gtg_gemm_bf16_mma"
+    if kind == "skinny":
+        _need(M <= SKINNY_MAX_ROWS, f"linear: the weight-streaming kernel takes at most {SKINNY_MAX_ROWS} rows")
+    _check(_fn(symbol)(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0),
+                       1 if out.dtype == torch.float32 else 0, M, N, K, _stream()), "linear(bfloat16)")
 
 
 # ----------------------------------------------------------------------- attention

@@ -198,13 +198,17 @@ def test_linear_float32_does_not_depend_on_the_batch():
 
 
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("kind", ["skinny", "tiled"])
 @pytest.mark.parametrize("M,N,K", [(1, 17, 8), (5, 96, 264), (64, 391, 96), (130, 130, 40),
                                    (257, 1000, 2048), (3, 2048, 8192), (8, 6144, 2048),
-                                   (300, 144, 96)])
-def test_linear_bfloat16(out_dtype, M, N, K):
+                                   (300, 144, 96), (9, 50, 1000), (17, 33, 72), (40, 1001, 2056),
+                                   (33, 16, 8200)])
+def test_linear_bfloat16(out_dtype, kind, M, N, K):
+    if kind == "skinny" and M > ops.SKINNY_MAX_ROWS:
+        pytest.skip("more rows than the weight-streaming kernel takes")
     x, w = rnd(M, K, dtype=torch.bfloat16, seed=1), rnd(N, K, dtype=torch.bfloat16, seed=2)
     out = torch.empty(M, N, dtype=out_dtype, device=DEV)
-    ops.linear(x, w, out)
+    ops.linear(x, w, out, kind=kind)
     want = (x.double() @ w.double().T).float()
     if out_dtype == torch.bfloat16:
         torch.testing.assert_close(out.float(), want.to(torch.bfloat16).float(), rtol=1.6e-2, atol=1e-2 * math.sqrt(K / 64))
