@@ -10,38 +10,82 @@
 //     MMA's k slots are assigned to those 8 values in the order they lie in
 //     memory (a dot product does not care about the order of k as long as both
 //     operands agree), so no shuffle or shared-memory staging is needed.
-//   * Four k blocks are in flight per thread (8 x 16-byte loads of W), W bypasses
-//     L1 (read once), X stays in L1/L2 (read by every CTA).
-//   * The 8 partial sums of an output are added in warp order through shared
-//     memory: the result does not depend on timing.
+//   * A CTA reads at most 2048 values of k per row and pass.  Its 16 x 4 KB of W
+//     arrive by sixteen bulk asynchronous copies (cp.async.bulk, the TMA engine)
+//     that one thread issues up front and that complete on one mbarrier: 64 KB
+//     in flight per CTA whatever the compiler does with registers, and one
+//     exposure to memory latency.  Rows are padded by 64 bytes in shared memory
+//     so that the 16-byte fragment reads of a quarter-warp fall in distinct
+//     banks.  Longer rows are split over a thread-block cluster (2, 4 or 8 CTAs
+//     along k) whose partial sums meet in the first CTA's shared memory, so that
+//     a product with few output features and a long inner size still fills the
+//     GPU.
+//   * The wait on the mbarrier is bounded: if the copies never land, the kernel
+//     records it in a status word (gtg_gemm_bf16_skinny_status) and returns.
+//   * X stays in L1/L2 (read by every CTA) and is loaded with plain loads.
+//   * Partial sums are added in a fixed order (warps, then cluster ranks): the
+//     result does not depend on timing.
 // Any N; K a multiple of 8; output bfloat16 or float.
 #include "mma_helpers.cuh"
+#include <cooperative_groups.h>
+
+namespace cg = cooperative_groups;
 
 namespace {
 constexpr int kWarps = 8;
-constexpr int kUnroll = 4;
+constexpr int kBlocksPerWarp = 8;                       // k blocks of 32 per warp and pass
+constexpr int kPassK = kWarps * kBlocksPerWarp * 32;    // 2048 values of k per CTA and pass
+constexpr int kMaxCluster = 8;
 
-__device__ __forceinline__ uint4 ld_stream16(const void* p) {
-    uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-    return v;
-}
+constexpr int kRowPad = 64;                              // bytes between rows of the staged tile
+constexpr int kRowStride = kPassK * 2 + kRowPad;
+constexpr int kTileBytes = 16 * kRowStride;
+constexpr unsigned kSpinLimit = 1u << 22;
+
+__device__ int g_status = 0;                             // 1: a wait on the copies gave up
+
 __device__ __forceinline__ uint4 ld_cached16(const void* p) {
     return __ldg(reinterpret_cast<const uint4*>(p));
 }
+__device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::);
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_copy(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+// True once the phase with this parity has completed; gives up after kSpinLimit polls.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (unsigned i = 0; i < kSpinLimit; ++i) {
+        uint32_t done;
+        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+                     "selp.u32 %0, 1, 0, p;\n}\n" : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    return false;
+}
 
+// grid = (ceil(N/16), S) with clusters of (1, S, 1): blockIdx.y is the CTA's
+// rank in its cluster and the index of its slice [rank*k_slice, +k_slice) of k.
 template <int NT, typename OutT>
 __global__ void __launch_bounds__(kWarps * 32)
 gemm_skinny_kernel(const bf16* __restrict__ X, int ldx, const bf16* __restrict__ W, int ldw,
-                   OutT* __restrict__ C, int ldc, int M, int N, int K) {
-    __shared__ float red[kWarps][16][NT * 8 + 1];
+                   OutT* __restrict__ C, int ldc, int M, int N, int K, int k_slice) {
+    extern __shared__ __align__(128) unsigned char tile[];      // 16 rows of W, kRowStride apart
+    __shared__ float red[kWarps][16][NT * 8 + 1];        // later reused for the cluster's partial sums
+    __shared__ __align__(8) unsigned long long bar_storage;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int n0 = blockIdx.x * 16;
-    const int r0 = min(n0 + g, N - 1), r1 = min(n0 + g + 8, N - 1);     // clamped: extra rows are dropped at the store
-    const bf16* w0 = W + (size_t)r0 * ldw + t * 8;
-    const bf16* w1 = W + (size_t)r1 * ldw + t * 8;
+    const int rank = blockIdx.y, n_ranks = gridDim.y;
+    const int k_begin = rank * k_slice, k_end = min(K, k_begin + k_slice);
+    const uint32_t bar = smem_u32(&bar_storage), tile_addr = smem_u32(tile);
+    if (threadIdx.x == 0) mbar_init(bar, 1);
+    __syncthreads();
     const bf16* xrow[NT];
 #pragma unroll
     for (int j = 0; j < NT; ++j) xrow[j] = X + (size_t)min(j * 8 + g, M - 1) * ldx + t * 8;
@@ -50,29 +94,40 @@ gemm_skinny_kernel(const bf16* __restrict__ X, int ldx, const bf16* __restrict__
 #pragma unroll
     for (int j = 0; j < NT; ++j) { acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f; }
 
-    const int nkb = (K + 31) / 32;
-    for (int kb = warp; kb < nkb; kb += kWarps * kUnroll) {
-        uint4 wa[kUnroll], wb[kUnroll];
-        bool ok[kUnroll];
-#pragma unroll
-        for (int u = 0; u < kUnroll; ++u) {
-            const int k = (kb + u * kWarps) * 32;
-            ok[u] = (kb + u * kWarps) < nkb && (k + t * 8) < K;
-            wa[u] = ok[u] ? ld_stream16(w0 + k) : make_uint4(0, 0, 0, 0);
-            wb[u] = ok[u] ? ld_stream16(w1 + k) : make_uint4(0, 0, 0, 0);
+    uint32_t parity = 0;
+    for (int base = k_begin; base < k_end; base += kPassK) {
+        const int k_len = min(kPassK, k_end - base);          // a multiple of 8
+        if (threadIdx.x == 0) {
+            mbar_expect_tx(bar, 16u * (uint32_t)k_len * 2u);
+            for (int r = 0; r < 16; ++r)                       // rows beyond N repeat the last one; dropped at the store
+                bulk_copy(tile_addr + r * kRowStride, W + (size_t)min(n0 + r, N - 1) * ldw + base,
+                          (uint32_t)k_len * 2u, bar);
         }
+        if (!mbar_wait(bar, parity)) {
+            if (threadIdx.x == 0) atomicExch(&g_status, 1);
+            mbar_wait(bar, parity);                            // give the copies in flight one more bounded chance
+            return;
+        }
+        parity ^= 1;
 #pragma unroll
-        for (int u = 0; u < kUnroll; ++u) {
-            const int k = (kb + u * kWarps) * 32;
-            const uint32_t a_lo[4] = {wa[u].x, wb[u].x, wa[u].y, wb[u].y};
-            const uint32_t a_hi[4] = {wa[u].z, wb[u].z, wa[u].w, wb[u].w};
+        for (int u = 0; u < kBlocksPerWarp; ++u) {
+            const int kl = (warp + u * kWarps) * 32 + t * 8;   // this thread's 8 values of k within the pass
+            const bool ok = kl < k_len;
+            uint4 wa = make_uint4(0, 0, 0, 0), wb = wa;
+            if (ok) {
+                wa = *reinterpret_cast<const uint4*>(tile + g * kRowStride + kl * 2);
+                wb = *reinterpret_cast<const uint4*>(tile + (g + 8) * kRowStride + kl * 2);
+            }
+            const uint32_t a_lo[4] = {wa.x, wb.x, wa.y, wb.y};
+            const uint32_t a_hi[4] = {wa.z, wb.z, wa.w, wb.w};
 #pragma unroll
             for (int j = 0; j < NT; ++j) {
-                const uint4 xb = ok[u] ? ld_cached16(xrow[j] + k) : make_uint4(0, 0, 0, 0);
+                const uint4 xb = ok ? ld_cached16(xrow[j] + base + kl - t * 8) : make_uint4(0, 0, 0, 0);
                 mma_bf16_16816(acc[j], a_lo, xb.x, xb.y);
                 mma_bf16_16816(acc[j], a_hi, xb.z, xb.w);
             }
         }
+        __syncthreads();                                       // the tile is free for the next pass
     }
     // acc[j][0,1]: feature g, tokens 8j+2t, +1;  acc[j][2,3]: feature g+8, same tokens
 #pragma unroll
@@ -83,27 +138,100 @@ gemm_skinny_kernel(const bf16* __restrict__ X, int ldx, const bf16* __restrict__
         red[warp][g + 8][j * 8 + t * 2 + 1] = acc[j][3];
     }
     __syncthreads();
+    if (n_ranks == 1) {
+        for (int idx = threadIdx.x; idx < 16 * NT * 8; idx += kWarps * 32) {
+            const int m = idx >> 4, r = idx & 15;          // consecutive threads -> consecutive features
+            if (m >= M || n0 + r >= N) continue;
+            float s = 0.f;
+#pragma unroll
+            for (int w = 0; w < kWarps; ++w) s += red[w][r][m];
+            C[(size_t)m * ldc + n0 + r] = from_f32<OutT>(s);
+        }
+        return;
+    }
+    // Several CTAs share the rows.  Every rank sums its warps into registers; once
+    // all ranks have done so (first cluster barrier) rank 0's `red` is free and
+    // receives one block of sums per rank; after the second barrier rank 0 adds
+    // them in rank order.
+    constexpr int kPerThread = (16 * NT * 8 + kWarps * 32 - 1) / (kWarps * 32);
+    float mine[kPerThread];
+#pragma unroll
+    for (int i = 0; i < kPerThread; ++i) {
+        const int idx = threadIdx.x + i * kWarps * 32;
+        float s = 0.f;
+        if (idx < 16 * NT * 8) {
+            const int m = idx >> 4, r = idx & 15;
+#pragma unroll
+            for (int w = 0; w < kWarps; ++w) s += red[w][r][m];
+        }
+        mine[i] = s;
+    }
+    cg::cluster_group cluster = cg::this_cluster();
+    cluster.sync();
+    float* gather = cluster.map_shared_rank(&red[0][0][0], 0);     // [rank][16 * NT * 8] in rank 0
+#pragma unroll
+    for (int i = 0; i < kPerThread; ++i) {
+        const int idx = threadIdx.x + i * kWarps * 32;
+        if (idx < 16 * NT * 8) gather[rank * 16 * NT * 8 + idx] = mine[i];
+    }
+    cluster.sync();
+    if (rank != 0) return;
+    const float* sums = &red[0][0][0];
     for (int idx = threadIdx.x; idx < 16 * NT * 8; idx += kWarps * 32) {
-        const int m = idx >> 4, r = idx & 15;          // consecutive threads -> consecutive features
+        const int m = idx >> 4, r = idx & 15;
         if (m >= M || n0 + r >= N) continue;
         float s = 0.f;
-#pragma unroll
-        for (int w = 0; w < kWarps; ++w) s += red[w][r][m];
+        for (int c = 0; c < n_ranks; ++c) s += sums[c * 16 * NT * 8 + idx];
         C[(size_t)m * ldc + n0 + r] = from_f32<OutT>(s);
     }
+}
+
+template <int NT, typename OutT>
+int launch_typed(const bf16* X, int ldx, const bf16* W, int ldw, OutT* C, int ldc,
+                 int M, int N, int K, cudaStream_t stream) {
+    // the fewest ranks (a power of two, at most 8) whose slice fits one pass
+    int ranks = 1;
+    while (ranks < kMaxCluster && (K + ranks - 1) / ranks > kPassK) ranks *= 2;
+    const int k_slice = (((K + ranks - 1) / ranks) + 31) / 32 * 32;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((N + 15) / 16, ranks, 1);
+    cfg.blockDim = dim3(kWarps * 32, 1, 1);
+    cfg.dynamicSmemBytes = kTileBytes;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t ce = cudaFuncSetAttribute(gemm_skinny_kernel<NT, OutT>,
+                                              cudaFuncAttributeMaxDynamicSharedMemorySize, kTileBytes);
+        if (ce != cudaSuccess) return (int)ce;
+        configured = true;
+    }
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = ranks;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_skinny_kernel<NT, OutT>, X, ldx, W, ldw, C, ldc, M, N, K, k_slice);
+    if (e != cudaSuccess) return (int)e;
+    return launch_status();
 }
 
 template <int NT>
 int launch(const bf16* X, int ldx, const bf16* W, int ldw, void* C, int ldc, int out_f32,
            int M, int N, int K, cudaStream_t stream) {
-    const int blocks = (N + 15) / 16;
-    if (out_f32)
-        gemm_skinny_kernel<NT, float><<<blocks, kWarps * 32, 0, stream>>>(X, ldx, W, ldw, (float*)C, ldc, M, N, K);
-    else
-        gemm_skinny_kernel<NT, bf16><<<blocks, kWarps * 32, 0, stream>>>(X, ldx, W, ldw, (bf16*)C, ldc, M, N, K);
-    return launch_status();
+    if (out_f32) return launch_typed<NT, float>(X, ldx, W, ldw, (float*)C, ldc, M, N, K, stream);
+    return launch_typed<NT, bf16>(X, ldx, W, ldw, (bf16*)C, ldc, M, N, K, stream);
 }
 }  // namespace
+
+// 0, or 1 if a kernel of this file ever gave up waiting for its copies (reading
+// it synchronises with the device).
+GTG_API int gtg_gemm_bf16_skinny_status() {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_status, sizeof(int)) != cudaSuccess) return -1;
+    return v;
+}
 
 // Rows (tokens) this kernel takes.
 GTG_API int gtg_gemm_bf16_skinny_max_rows() { return 64; }
@@ -114,6 +242,7 @@ GTG_API int gtg_gemm_bf16_skinny(const void* X, int ldx, const void* W, int ldw,
     if (K <= 0 || ldx < K || ldw < K || ldc < N) return kErrBadArgument;
     if (M > 64) return kErrUnsupported;
     if (K % 8 || ldx % 8 || ldw % 8 || ((uintptr_t)X % 16) || ((uintptr_t)W % 16)) return kErrUnsupported;
+    if ((N + 15) / 16 > 0x7fffffff / 16) return kErrUnsupported;
     const bf16* x = (const bf16*)X;
     const bf16* w = (const bf16*)W;
     if (M <= 8) return launch<1>(x, ldx, w, ldw, C, ldc, out_f32, M, N, K, stream);

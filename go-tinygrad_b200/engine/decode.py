@@ -70,7 +70,7 @@ class DecodeBatch:
         return StepContext(rt=self.model.rt, n_tokens=self.B, n_seqs=self.B, tokens=self.tokens,
                            positions=self.positions, token_seq=self.token_seq, cu_seqlens=self.cu,
                            slots=self.slot_ids, start_pos=self.positions, max_q_len=1,
-                           max_kv_len=0, is_decode=True)
+                           max_kv_len=max(self.cache.length(s) for s in self.slots) + 1, is_decode=True)
 
     def _forward(self) -> None:
         ctx = self._context()

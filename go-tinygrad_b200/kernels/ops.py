@@ -30,6 +30,7 @@ _SIGNATURES = {
     "gtg_gemm_f32": ("gemm_f32", [_P, _I, _P, _I, _P, _I, _I, _I, _I, _P]),
     "gtg_gemm_bf16_mma": ("gemm_bf16_mma", [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _P]),
     "gtg_gemm_bf16_skinny": ("gemm_bf16_skinny", [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _P]),
+    "gtg_gemm_bf16_skinny_status": ("gemm_bf16_skinny", []),
     "gtg_attention_simple": ("attention_simple", [_I, _P, _I, _P, _I, _P, _P, _L, _P, _I, _P, _P, _P,
                                                   _I, _I, _I, _I, _F, _I, _P]),
     "gtg_attention_bf16_supports": ("attention_bf16", [_I]),
@@ -222,6 +223,12 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, kind: str = "aut
         _need(M <= SKINNY_MAX_ROWS, f"linear: the weight-streaming kernel takes at most {SKINNY_MAX_ROWS} rows")
     _check(_fn(symbol)(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0),
                        1 if out.dtype == torch.float32 else 0, M, N, K, _stream()), "linear(bfloat16)")
+
+
+def bounded_wait_failures() -> int:
+    """Non-zero if a kernel ever gave up a bounded wait on its own asynchronous
+    copies (it then returned without a result).  Reading it synchronises."""
+    return int(_fn("gtg_gemm_bf16_skinny_status")())
 
 
 # ----------------------------------------------------------------------- attention

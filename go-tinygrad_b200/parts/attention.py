@@ -25,7 +25,7 @@ from ..kernels import ops
 from ..weights.binder import WeightSpec
 from .base import Mixer, Runtime, StepContext, build_part, register_part
 
-_TARGET_CTAS = 2 * 148      # decode attention: fill the SMs about twice over
+_SMS = 148                  # streaming multiprocessors of a B200
 
 
 @register_part("mixer", "gqa_attention")
@@ -70,8 +70,26 @@ class GQAttention(Mixer):
         self.position.load(tensors, rt)
 
     def _decode_splits(self, ctx: StepContext) -> int:
-        per_split_one = ctx.n_seqs * self.n_kv * ((self.n_heads // self.n_kv + 15) // 16)
-        return max(1, min(32, (_TARGET_CTAS + per_split_one - 1) // per_split_one))
+        """Into how many thread blocks the keys of one (sequence, key/value head)
+        are split.  Blocks run in waves of `slots` (what the GPU holds at once):
+        a count just above a whole number of waves leaves the last wave nearly
+        empty, and a split of very few pages pays its fixed cost (query load,
+        merge, partial write) for little work.  The choice depends on the batch
+        and on the longest sequence only, never on the data."""
+        base = ctx.n_seqs * self.n_kv * ((self.n_heads // self.n_kv + 15) // 16)
+        dp = 16 if self.head_dim <= 16 else 32 if self.head_dim <= 32 else 64 if self.head_dim <= 64 else 128
+        smem = 16 * dp * 2 + 4 * 2 * 64 * dp * 2 + 1024
+        slots = _SMS * max(1, min(8, (227 * 1024) // smem))
+        pages = max(1, (max(ctx.max_kv_len, 1) + 63) // 64)
+        best, best_score = 1, -1.0
+        for s in range(1, min(64, pages) + 1):
+            blocks = base * s
+            waves = -(-blocks // slots)
+            per_split = -(-pages // s)
+            score = blocks / (waves * slots) * per_split / (per_split + 1.0)
+            if score > best_score + 1e-9:
+                best, best_score = s, score
+        return best
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheHandle) -> torch.Tensor:
         rt = ctx.rt

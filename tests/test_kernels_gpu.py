@@ -227,6 +227,22 @@ def test_linear_strided_operands():
     assert float(outb[:, :10].abs().sum()) == 0 and float(outb[:, 60:].abs().sum()) == 0
 
 
+@pytest.mark.parametrize("M,N,K", [(1, 2048, 8192), (8, 2048, 2048), (3, 40, 14336), (16, 100, 20000),
+                                   (2, 16, 32768 + 40)])
+def test_linear_skinny_long_rows_split_over_a_cluster(M, N, K):
+    """Inner sizes beyond one pass: 2, 4 or 8 CTAs share a row, and beyond that a
+    CTA makes several passes."""
+    x, w = rnd(M, K, dtype=torch.bfloat16, seed=1), rnd(N, K, dtype=torch.bfloat16, seed=2)
+    out = torch.empty(M, N, dtype=torch.float32, device=DEV)
+    ops.linear(x, w, out, kind="skinny")
+    want = (x.double() @ w.double().T).float()
+    torch.testing.assert_close(out, want, rtol=1e-4, atol=2e-3 * math.sqrt(K / 64))
+    again = torch.empty_like(out)
+    ops.linear(x, w, again, kind="skinny")
+    assert torch.equal(out, again)                    # fixed summation order
+    assert ops.bounded_wait_failures() == 0
+
+
 def test_linear_refuses_unaligned_inner_size():
     x, w = rnd(4, 12, dtype=torch.bfloat16), rnd(5, 12, dtype=torch.bfloat16)
     with pytest.raises(ops.KernelError, match="multiples of 8"):
