@@ -217,9 +217,157 @@ int launch_typed(const bf16* X, int ldx, const bf16* W, int ldw, OutT* C, int ld
     return launch_status();
 }
 
+// ---------------------------------------------------------------- persistent form
+// For M <= 16 and K <= 16384.  The grid is one cluster-row of CTAs per SM-sized
+// share of the GPU; CTA (c, rank) walks the row tiles c, c+G, c+2G, ... of its
+// slice of k with two staged tiles: while tile i is multiplied, reduced and
+// stored, the sixteen bulk copies of tile i+1 are already in flight.  The
+// activations of the slice are the same for every row tile, so each thread loads
+// its fragments of X once, into registers, before the loop.
+template <int NT, typename OutT>
+__global__ void __launch_bounds__(kWarps * 32, 1)
+gemm_stream_kernel(const bf16* __restrict__ X, int ldx, const bf16* __restrict__ W, int ldw,
+                   OutT* __restrict__ C, int ldc, int M, int N, int K, int k_slice) {
+    extern __shared__ __align__(128) unsigned char tiles[];     // two tiles of 16 rows, kRowStride apart
+    __shared__ float red[kWarps][16][NT * 8 + 1];               // later reused for the cluster's partial sums
+    __shared__ __align__(8) unsigned long long bar_storage[2];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int rank = blockIdx.y, n_ranks = gridDim.y;
+    const int k_begin = rank * k_slice, k_len = min(K, k_begin + k_slice) - k_begin;   // one pass: k_len <= kPassK
+    const int row_tiles = (N + 15) / 16;
+    const uint32_t bar0 = smem_u32(&bar_storage[0]), tile0 = smem_u32(tiles);
+    if (threadIdx.x == 0) { mbar_init(bar0, 1); mbar_init(bar0 + 8, 1); }
+    __syncthreads();
+
+    auto issue = [&](int tile, int stage) {                     // thread 0 only
+        const uint32_t bar = bar0 + 8 * stage, dst = tile0 + stage * kTileBytes;
+        mbar_expect_tx(bar, 16u * (uint32_t)k_len * 2u);
+        for (int r = 0; r < 16; ++r)                            // rows beyond N repeat the last one; dropped at the store
+            bulk_copy(dst + r * kRowStride, W + (size_t)min(tile * 16 + r, N - 1) * ldw + k_begin,
+                      (uint32_t)k_len * 2u, bar);
+    };
+    if (threadIdx.x == 0 && (int)blockIdx.x < row_tiles) issue(blockIdx.x, 0);
+
+    // this thread's fragments of the activations: 8 k blocks x NT token tiles
+    uint4 xf[kBlocksPerWarp][NT];
+    bool ok[kBlocksPerWarp];
+#pragma unroll
+    for (int u = 0; u < kBlocksPerWarp; ++u) {
+        const int kl = (warp + u * kWarps) * 32 + t * 8;
+        ok[u] = kl < k_len;
+#pragma unroll
+        for (int j = 0; j < NT; ++j)
+            xf[u][j] = ok[u] ? ld_cached16(X + (size_t)min(j * 8 + g, M - 1) * ldx + k_begin + kl)
+                             : make_uint4(0, 0, 0, 0);
+    }
+
+    cg::cluster_group cluster = cg::this_cluster();
+    uint32_t phases = 0;                                        // bit s: parity of stage s
+    bool failed = false;
+    for (int tile = blockIdx.x, it = 0; tile < row_tiles; tile += gridDim.x, ++it) {
+        const int stage = it & 1;
+        if (threadIdx.x == 0 && tile + (int)gridDim.x < row_tiles) issue(tile + gridDim.x, stage ^ 1);
+        if (!mbar_wait(bar0 + 8 * stage, (phases >> stage) & 1u)) failed = true;   // keep going: peers wait at the barriers below
+        phases ^= 1u << stage;
+        const unsigned char* tl = tiles + stage * kTileBytes;
+        float acc[NT][4];
+#pragma unroll
+        for (int j = 0; j < NT; ++j) { acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f; }
+#pragma unroll
+        for (int u = 0; u < kBlocksPerWarp; ++u) {
+            const int kl = (warp + u * kWarps) * 32 + t * 8;
+            uint4 wa = make_uint4(0, 0, 0, 0), wb = wa;
+            if (ok[u] && !failed) {
+                wa = *reinterpret_cast<const uint4*>(tl + g * kRowStride + kl * 2);
+                wb = *reinterpret_cast<const uint4*>(tl + (g + 8) * kRowStride + kl * 2);
+            }
+            const uint32_t a_lo[4] = {wa.x, wb.x, wa.y, wb.y};
+            const uint32_t a_hi[4] = {wa.z, wb.z, wa.w, wb.w};
+#pragma unroll
+            for (int j = 0; j < NT; ++j) {
+                mma_bf16_16816(acc[j], a_lo, xf[u][j].x, xf[u][j].y);
+                mma_bf16_16816(acc[j], a_hi, xf[u][j].z, xf[u][j].w);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+            red[warp][g][j * 8 + t * 2] = acc[j][0];
+            red[warp][g][j * 8 + t * 2 + 1] = acc[j][1];
+            red[warp][g + 8][j * 8 + t * 2] = acc[j][2];
+            red[warp][g + 8][j * 8 + t * 2 + 1] = acc[j][3];
+        }
+        __syncthreads();
+        // 16 features x NT*8 tokens: at most one sum per thread (NT <= 2)
+        const int idx = threadIdx.x, m = idx >> 4, r = idx & 15;
+        const bool mine_valid = idx < 16 * NT * 8;
+        float mine = 0.f;
+        if (mine_valid) {
+#pragma unroll
+            for (int w = 0; w < kWarps; ++w) mine += red[w][r][m];
+        }
+        if (n_ranks > 1) {
+            cluster.sync();                                       // every rank is done reading its own `red`
+            float* gather = cluster.map_shared_rank(&red[0][0][0], 0);
+            if (mine_valid) gather[rank * 16 * NT * 8 + idx] = mine;
+            cluster.sync();
+            if (rank == 0 && mine_valid) {
+                const float* sums = &red[0][0][0];
+                mine = 0.f;
+                for (int c = 0; c < n_ranks; ++c) mine += sums[c * 16 * NT * 8 + idx];
+            }
+        }
+        if (rank == 0 && mine_valid && m < M && tile * 16 + r < N)
+            C[(size_t)m * ldc + tile * 16 + r] = from_f32<OutT>(mine);
+        __syncthreads();                                          // `red` and the stage are free again
+    }
+    if (failed && threadIdx.x == 0) atomicExch(&g_status, 1);
+}
+
+template <int NT, typename OutT>
+int launch_stream(const bf16* X, int ldx, const bf16* W, int ldw, OutT* C, int ldc,
+                  int M, int N, int K, cudaStream_t stream) {
+    int ranks = 1;
+    while (ranks < kMaxCluster && (K + ranks - 1) / ranks > kPassK) ranks *= 2;
+    const int k_slice = (((K + ranks - 1) / ranks) + 31) / 32 * 32;
+    if (k_slice > kPassK) return kErrUnsupported;
+    const int row_tiles = (N + 15) / 16;
+    const int smem = 2 * kTileBytes;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t ce = cudaFuncSetAttribute(gemm_stream_kernel<NT, OutT>,
+                                              cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (ce != cudaSuccess) return (int)ce;
+        configured = true;
+    }
+    int per_rank = 148 / ranks;                 // one CTA per SM
+    if (per_rank < 1) per_rank = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(row_tiles < per_rank ? row_tiles : per_rank, ranks, 1);
+    cfg.blockDim = dim3(kWarps * 32, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = ranks;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_stream_kernel<NT, OutT>, X, ldx, W, ldw, C, ldc, M, N, K, k_slice);
+    if (e != cudaSuccess) return (int)e;
+    return launch_status();
+}
+
 template <int NT>
 int launch(const bf16* X, int ldx, const bf16* W, int ldw, void* C, int ldc, int out_f32,
            int M, int N, int K, cudaStream_t stream) {
+    if constexpr (NT <= 2) {
+        if (K <= kMaxCluster * kPassK) {
+            if (out_f32) return launch_stream<NT, float>(X, ldx, W, ldw, (float*)C, ldc, M, N, K, stream);
+            return launch_stream<NT, bf16>(X, ldx, W, ldw, (bf16*)C, ldc, M, N, K, stream);
+        }
+    }
     if (out_f32) return launch_typed<NT, float>(X, ldx, W, ldw, (float*)C, ldc, M, N, K, stream);
     return launch_typed<NT, bf16>(X, ldx, W, ldw, (bf16*)C, ldc, M, N, K, stream);
 }

@@ -1,0 +1,276 @@
+// bfloat16 matrix product on the fifth-generation tensor cores:
+//   C[M,N] = A[M,K] . W[N,K]^T,  float accumulation in tensor memory (TMEM),
+// output bfloat16 or float.  Both operands are K-major, W as in the checkpoint.
+//
+// One CTA computes one 128 x 256 tile of C.  Roles by warp:
+//   warps 0-3  epilogue: tcgen05.ld the accumulator (warp w owns TMEM lanes
+//              32w..32w+31 = rows of the tile), convert, store to global
+//   warp 4     producer: one thread issues the TMA loads (cp.async.bulk.tensor,
+//              128-byte swizzle) of the A tile (128 x 64) and the W tile
+//              (256 x 64) of each k block into a four-stage ring
+//   warp 5     allocates TMEM; one thread issues tcgen05.mma (128 x 256 x 16,
+//              four per k block) and releases ring stages with tcgen05.commit
+// Rows and columns beyond M, N and the tail of K are zero-filled by TMA and
+// dropped at the store, so any M and N work; K must be a multiple of 8 (the
+// 16-byte row pitch TMA needs).
+//
+// Every wait on an mbarrier is bounded.  A wait that gives up sets a flag in
+// shared memory that makes all roles fall through to the common exit (where TMEM
+// is released) and records it in a status word the host can read
+// (gtg_gemm_bf16_tcgen05_status).  No cluster multicast is used anywhere.
+#include "common.cuh"
+#include <cuda.h>
+
+namespace {
+constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
+constexpr int kThreads = 192;
+constexpr int kABytes = BM * BK * 2, kBBytes = BN * BK * 2, kStageBytes = kABytes + kBBytes;
+constexpr int kTmemCols = 256;
+constexpr unsigned kSpinLimit = 1u << 22;
+constexpr int kSmemBytes = STAGES * kStageBytes + 1024 /* alignment slack */ + 256 /* barriers */;
+
+__device__ int g_status = 0;
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+// Polls until the phase with `parity` completes, the abort flag is raised, or the limit is hit.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    for (unsigned i = 0; i < kSpinLimit; ++i) {
+        uint32_t done;
+        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+                     "selp.u32 %0, 1, 0, p;\n}\n" : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+        if (done) return true;
+        if ((i & 1023u) == 1023u && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    atomicExch(&g_status, 1);
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
+}
+// Shared-memory operand descriptor: K-major tile whose rows are 128 bytes (64
+// bfloat16), 128-byte swizzle, 8-row groups 1024 bytes apart, descriptor version 1.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3FFFFu) >> 4);             // start address
+    d |= (uint64_t)1 << 16;                              // leading byte offset (unused with swizzle)
+    d |= (uint64_t)(1024 >> 4) << 32;                    // stride byte offset
+    d |= (uint64_t)1 << 46;                              // version
+    d |= (uint64_t)2 << 61;                              // SWIZZLE_128B
+    return d;
+}
+// Instruction descriptor of kind::f16: float accumulator, bfloat16 A and B, both K-major.
+__host__ __device__ constexpr uint32_t umma_idesc(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+                 ::"r"(tmem_d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t addr, uint32_t* r) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+                 "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(addr));
+}
+
+template <typename OutT> __device__ __forceinline__ void store_chunk(OutT* dst, const uint32_t* v, int n_valid, bool vec_ok);
+template <> __device__ __forceinline__ void store_chunk<float>(float* dst, const uint32_t* v, int n_valid, bool vec_ok) {
+    if (vec_ok && n_valid == 32) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            reinterpret_cast<uint4*>(dst)[i] = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+    } else {
+        for (int i = 0; i < n_valid; ++i) dst[i] = __uint_as_float(v[i]);
+    }
+}
+template <> __device__ __forceinline__ void store_chunk<bf16>(bf16* dst, const uint32_t* v, int n_valid, bool vec_ok) {
+    if (vec_ok && n_valid == 32) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            uint32_t p[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[8 * i + 2 * j]), __uint_as_float(v[8 * i + 2 * j + 1]));
+                p[j] = *reinterpret_cast<uint32_t*>(&h);
+            }
+            reinterpret_cast<uint4*>(dst)[i] = make_uint4(p[0], p[1], p[2], p[3]);
+        }
+    } else {
+        for (int i = 0; i < n_valid; ++i) dst[i] = __float2bfloat16_rn(__uint_as_float(v[i]));
+    }
+}
+
+template <typename OutT>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                    OutT* __restrict__ C, int ldc, int M, int N, int K) {
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t base = (smem_addr(smem_raw) + 1023u) & ~1023u;        // tiles need 1024-byte alignment
+    unsigned char* aligned = smem_raw + (base - smem_addr(smem_raw));
+    const uint32_t bars = base + STAGES * kStageBytes;                   // full[4], empty[4], tmem_full
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(aligned + STAGES * kStageBytes + 128);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(aligned + STAGES * kStageBytes + 136);
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
+    const uint32_t tmem_full_bar = bars + 8u * (2 * STAGES);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    const int n_kb = (K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        mbar_init(tmem_full_bar, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::);
+    }
+    if (warp == 5) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n"
+                     ::"r"(smem_addr(tmem_holder)), "r"(kTmemCols));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::);
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::);
+    const uint32_t tmem_base = *tmem_holder;
+
+    if (warp == 4) {
+        // ------------------------------------------------------------ producer
+        if (lane == 0) {
+            for (int kb = 0; kb < n_kb; ++kb) {
+                const int s = kb % STAGES;
+                const uint32_t round = kb / STAGES;
+                if (!mbar_wait(empty_bar(s), (round & 1u) ^ 1u, abort_flag)) break;   // passes at once in round 0
+                mbar_expect_tx(full_bar(s), kStageBytes);
+                tma_load_2d(base + s * kStageBytes, &map_a, kb * BK, m0, full_bar(s));
+                tma_load_2d(base + s * kStageBytes + kABytes, &map_w, kb * BK, n0, full_bar(s));
+            }
+        }
+    } else if (warp == 5) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc(BM, BN);
+            bool ok = true;
+            for (int kb = 0; kb < n_kb && ok; ++kb) {
+                const int s = kb % STAGES;
+                const uint32_t round = kb / STAGES;
+                ok = mbar_wait(full_bar(s), round & 1u, abort_flag);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::);
+                const uint64_t da = umma_desc(base + s * kStageBytes);
+                const uint64_t db = umma_desc(base + s * kStageBytes + kABytes);
+#pragma unroll
+                for (int j = 0; j < BK / 16; ++j)           // 32 bytes (16 values of k) further per step
+                    umma(tmem_base, da + 2 * j, db + 2 * j, idesc, (kb > 0 || j > 0) ? 1u : 0u);
+                umma_commit(empty_bar(s));                  // the stage is free once these MMAs have read it
+            }
+            umma_commit(tmem_full_bar);                     // the accumulator is complete
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue
+        const bool ready = mbar_wait(tmem_full_bar, 0, abort_flag);
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::);
+        if (ready) {
+            const int row = m0 + warp * 32 + lane;
+            const bool vec_ok = (ldc % 8 == 0) && ((reinterpret_cast<uintptr_t>(C) & 15) == 0) && (n0 % 8 == 0);
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t v[32];
+                tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(c * 32), v);
+                asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+                const int col = n0 + c * 32;
+                if (row < M && col < N)
+                    store_chunk<OutT>(C + (size_t)row * ldc + col, v, min(32, N - col), vec_ok);
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::);
+    __syncthreads();
+    if (warp == 5) {
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::);
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(kTmemCols));
+    }
+}
+
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_fn() {
+    static EncodeTiled fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiled)p;
+    }
+    return fn;
+}
+
+// A [rows, K] bfloat16 matrix with `ld` elements between rows, read in boxes of 64 x box_rows.
+int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int ld, int box_rows) {
+    EncodeTiled enc = encode_fn();
+    if (!enc) return kErrUnsupported;
+    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : kErrBadArgument;
+}
+}  // namespace
+
+// 0, or 1 if a kernel of this file ever gave up a bounded wait (reading it
+// synchronises with the device).
+GTG_API int gtg_gemm_bf16_tcgen05_status() {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_status, sizeof(int)) != cudaSuccess) return -1;
+    return v;
+}
+
+GTG_API int gtg_gemm_bf16_tcgen05(const void* A, int lda, const void* W, int ldw, void* C, int ldc,
+                                  int out_f32, int M, int N, int K, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0 || lda < K || ldw < K || ldc < N) return kErrBadArgument;
+    if (K % 8 || lda % 8 || ldw % 8 || ((uintptr_t)A % 16) || ((uintptr_t)W % 16)) return kErrUnsupported;
+    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+    if (grid.y > 65535) return kErrUnsupported;
+    CUtensorMap map_a, map_w;
+    int st = make_map(&map_a, A, M, K, lda, BM);
+    if (st != 0) return st;
+    st = make_map(&map_w, W, N, K, ldw, BN);
+    if (st != 0) return st;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        if (e != cudaSuccess) return (int)e;
+        e = cudaFuncSetAttribute(gemm_tcgen05_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    if (out_f32)
+        gemm_tcgen05_kernel<float><<<grid, kThreads, kSmemBytes, stream>>>(map_a, map_w, (float*)C, ldc, M, N, K);
+    else
+        gemm_tcgen05_kernel<bf16><<<grid, kThreads, kSmemBytes, stream>>>(map_a, map_w, (bf16*)C, ldc, M, N, K);
+    return launch_status();
+}

@@ -31,6 +31,8 @@ _SIGNATURES = {
     "gtg_gemm_bf16_mma": ("gemm_bf16_mma", [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _P]),
     "gtg_gemm_bf16_skinny": ("gemm_bf16_skinny", [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _P]),
     "gtg_gemm_bf16_skinny_status": ("gemm_bf16_skinny", []),
+    "gtg_gemm_bf16_tcgen05": ("gemm_bf16_tcgen05", [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _P]),
+    "gtg_gemm_bf16_tcgen05_status": ("gemm_bf16_tcgen05", []),
     "gtg_attention_simple": ("attention_simple", [_I, _P, _I, _P, _I, _P, _P, _L, _P, _I, _P, _P, _P,
                                                   _I, _I, _I, _I, _F, _I, _P]),
     "gtg_attention_bf16_supports": ("attention_bf16", [_I]),
@@ -197,6 +199,7 @@ def advance(tokens: torch.Tensor, positions: torch.Tensor, steps: torch.Tensor,
 
 # ---------------------------------------------------------------- matrix products
 SKINNY_MAX_ROWS = 64
+TILED_KIND = "tcgen05"        # what "auto" uses beyond SKINNY_MAX_ROWS rows
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, kind: str = "auto") -> None:
@@ -218,7 +221,11 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, kind: str = "aut
     _need(K % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0,
           f"linear(bfloat16): the inner size {K} and the row strides must be multiples of 8")
     # few rows (a decode step): stream the weights once; many rows: tiled product
-    symbol = "gtg_gemm_bf16_skinny" if M <= SKINNY_MAX_ROWS and kind != "tiled" else "gtg_gemm_bf16_mma"
+    if kind == "auto":
+        kind = "skinny" if M <= SKINNY_MAX_ROWS else TILED_KIND
+    symbol = {"skinny": "gtg_gemm_bf16_skinny", "tiled": "gtg_gemm_bf16_mma",
+              "tcgen05": "gtg_gemm_bf16_tcgen05"}.get(kind)
+    _need(symbol is not None, f"linear: unknown kind {kind!r}")
     if kind == "skinny":
         _need(M <= SKINNY_MAX_ROWS, f"linear: the weight-streaming kernel takes at most {SKINNY_MAX_ROWS} rows")
     _check(_fn(symbol)(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0),
@@ -228,7 +235,11 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, kind: str = "aut
 def bounded_wait_failures() -> int:
     """Non-zero if a kernel ever gave up a bounded wait on its own asynchronous
     copies (it then returned without a result).  Reading it synchronises."""
-    return int(_fn("gtg_gemm_bf16_skinny_status")())
+    total = 0
+    for symbol in ("gtg_gemm_bf16_skinny_status", "gtg_gemm_bf16_tcgen05_status"):
+        if _SIGNATURES[symbol][0] in build._LOADED:        # only libraries that have run can have failed
+            total += int(_fn(symbol)())
+    return total
 
 
 # ----------------------------------------------------------------------- attention

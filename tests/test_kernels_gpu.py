@@ -198,7 +198,7 @@ def test_linear_float32_does_not_depend_on_the_batch():
 
 
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
-@pytest.mark.parametrize("kind", ["skinny", "tiled"])
+@pytest.mark.parametrize("kind", ["skinny", "tiled", "tcgen05"])
 @pytest.mark.parametrize("M,N,K", [(1, 17, 8), (5, 96, 264), (64, 391, 96), (130, 130, 40),
                                    (257, 1000, 2048), (3, 2048, 8192), (8, 6144, 2048),
                                    (300, 144, 96), (9, 50, 1000), (17, 33, 72), (40, 1001, 2056),
@@ -214,6 +214,7 @@ def test_linear_bfloat16(out_dtype, kind, M, N, K):
         torch.testing.assert_close(out.float(), want.to(torch.bfloat16).float(), rtol=1.6e-2, atol=1e-2 * math.sqrt(K / 64))
     else:
         torch.testing.assert_close(out, want, rtol=1e-4, atol=2e-3 * math.sqrt(K / 64))
+    assert ops.bounded_wait_failures() == 0
 
 
 def test_linear_strided_operands():
