@@ -69,12 +69,29 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     return false;
 }
 
+// Writes one output of a 16-feature tile; every lane of the warp must call it.
+//   epi == 0: C[m][n0 + r] = s.
+//   epi == 1: SwiGLU over a tile that holds 8 gate features followed by their 8
+//             up features: the thread of gate r < 8 fetches the up value from the
+//             thread of r + 8 and writes silu(gate) * up to C[m][n0/2 + r].
+template <typename OutT>
+__device__ __forceinline__ void store_feature(OutT* C, int ldc, int m, int n0, int r, int M, int N,
+                                              float s, int epi) {
+    if (epi == 0) {
+        if (m < M && n0 + r < N) C[(size_t)m * ldc + n0 + r] = from_f32<OutT>(s);
+        return;
+    }
+    const float up = __shfl_down_sync(0xffffffffu, s, 8);
+    if (r < 8 && m < M && n0 + r + 8 < N)
+        C[(size_t)m * ldc + (n0 >> 1) + r] = from_f32<OutT>(s / (1.0f + expf(-s)) * up);
+}
+
 // grid = (ceil(N/16), S) with clusters of (1, S, 1): blockIdx.y is the CTA's
 // rank in its cluster and the index of its slice [rank*k_slice, +k_slice) of k.
 template <int NT, typename OutT>
 __global__ void __launch_bounds__(kWarps * 32)
 gemm_skinny_kernel(const bf16* __restrict__ X, int ldx, const bf16* __restrict__ W, int ldw,
-                   OutT* __restrict__ C, int ldc, int M, int N, int K, int k_slice) {
+                   OutT* __restrict__ C, int ldc, int M, int N, int K, int k_slice, int epi) {
     extern __shared__ __align__(128) unsigned char tile[];      // 16 rows of W, kRowStride apart
     __shared__ float red[kWarps][16][NT * 8 + 1];        // later reused for the cluster's partial sums
     __shared__ __align__(8) unsigned long long bar_storage;
@@ -141,11 +158,10 @@ gemm_skinny_kernel(const bf16* __restrict__ X, int ldx, const bf16* __restrict__
     if (n_ranks == 1) {
         for (int idx = threadIdx.x; idx < 16 * NT * 8; idx += kWarps * 32) {
             const int m = idx >> 4, r = idx & 15;          // consecutive threads -> consecutive features
-            if (m >= M || n0 + r >= N) continue;
             float s = 0.f;
 #pragma unroll
             for (int w = 0; w < kWarps; ++w) s += red[w][r][m];
-            C[(size_t)m * ldc + n0 + r] = from_f32<OutT>(s);
+            store_feature<OutT>(C, ldc, m, n0, r, M, N, s, epi);
         }
         return;
     }
@@ -179,16 +195,15 @@ gemm_skinny_kernel(const bf16* __restrict__ X, int ldx, const bf16* __restrict__
     const float* sums = &red[0][0][0];
     for (int idx = threadIdx.x; idx < 16 * NT * 8; idx += kWarps * 32) {
         const int m = idx >> 4, r = idx & 15;
-        if (m >= M || n0 + r >= N) continue;
         float s = 0.f;
         for (int c = 0; c < n_ranks; ++c) s += sums[c * 16 * NT * 8 + idx];
-        C[(size_t)m * ldc + n0 + r] = from_f32<OutT>(s);
+        store_feature<OutT>(C, ldc, m, n0, r, M, N, s, epi);
     }
 }
 
 template <int NT, typename OutT>
 int launch_typed(const bf16* X, int ldx, const bf16* W, int ldw, OutT* C, int ldc,
-                 int M, int N, int K, cudaStream_t stream) {
+                 int M, int N, int K, int epi, cudaStream_t stream) {
     // the fewest ranks (a power of two, at most 8) whose slice fits one pass
     int ranks = 1;
     while (ranks < kMaxCluster && (K + ranks - 1) / ranks > kPassK) ranks *= 2;
@@ -212,7 +227,7 @@ int launch_typed(const bf16* X, int ldx, const bf16* W, int ldw, OutT* C, int ld
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_skinny_kernel<NT, OutT>, X, ldx, W, ldw, C, ldc, M, N, K, k_slice);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_skinny_kernel<NT, OutT>, X, ldx, W, ldw, C, ldc, M, N, K, k_slice, epi);
     if (e != cudaSuccess) return (int)e;
     return launch_status();
 }
@@ -227,7 +242,7 @@ int launch_typed(const bf16* X, int ldx, const bf16* W, int ldw, OutT* C, int ld
 template <int NT, typename OutT>
 __global__ void __launch_bounds__(kWarps * 32, 1)
 gemm_stream_kernel(const bf16* __restrict__ X, int ldx, const bf16* __restrict__ W, int ldw,
-                   OutT* __restrict__ C, int ldc, int M, int N, int K, int k_slice) {
+                   OutT* __restrict__ C, int ldc, int M, int N, int K, int k_slice, int epi) {
     extern __shared__ __align__(128) unsigned char tiles[];     // two tiles of 16 rows, kRowStride apart
     __shared__ float red[kWarps][16][NT * 8 + 1];               // later reused for the cluster's partial sums
     __shared__ __align__(8) unsigned long long bar_storage[2];
@@ -317,8 +332,8 @@ gemm_stream_kernel(const bf16* __restrict__ X, int ldx, const bf16* __restrict__
                 for (int c = 0; c < n_ranks; ++c) mine += sums[c * 16 * NT * 8 + idx];
             }
         }
-        if (rank == 0 && mine_valid && m < M && tile * 16 + r < N)
-            C[(size_t)m * ldc + tile * 16 + r] = from_f32<OutT>(mine);
+        if (rank == 0 && mine_valid)                              // uniform per warp: whole warps are valid or not
+            store_feature<OutT>(C, ldc, m, tile * 16, r, M, N, mine, epi);
         __syncthreads();                                          // `red` and the stage are free again
     }
     if (failed && threadIdx.x == 0) atomicExch(&g_status, 1);
@@ -326,7 +341,7 @@ gemm_stream_kernel(const bf16* __restrict__ X, int ldx, const bf16* __restrict__
 
 template <int NT, typename OutT>
 int launch_stream(const bf16* X, int ldx, const bf16* W, int ldw, OutT* C, int ldc,
-                  int M, int N, int K, cudaStream_t stream) {
+                  int M, int N, int K, int epi, cudaStream_t stream) {
     int ranks = 1;
     while (ranks < kMaxCluster && (K + ranks - 1) / ranks > kPassK) ranks *= 2;
     const int k_slice = (((K + ranks - 1) / ranks) + 31) / 32 * 32;
@@ -354,22 +369,22 @@ int launch_stream(const bf16* X, int ldx, const bf16* W, int ldw, OutT* C, int l
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_stream_kernel<NT, OutT>, X, ldx, W, ldw, C, ldc, M, N, K, k_slice);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_stream_kernel<NT, OutT>, X, ldx, W, ldw, C, ldc, M, N, K, k_slice, epi);
     if (e != cudaSuccess) return (int)e;
     return launch_status();
 }
 
 template <int NT>
 int launch(const bf16* X, int ldx, const bf16* W, int ldw, void* C, int ldc, int out_f32,
-           int M, int N, int K, cudaStream_t stream) {
+           int M, int N, int K, int epi, cudaStream_t stream) {
     if constexpr (NT <= 2) {
         if (K <= kMaxCluster * kPassK) {
-            if (out_f32) return launch_stream<NT, float>(X, ldx, W, ldw, (float*)C, ldc, M, N, K, stream);
-            return launch_stream<NT, bf16>(X, ldx, W, ldw, (bf16*)C, ldc, M, N, K, stream);
+            if (out_f32) return launch_stream<NT, float>(X, ldx, W, ldw, (float*)C, ldc, M, N, K, epi, stream);
+            return launch_stream<NT, bf16>(X, ldx, W, ldw, (bf16*)C, ldc, M, N, K, epi, stream);
         }
     }
-    if (out_f32) return launch_typed<NT, float>(X, ldx, W, ldw, (float*)C, ldc, M, N, K, stream);
-    return launch_typed<NT, bf16>(X, ldx, W, ldw, (bf16*)C, ldc, M, N, K, stream);
+    if (out_f32) return launch_typed<NT, float>(X, ldx, W, ldw, (float*)C, ldc, M, N, K, epi, stream);
+    return launch_typed<NT, bf16>(X, ldx, W, ldw, (bf16*)C, ldc, M, N, K, epi, stream);
 }
 }  // namespace
 
@@ -384,17 +399,21 @@ GTG_API int gtg_gemm_bf16_skinny_status() {
 // Rows (tokens) this kernel takes.
 GTG_API int gtg_gemm_bf16_skinny_max_rows() { return 64; }
 
+// epilogue 0: C[M,N] = X W^T.  epilogue 1: W's rows come in blocks of 8 gate
+// features followed by their 8 up features, and C[M,N/2] = silu(gate) * up.
 GTG_API int gtg_gemm_bf16_skinny(const void* X, int ldx, const void* W, int ldw, void* C, int ldc,
-                                 int out_f32, int M, int N, int K, cudaStream_t stream) {
+                                 int out_f32, int M, int N, int K, int epilogue, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
-    if (K <= 0 || ldx < K || ldw < K || ldc < N) return kErrBadArgument;
+    if (epilogue != 0 && epilogue != 1) return kErrBadArgument;
+    if (epilogue == 1 && N % 16 != 0) return kErrUnsupported;
+    if (K <= 0 || ldx < K || ldw < K || ldc < (epilogue ? N / 2 : N)) return kErrBadArgument;
     if (M > 64) return kErrUnsupported;
     if (K % 8 || ldx % 8 || ldw % 8 || ((uintptr_t)X % 16) || ((uintptr_t)W % 16)) return kErrUnsupported;
     if ((N + 15) / 16 > 0x7fffffff / 16) return kErrUnsupported;
     const bf16* x = (const bf16*)X;
     const bf16* w = (const bf16*)W;
-    if (M <= 8) return launch<1>(x, ldx, w, ldw, C, ldc, out_f32, M, N, K, stream);
-    if (M <= 16) return launch<2>(x, ldx, w, ldw, C, ldc, out_f32, M, N, K, stream);
-    if (M <= 32) return launch<4>(x, ldx, w, ldw, C, ldc, out_f32, M, N, K, stream);
-    return launch<8>(x, ldx, w, ldw, C, ldc, out_f32, M, N, K, stream);
+    if (M <= 8) return launch<1>(x, ldx, w, ldw, C, ldc, out_f32, M, N, K, epilogue, stream);
+    if (M <= 16) return launch<2>(x, ldx, w, ldw, C, ldc, out_f32, M, N, K, epilogue, stream);
+    if (M <= 32) return launch<4>(x, ldx, w, ldw, C, ldc, out_f32, M, N, K, epilogue, stream);
+    return launch<8>(x, ldx, w, ldw, C, ldc, out_f32, M, N, K, epilogue, stream);
 }

@@ -120,7 +120,7 @@ template <> __device__ __forceinline__ void store_chunk<bf16>(bf16* dst, const u
 template <typename OutT>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                    OutT* __restrict__ C, int ldc, int M, int N, int K) {
+                    OutT* __restrict__ C, int ldc, int M, int N, int K, int epi) {
     extern __shared__ unsigned char smem_raw[];
     const uint32_t base = (smem_addr(smem_raw) + 1023u) & ~1023u;        // tiles need 1024-byte alignment
     unsigned char* aligned = smem_raw + (base - smem_addr(smem_raw));
@@ -196,8 +196,44 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(c * 32), v);
                 asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
                 const int col = n0 + c * 32;
-                if (row < M && col < N)
+                if (row >= M || col >= N) continue;
+                if (epi == 0) {
                     store_chunk<OutT>(C + (size_t)row * ldc + col, v, min(32, N - col), vec_ok);
+                } else {
+                    // SwiGLU: the 32 columns are two blocks of 8 gate features followed by
+                    // their 8 up features; 16 outputs land at column col/2
+                    uint32_t o[32];
+#pragma unroll
+                    for (int blk = 0; blk < 2; ++blk)
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const float g = __uint_as_float(v[16 * blk + j]), u = __uint_as_float(v[16 * blk + 8 + j]);
+                            o[8 * blk + j] = __float_as_uint(g / (1.0f + expf(-g)) * u);
+                        }
+                    const int n_out = min(16, (N - col) / 2);
+                    OutT* dst = C + (size_t)row * ldc + (col >> 1);
+                    if (vec_ok && n_out == 16) {
+                        if constexpr (sizeof(OutT) == 2) {
+#pragma unroll
+                            for (int i = 0; i < 2; ++i) {
+                                uint32_t p[4];
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(o[8 * i + 2 * j]),
+                                                                             __uint_as_float(o[8 * i + 2 * j + 1]));
+                                    p[j] = *reinterpret_cast<uint32_t*>(&h);
+                                }
+                                reinterpret_cast<uint4*>(dst)[i] = make_uint4(p[0], p[1], p[2], p[3]);
+                            }
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 4; ++i)
+                                reinterpret_cast<uint4*>(dst)[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+                        }
+                    } else {
+                        for (int i = 0; i < n_out; ++i) dst[i] = from_f32<OutT>(__uint_as_float(o[i]));
+                    }
+                }
             }
         }
     }
@@ -248,10 +284,14 @@ GTG_API int gtg_gemm_bf16_tcgen05_status() {
     return v;
 }
 
+// epilogue 0: C[M,N] = A W^T.  epilogue 1: W's rows come in blocks of 8 gate
+// features followed by their 8 up features, and C[M,N/2] = silu(gate) * up.
 GTG_API int gtg_gemm_bf16_tcgen05(const void* A, int lda, const void* W, int ldw, void* C, int ldc,
-                                  int out_f32, int M, int N, int K, cudaStream_t stream) {
+                                  int out_f32, int M, int N, int K, int epilogue, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
-    if (K <= 0 || lda < K || ldw < K || ldc < N) return kErrBadArgument;
+    if (epilogue != 0 && epilogue != 1) return kErrBadArgument;
+    if (epilogue == 1 && N % 16 != 0) return kErrUnsupported;
+    if (K <= 0 || lda < K || ldw < K || ldc < (epilogue ? N / 2 : N)) return kErrBadArgument;
     if (K % 8 || lda % 8 || ldw % 8 || ((uintptr_t)A % 16) || ((uintptr_t)W % 16)) return kErrUnsupported;
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
     if (grid.y > 65535) return kErrUnsupported;
@@ -269,8 +309,8 @@ GTG_API int gtg_gemm_bf16_tcgen05(const void* A, int lda, const void* W, int ldw
         configured = true;
     }
     if (out_f32)
-        gemm_tcgen05_kernel<float><<<grid, kThreads, kSmemBytes, stream>>>(map_a, map_w, (float*)C, ldc, M, N, K);
+        gemm_tcgen05_kernel<float><<<grid, kThreads, kSmemBytes, stream>>>(map_a, map_w, (float*)C, ldc, M, N, K, epilogue);
     else
-        gemm_tcgen05_kernel<bf16><<<grid, kThreads, kSmemBytes, stream>>>(map_a, map_w, (bf16*)C, ldc, M, N, K);
+        gemm_tcgen05_kernel<bf16><<<grid, kThreads, kSmemBytes, stream>>>(map_a, map_w, (bf16*)C, ldc, M, N, K, epilogue);
     return launch_status();
 }

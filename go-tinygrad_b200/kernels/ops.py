@@ -29,9 +29,9 @@ _SIGNATURES = {
     "gtg_advance": ("elementwise", [_P, _P, _P, _P, _I, _P]),
     "gtg_gemm_f32": ("gemm_f32", [_P, _I, _P, _I, _P, _I, _I, _I, _I, _P]),
     "gtg_gemm_bf16_mma": ("gemm_bf16_mma", [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _P]),
-    "gtg_gemm_bf16_skinny": ("gemm_bf16_skinny", [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _P]),
+    "gtg_gemm_bf16_skinny": ("gemm_bf16_skinny", [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _P]),
     "gtg_gemm_bf16_skinny_status": ("gemm_bf16_skinny", []),
-    "gtg_gemm_bf16_tcgen05": ("gemm_bf16_tcgen05", [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _P]),
+    "gtg_gemm_bf16_tcgen05": ("gemm_bf16_tcgen05", [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _P]),
     "gtg_gemm_bf16_tcgen05_status": ("gemm_bf16_tcgen05", []),
     "gtg_attention_simple": ("attention_simple", [_I, _P, _I, _P, _I, _P, _P, _L, _P, _I, _P, _P, _P,
                                                   _I, _I, _I, _I, _F, _I, _P]),
@@ -202,16 +202,32 @@ SKINNY_MAX_ROWS = 64
 TILED_KIND = "tcgen05"        # what "auto" uses beyond SKINNY_MAX_ROWS rows
 
 
-def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, kind: str = "auto") -> None:
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """The weight layout of the fused SwiGLU epilogue: rows in blocks of 8 gate
+    features followed by the same 8 up features.  gate, up: [I, K] with I % 8 == 0."""
+    i, k = gate.shape
+    _need(up.shape == gate.shape and i % 8 == 0, "interleave_gate_up: equal shapes with a multiple of 8 rows")
+    return torch.stack([gate.reshape(i // 8, 8, k), up.reshape(i // 8, 8, k)], dim=1).reshape(2 * i, k).contiguous()
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, kind: str = "auto",
+           epilogue: str = "none") -> None:
     """out[M,N] = x[M,K] . w[N,K]^T.  float32 operands take the true 32-bit
     kernel; bfloat16 operands accumulate in float and write bfloat16 or float32.
     `kind` picks the bfloat16 kernel: "auto" (by the number of rows), "skinny"
-    (weight streaming, up to 64 rows) or "tiled"."""
+    (weight streaming, up to 64 rows), "tcgen05" (TMA + tensor memory) or "tiled"
+    (warp-level MMA).  epilogue="swiglu" (bfloat16, not "tiled"): w is laid out by
+    `interleave_gate_up` and out[M, N/2] = silu(gate) * up, computed from the
+    float accumulators."""
     _rows2d(x, "linear: x"); _rows2d(w, "linear: w"); _rows2d(out, "linear: out")
     M, K = x.shape
     N = w.shape[0]
-    _need(w.shape[1] == K and tuple(out.shape) == (M, N), f"linear: shapes {tuple(x.shape)} x {tuple(w.shape)} -> {tuple(out.shape)}")
+    _need(epilogue in ("none", "swiglu"), f"linear: unknown epilogue {epilogue!r}")
+    n_out = N // 2 if epilogue == "swiglu" else N
+    _need(w.shape[1] == K and tuple(out.shape) == (M, n_out),
+          f"linear: shapes {tuple(x.shape)} x {tuple(w.shape)} -> {tuple(out.shape)} (epilogue {epilogue})")
     if x.dtype == torch.float32:
+        _need(epilogue == "none", "linear: the float32 product has no fused epilogue")
         _need(w.dtype == torch.float32 and out.dtype == torch.float32, "linear: float32 x needs float32 w and out")
         _check(_fn("gtg_gemm_f32")(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0),
                                    M, N, K, _stream()), "linear(float32)")
@@ -228,8 +244,17 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, kind: str = "aut
     _need(symbol is not None, f"linear: unknown kind {kind!r}")
     if kind == "skinny":
         _need(M <= SKINNY_MAX_ROWS, f"linear: the weight-streaming kernel takes at most {SKINNY_MAX_ROWS} rows")
-    _check(_fn(symbol)(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0),
-                       1 if out.dtype == torch.float32 else 0, M, N, K, _stream()), "linear(bfloat16)")
+    out_f32 = 1 if out.dtype == torch.float32 else 0
+    if kind == "tiled":
+        _need(epilogue == "none", "linear: the warp-level kernel has no fused epilogue")
+        code = _fn(symbol)(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0),
+                           out_f32, M, N, K, _stream())
+    else:
+        if epilogue == "swiglu":
+            _need(N % 16 == 0, f"linear: the fused SwiGLU needs a multiple of 16 rows of w, got {N}")
+        code = _fn(symbol)(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0),
+                           out_f32, M, N, K, 1 if epilogue == "swiglu" else 0, _stream())
+    _check(code, "linear(bfloat16)")
 
 
 def bounded_wait_failures() -> int:

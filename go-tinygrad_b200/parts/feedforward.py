@@ -32,17 +32,27 @@ class SwiGLU(FeedForward):
                 WeightSpec(self.names["down"], (self.hidden, self.inter))]
 
     def load(self, tensors: Mapping[str, torch.Tensor], rt: Runtime) -> None:
-        self.w_gate_up = rt.matrix(torch.cat([tensors[self.names["gate"]].to(rt.dtype),
-                                              tensors[self.names["up"]].to(rt.dtype)], dim=0))
+        gate, up = tensors[self.names["gate"]].to(rt.dtype), tensors[self.names["up"]].to(rt.dtype)
+        # bfloat16: gate and up rows interleaved in blocks of 8 so that the product's
+        # epilogue can apply silu(gate) * up to its float accumulators and write the
+        # activation directly; float32: gate rows then up rows, and a kernel of its own
+        self.fused = rt.dtype == torch.bfloat16 and self.inter % 8 == 0
+        if self.fused:
+            self.w_gate_up = rt.matrix(ops.interleave_gate_up(gate, up))
+        else:
+            self.w_gate_up = rt.matrix(torch.cat([gate, up], dim=0))
         self.w_down = rt.matrix(tensors[self.names["down"]])
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         rt = ctx.rt
         n = x.shape[0]
-        gate_up = rt.empty(n, 2 * self.inter)
-        ops.linear(x, self.w_gate_up, gate_up)
         act = rt.empty(n, self.inter)
-        ops.swiglu(gate_up, act)
+        if self.fused:
+            ops.linear(x, self.w_gate_up, act, epilogue="swiglu")
+        else:
+            gate_up = rt.empty(n, 2 * self.inter)
+            ops.linear(x, self.w_gate_up, gate_up)
+            ops.swiglu(gate_up, act)
         out = rt.empty(n, self.hidden)
         ops.linear(act, self.w_down, out)
         return out

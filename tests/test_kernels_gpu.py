@@ -244,6 +244,26 @@ def test_linear_skinny_long_rows_split_over_a_cluster(M, N, K):
     assert ops.bounded_wait_failures() == 0
 
 
+@pytest.mark.parametrize("kind", ["skinny", "tcgen05"])
+@pytest.mark.parametrize("M,I,K", [(1, 8, 96), (8, 264, 96), (16, 1000, 2048), (33, 24, 8192), (64, 264, 264),
+                                   (200, 264, 96), (130, 1000, 2048)])
+def test_linear_with_fused_swiglu(kind, M, I, K):
+    """The product over interleaved gate/up rows writes silu(gate) * up directly."""
+    if kind == "skinny" and M > ops.SKINNY_MAX_ROWS:
+        pytest.skip("more rows than the weight-streaming kernel takes")
+    x = rnd(M, K, dtype=torch.bfloat16, seed=1, scale=0.5)
+    gate, up = rnd(I, K, dtype=torch.bfloat16, seed=2, scale=0.2), rnd(I, K, dtype=torch.bfloat16, seed=3, scale=0.2)
+    w = ops.interleave_gate_up(gate, up)
+    assert w.shape == (2 * I, K) and torch.equal(w[8:16], up[:8]) and torch.equal(w[16:24], gate[8:16]) if I >= 16 \
+        else torch.equal(w[8:16], up[:8])
+    out = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.linear(x, w, out, kind=kind, epilogue="swiglu")
+    g, u = x.double() @ gate.double().T, x.double() @ up.double().T
+    want = (g / (1 + torch.exp(-g)) * u).float()
+    torch.testing.assert_close(out.float(), want.to(torch.bfloat16).float(), rtol=2e-2, atol=2e-2 * math.sqrt(K / 64))
+    assert ops.bounded_wait_failures() == 0
+
+
 def test_linear_refuses_unaligned_inner_size():
     x, w = rnd(4, 12, dtype=torch.bfloat16), rnd(5, 12, dtype=torch.bfloat16)
     with pytest.raises(ops.KernelError, match="multiples of 8"):
