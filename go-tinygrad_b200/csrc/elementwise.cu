@@ -64,10 +64,67 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __rest
         o[i] = from_f32<T>((weight[i] * row[i]) * s);
 }
 
+// The same for bfloat16 rows whose width is a multiple of 8 and at most 8192:
+// every thread owns 8 consecutive channels, moved with 16- and 32-byte accesses
+// and kept in registers between the sum of squares and the scaling.
+__global__ void __launch_bounds__(1024)
+add_rmsnorm_bf16_vec_kernel(float* __restrict__ residual, const bf16* __restrict__ pending,
+                            const float* __restrict__ weight, float eps, bf16* __restrict__ out,
+                            const int* __restrict__ rows, int H) {
+    __shared__ float scratch[33];
+    const int i_out = blockIdx.x;
+    const int r = rows ? rows[i_out] : i_out;
+    const int c = threadIdx.x * 8;
+    const bool active = c < H;
+    float x[8];
+    float w[8];
+    float ss = 0.f;
+    if (active) {
+        const float4* wp = reinterpret_cast<const float4*>(weight + c);
+        const float4 w0 = wp[0], w1 = wp[1];
+        w[0] = w0.x; w[1] = w0.y; w[2] = w0.z; w[3] = w0.w; w[4] = w1.x; w[5] = w1.y; w[6] = w1.z; w[7] = w1.w;
+        float4* rp = reinterpret_cast<float4*>(residual + (size_t)r * H + c);
+        const float4 a = rp[0], b = rp[1];
+        x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w; x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+        if (pending) {
+            const uint4 p = *reinterpret_cast<const uint4*>(pending + (size_t)r * H + c);
+            const __nv_bfloat162* ph = reinterpret_cast<const __nv_bfloat162*>(&p);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 f = __bfloat1622float2(ph[j]);
+                x[2 * j] += f.x;
+                x[2 * j + 1] += f.y;
+            }
+            if (!rows) {
+                rp[0] = make_float4(x[0], x[1], x[2], x[3]);
+                rp[1] = make_float4(x[4], x[5], x[6], x[7]);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss += x[j] * x[j];
+    }
+    const float total = block_sum(ss, scratch);
+    const float s = 1.0f / sqrtf(total / (float)H + eps);
+    if (active) {
+        uint4 o;
+        __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            oh[j] = __floats2bfloat162_rn((w[2 * j] * x[2 * j]) * s, (w[2 * j + 1] * x[2 * j + 1]) * s);
+        *reinterpret_cast<uint4*>(out + (size_t)i_out * H + c) = o;
+    }
+}
+
 GTG_API int gtg_add_rmsnorm(int dtype, float* residual, const void* pending, const float* weight,
                             float eps, void* out, const int* rows, int R, int H,
                             cudaStream_t stream) {
     if (R <= 0) return 0;
+    if (dtype == 1 && H % 8 == 0 && H <= 8192 && ((uintptr_t)residual % 16) == 0 && ((uintptr_t)out % 16) == 0 &&
+        ((uintptr_t)weight % 16) == 0 && ((uintptr_t)pending % 16) == 0) {
+        int t = ((H / 8) + 31) / 32 * 32;
+        add_rmsnorm_bf16_vec_kernel<<<R, t, 0, stream>>>(residual, (const bf16*)pending, weight, eps, (bf16*)out, rows, H);
+        return launch_status();
+    }
     int threads = 32;
     while (threads < 1024 && threads * 4 < H) threads *= 2;
     const size_t smem = (size_t)(H + 33) * sizeof(float);
@@ -189,6 +246,57 @@ __global__ void rope_kv_store_kernel(T* __restrict__ qkv, int ld, const float2* 
     }
 }
 
+// The same for bfloat16 with head sizes that are multiples of 16 and 16-byte
+// aligned rows: one thread rotates 8 consecutive pairs with 16-byte accesses.
+__global__ void rope_kv_store_bf16_vec_kernel(bf16* __restrict__ qkv, int ld, const float2* __restrict__ cos_sin,
+                                              int n_heads, int n_kv_store, int hd,
+                                              bf16* __restrict__ kc, bf16* __restrict__ vc, long long page_stride,
+                                              const int* __restrict__ block_table, int table_stride,
+                                              const int* __restrict__ token_seq, const int* __restrict__ slots,
+                                              const int* __restrict__ positions) {
+    const int n = blockIdx.x;
+    const int half = hd >> 1, chunks = half >> 3;
+    const int pos = positions[n];
+    bf16* row = qkv + (size_t)n * ld;
+    size_t cache_off = 0;
+    if (n_kv_store > 0) {
+        const int slot = slots[token_seq[n]];
+        const int page = block_table[(size_t)slot * table_stride + pos / kPageTokens];
+        cache_off = (size_t)page * page_stride + (size_t)(pos % kPageTokens) * hd;
+    }
+    const int items = (n_heads + 2 * n_kv_store) * chunks;
+    for (int it = threadIdx.x; it < items; it += blockDim.x) {
+        const int head = it / chunks, i = (it - head * chunks) * 8;
+        bf16* src = row + head * hd;
+        const uint4 av = *reinterpret_cast<const uint4*>(src + i);
+        const uint4 bv = *reinterpret_cast<const uint4*>(src + i + half);
+        if (head >= n_heads + n_kv_store) {                       // a value head: copy
+            bf16* dst = vc + cache_off + (size_t)(head - n_heads - n_kv_store) * kPageTokens * hd;
+            *reinterpret_cast<uint4*>(dst + i) = av;
+            *reinterpret_cast<uint4*>(dst + i + half) = bv;
+            continue;
+        }
+        uint4 ra = av, rb = bv;
+        if (cos_sin) {
+            const float4* cs = reinterpret_cast<const float4*>(cos_sin + (size_t)n * half + i);   // (c0,s0,c1,s1) x 4
+            const __nv_bfloat162* ah = reinterpret_cast<const __nv_bfloat162*>(&av);
+            const __nv_bfloat162* bh = reinterpret_cast<const __nv_bfloat162*>(&bv);
+            __nv_bfloat162* rah = reinterpret_cast<__nv_bfloat162*>(&ra);
+            __nv_bfloat162* rbh = reinterpret_cast<__nv_bfloat162*>(&rb);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float4 t = cs[j];
+                const float2 a = __bfloat1622float2(ah[j]), b = __bfloat1622float2(bh[j]);
+                rah[j] = __floats2bfloat162_rn(a.x * t.x - b.x * t.y, a.y * t.z - b.y * t.w);
+                rbh[j] = __floats2bfloat162_rn(a.x * t.y + b.x * t.x, a.y * t.w + b.y * t.z);
+            }
+        }
+        bf16* dst = head < n_heads ? src : kc + cache_off + (size_t)(head - n_heads) * kPageTokens * hd;
+        *reinterpret_cast<uint4*>(dst + i) = ra;
+        *reinterpret_cast<uint4*>(dst + i + half) = rb;
+    }
+}
+
 GTG_API int gtg_rope_kv_store(int dtype, void* qkv, int ld, const float* cos_sin,
                               int n_heads, int n_kv_store, int hd,
                               void* kc, void* vc, long long page_stride,
@@ -197,6 +305,15 @@ GTG_API int gtg_rope_kv_store(int dtype, void* qkv, int ld, const float* cos_sin
                               int N, cudaStream_t stream) {
     if (N <= 0) return 0;
     if (hd <= 0 || (hd & 1)) return kErrBadArgument;
+    if (dtype == 1 && hd % 16 == 0 && ld % 8 == 0 && page_stride % 8 == 0 && ((uintptr_t)qkv % 16) == 0 &&
+        ((uintptr_t)kc % 16) == 0 && ((uintptr_t)vc % 16) == 0 && ((uintptr_t)cos_sin % 16) == 0) {
+        const int vec_items = (n_heads + 2 * n_kv_store) * (hd / 16);
+        int t = 32;
+        while (t < 256 && t < vec_items) t *= 2;
+        rope_kv_store_bf16_vec_kernel<<<N, t, 0, stream>>>((bf16*)qkv, ld, (const float2*)cos_sin, n_heads, n_kv_store, hd,
+            (bf16*)kc, (bf16*)vc, page_stride, block_table, table_stride, token_seq, slots, positions);
+        return launch_status();
+    }
     const int items = (n_heads + 2 * n_kv_store) * (hd / 2);
     int threads = 64;
     while (threads < 512 && threads < items) threads *= 2;

@@ -43,7 +43,8 @@ def ref_rmsnorm(x, w, eps):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("H,N,eps", [(24, 3, 1e-5), (2048, 19, 1e-6), (1000, 4, 1e-3), (13000, 2, 1e-5)])
+@pytest.mark.parametrize("H,N,eps", [(24, 3, 1e-5), (2048, 19, 1e-6), (1000, 4, 1e-3), (13000, 2, 1e-5), (36, 5, 1e-5),
+                                     (8192, 3, 1e-5)])
 def test_add_rmsnorm(dtype, H, N, eps):
     res = rnd(N, H, scale=3.0, seed=1)
     pend = rnd(N, H, dtype=dtype, seed=2)
@@ -129,7 +130,7 @@ def read_sequence(cache, entry, slot, T):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("n_heads,n_kv,hd", [(4, 2, 16), (3, 1, 48), (8, 8, 64), (5, 5, 112)])
+@pytest.mark.parametrize("n_heads,n_kv,hd", [(4, 2, 16), (3, 1, 48), (8, 8, 64), (5, 5, 112), (2, 2, 24), (32, 8, 128)])
 def test_rope_kv_store(dtype, n_heads, n_kv, hd):
     cache = make_cache(n_kv, hd, dtype)
     slots = [cache.open_sequence() for _ in range(3)]
