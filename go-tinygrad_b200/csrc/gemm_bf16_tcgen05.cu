@@ -2,14 +2,19 @@
 //   C[M,N] = A[M,K] . W[N,K]^T,  float accumulation in tensor memory (TMEM),
 // output bfloat16 or float.  Both operands are K-major, W as in the checkpoint.
 //
-// One CTA computes one 128 x 256 tile of C.  Roles by warp:
+// Persistent CTAs, one per SM, each walking 128 x 256 tiles of C (tile index
+// = m + n * tiles_m, so that the CTAs running at one time share the rows of A
+// and read each tile of W once).  Roles by warp:
 //   warps 0-3  epilogue: tcgen05.ld the accumulator (warp w owns TMEM lanes
-//              32w..32w+31 = rows of the tile), convert, store to global
+//              32w..32w+31 = rows of the tile), optional SwiGLU, convert, store
 //   warp 4     producer: one thread issues the TMA loads (cp.async.bulk.tensor,
 //              128-byte swizzle) of the A tile (128 x 64) and the W tile
-//              (256 x 64) of each k block into a four-stage ring
+//              (256 x 64) of each k block into a four-stage ring that runs on
+//              across tiles
 //   warp 5     allocates TMEM; one thread issues tcgen05.mma (128 x 256 x 16,
 //              four per k block) and releases ring stages with tcgen05.commit
+// TMEM holds two accumulators (2 x 256 columns): while the epilogue drains one,
+// the MMAs of the next tile fill the other.
 // Rows and columns beyond M, N and the tail of K are zero-filled by TMA and
 // dropped at the store, so any M and N work; K must be a multiple of 8 (the
 // 16-byte row pitch TMA needs).
@@ -25,7 +30,7 @@ namespace {
 constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
 constexpr int kThreads = 192;
 constexpr int kABytes = BM * BK * 2, kBBytes = BN * BK * 2, kStageBytes = kABytes + kBBytes;
-constexpr int kTmemCols = 256;
+constexpr int kTmemCols = 512;                     // two accumulators of BN columns
 constexpr unsigned kSpinLimit = 1u << 22;
 constexpr int kSmemBytes = STAGES * kStageBytes + 1024 /* alignment slack */ + 256 /* barriers */;
 
@@ -38,6 +43,9 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
 }
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
 }
 // Polls until the phase with `parity` completes, the abort flag is raised, or the limit is hit.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
@@ -90,30 +98,29 @@ __device__ __forceinline__ void tmem_ld32(uint32_t addr, uint32_t* r) {
                  : "r"(addr));
 }
 
-template <typename OutT> __device__ __forceinline__ void store_chunk(OutT* dst, const uint32_t* v, int n_valid, bool vec_ok);
-template <> __device__ __forceinline__ void store_chunk<float>(float* dst, const uint32_t* v, int n_valid, bool vec_ok) {
-    if (vec_ok && n_valid == 32) {
+// n_valid values (float bits in v) to dst; 16-byte stores when the row allows.
+template <typename OutT, int n_full>
+__device__ __forceinline__ void store_values(OutT* dst, const uint32_t* v, int n_valid, bool vec_ok) {
+    if (vec_ok && n_valid == n_full) {
+        if constexpr (sizeof(OutT) == 2) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i)
-            reinterpret_cast<uint4*>(dst)[i] = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-    } else {
-        for (int i = 0; i < n_valid; ++i) dst[i] = __uint_as_float(v[i]);
-    }
-}
-template <> __device__ __forceinline__ void store_chunk<bf16>(bf16* dst, const uint32_t* v, int n_valid, bool vec_ok) {
-    if (vec_ok && n_valid == 32) {
+            for (int i = 0; i < n_full / 8; ++i) {
+                uint32_t p[4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            uint32_t p[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[8 * i + 2 * j]), __uint_as_float(v[8 * i + 2 * j + 1]));
-                p[j] = *reinterpret_cast<uint32_t*>(&h);
+                for (int j = 0; j < 4; ++j) {
+                    __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[8 * i + 2 * j]),
+                                                             __uint_as_float(v[8 * i + 2 * j + 1]));
+                    p[j] = *reinterpret_cast<uint32_t*>(&h);
+                }
+                reinterpret_cast<uint4*>(dst)[i] = make_uint4(p[0], p[1], p[2], p[3]);
             }
-            reinterpret_cast<uint4*>(dst)[i] = make_uint4(p[0], p[1], p[2], p[3]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < n_full / 4; ++i)
+                reinterpret_cast<uint4*>(dst)[i] = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
         }
     } else {
-        for (int i = 0; i < n_valid; ++i) dst[i] = __float2bfloat16_rn(__uint_as_float(v[i]));
+        for (int i = 0; i < n_valid; ++i) dst[i] = from_f32<OutT>(__uint_as_float(v[i]));
     }
 }
 
@@ -124,20 +131,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     extern __shared__ unsigned char smem_raw[];
     const uint32_t base = (smem_addr(smem_raw) + 1023u) & ~1023u;        // tiles need 1024-byte alignment
     unsigned char* aligned = smem_raw + (base - smem_addr(smem_raw));
-    const uint32_t bars = base + STAGES * kStageBytes;                   // full[4], empty[4], tmem_full
+    const uint32_t bars = base + STAGES * kStageBytes;   // full[S], empty[S], acc_full[2], acc_empty[2]
     uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(aligned + STAGES * kStageBytes + 128);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(aligned + STAGES * kStageBytes + 136);
     auto full_bar = [&](int s) { return bars + 8u * s; };
     auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
-    const uint32_t tmem_full_bar = bars + 8u * (2 * STAGES);
+    auto acc_full_bar = [&](int a) { return bars + 8u * (2 * STAGES + a); };
+    auto acc_empty_bar = [&](int a) { return bars + 8u * (2 * STAGES + 2 + a); };
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
+    const int n_tiles = tiles_m * tiles_n;
     const int n_kb = (K + BK - 1) / BK;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-        mbar_init(tmem_full_bar, 1);
+        for (int a = 0; a < 2; ++a) { mbar_init(acc_full_bar(a), 1); mbar_init(acc_empty_bar(a), 4); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::);
     }
@@ -154,87 +163,88 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (warp == 4) {
         // ------------------------------------------------------------ producer
         if (lane == 0) {
-            for (int kb = 0; kb < n_kb; ++kb) {
-                const int s = kb % STAGES;
-                const uint32_t round = kb / STAGES;
-                if (!mbar_wait(empty_bar(s), (round & 1u) ^ 1u, abort_flag)) break;   // passes at once in round 0
-                mbar_expect_tx(full_bar(s), kStageBytes);
-                tma_load_2d(base + s * kStageBytes, &map_a, kb * BK, m0, full_bar(s));
-                tma_load_2d(base + s * kStageBytes + kABytes, &map_w, kb * BK, n0, full_bar(s));
+            uint32_t it = 0;                                   // k blocks issued so far, over all tiles
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+                const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+                for (int kb = 0; kb < n_kb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t round = it / STAGES;
+                    ok = mbar_wait(empty_bar(s), (round & 1u) ^ 1u, abort_flag);   // passes at once in round 0
+                    if (!ok) break;
+                    mbar_expect_tx(full_bar(s), kStageBytes);
+                    tma_load_2d(base + s * kStageBytes, &map_a, kb * BK, m0, full_bar(s));
+                    tma_load_2d(base + s * kStageBytes + kABytes, &map_w, kb * BK, n0, full_bar(s));
+                }
             }
         }
     } else if (warp == 5) {
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             const uint32_t idesc = umma_idesc(BM, BN);
+            uint32_t it = 0;
             bool ok = true;
-            for (int kb = 0; kb < n_kb && ok; ++kb) {
-                const int s = kb % STAGES;
-                const uint32_t round = kb / STAGES;
-                ok = mbar_wait(full_bar(s), round & 1u, abort_flag);
+            int t = 0;                                         // tiles done by this CTA
+            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++t) {
+                const int acc = t & 1;
+                ok = mbar_wait(acc_empty_bar(acc), (((uint32_t)t >> 1) & 1u) ^ 1u, abort_flag);   // epilogue drained it
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::);
-                const uint64_t da = umma_desc(base + s * kStageBytes);
-                const uint64_t db = umma_desc(base + s * kStageBytes + kABytes);
+                const uint32_t tmem_acc = tmem_base + (uint32_t)(acc * BN);
+                for (int kb = 0; kb < n_kb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t round = it / STAGES;
+                    ok = mbar_wait(full_bar(s), round & 1u, abort_flag);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;\n" ::);
+                    const uint64_t da = umma_desc(base + s * kStageBytes);
+                    const uint64_t db = umma_desc(base + s * kStageBytes + kABytes);
 #pragma unroll
-                for (int j = 0; j < BK / 16; ++j)           // 32 bytes (16 values of k) further per step
-                    umma(tmem_base, da + 2 * j, db + 2 * j, idesc, (kb > 0 || j > 0) ? 1u : 0u);
-                umma_commit(empty_bar(s));                  // the stage is free once these MMAs have read it
+                    for (int j = 0; j < BK / 16; ++j)           // 32 bytes (16 values of k) further per step
+                        umma(tmem_acc, da + 2 * j, db + 2 * j, idesc, (kb > 0 || j > 0) ? 1u : 0u);
+                    umma_commit(empty_bar(s));                  // the stage is free once these MMAs have read it
+                }
+                umma_commit(acc_full_bar(acc));                 // this accumulator is complete
             }
-            umma_commit(tmem_full_bar);                     // the accumulator is complete
         }
     } else {
         // ------------------------------------------------------------ epilogue
-        const bool ready = mbar_wait(tmem_full_bar, 0, abort_flag);
-        asm volatile("tcgen05.fence::after_thread_sync;\n" ::);
-        if (ready) {
+        const bool vec_ok = (ldc % 8 == 0) && ((reinterpret_cast<uintptr_t>(C) & 15) == 0);
+        int t = 0;
+        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++t) {
+            const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+            const int acc = t & 1;
+            if (!mbar_wait(acc_full_bar(acc), ((uint32_t)t >> 1) & 1u, abort_flag)) break;
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::);
             const int row = m0 + warp * 32 + lane;
-            const bool vec_ok = (ldc % 8 == 0) && ((reinterpret_cast<uintptr_t>(C) & 15) == 0) && (n0 % 8 == 0);
+            const uint32_t tmem_row = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(acc * BN);
 #pragma unroll 1
             for (int c = 0; c < BN / 32; ++c) {
                 uint32_t v[32];
-                tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(c * 32), v);
+                tmem_ld32(tmem_row + (uint32_t)(c * 32), v);
                 asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
                 const int col = n0 + c * 32;
                 if (row >= M || col >= N) continue;
                 if (epi == 0) {
-                    store_chunk<OutT>(C + (size_t)row * ldc + col, v, min(32, N - col), vec_ok);
+                    store_values<OutT, 32>(C + (size_t)row * ldc + col, v, min(32, N - col), vec_ok);
                 } else {
                     // SwiGLU: the 32 columns are two blocks of 8 gate features followed by
                     // their 8 up features; 16 outputs land at column col/2
-                    uint32_t o[32];
+                    uint32_t o[16];
 #pragma unroll
                     for (int blk = 0; blk < 2; ++blk)
 #pragma unroll
                         for (int j = 0; j < 8; ++j) {
                             const float g = __uint_as_float(v[16 * blk + j]), u = __uint_as_float(v[16 * blk + 8 + j]);
-                            o[8 * blk + j] = __float_as_uint(g / (1.0f + expf(-g)) * u);
+                            o[8 * blk + j] = __float_as_uint(g / (1.0f + __expf(-g)) * u);
                         }
-                    const int n_out = min(16, (N - col) / 2);
-                    OutT* dst = C + (size_t)row * ldc + (col >> 1);
-                    if (vec_ok && n_out == 16) {
-                        if constexpr (sizeof(OutT) == 2) {
-#pragma unroll
-                            for (int i = 0; i < 2; ++i) {
-                                uint32_t p[4];
-#pragma unroll
-                                for (int j = 0; j < 4; ++j) {
-                                    __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(o[8 * i + 2 * j]),
-                                                                             __uint_as_float(o[8 * i + 2 * j + 1]));
-                                    p[j] = *reinterpret_cast<uint32_t*>(&h);
-                                }
-                                reinterpret_cast<uint4*>(dst)[i] = make_uint4(p[0], p[1], p[2], p[3]);
-                            }
-                        } else {
-#pragma unroll
-                            for (int i = 0; i < 4; ++i)
-                                reinterpret_cast<uint4*>(dst)[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
-                        }
-                    } else {
-                        for (int i = 0; i < n_out; ++i) dst[i] = from_f32<OutT>(__uint_as_float(o[i]));
-                    }
+                    store_values<OutT, 16>(C + (size_t)row * ldc + (col >> 1), o, min(16, (N - col) / 2), vec_ok);
                 }
             }
+            // all of this warp's reads of the accumulator are done: hand it back
+            asm volatile("tcgen05.fence::before_thread_sync;\n" ::);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty_bar(acc));
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::);
@@ -293,21 +303,27 @@ GTG_API int gtg_gemm_bf16_tcgen05(const void* A, int lda, const void* W, int ldw
     if (epilogue == 1 && N % 16 != 0) return kErrUnsupported;
     if (K <= 0 || lda < K || ldw < K || ldc < (epilogue ? N / 2 : N)) return kErrBadArgument;
     if (K % 8 || lda % 8 || ldw % 8 || ((uintptr_t)A % 16) || ((uintptr_t)W % 16)) return kErrUnsupported;
-    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-    if (grid.y > 65535) return kErrUnsupported;
+    const long long tiles = (long long)((N + BN - 1) / BN) * ((M + BM - 1) / BM);
+    if (tiles > 0x7fffffffLL) return kErrUnsupported;
     CUtensorMap map_a, map_w;
     int st = make_map(&map_a, A, M, K, lda, BM);
     if (st != 0) return st;
     st = make_map(&map_w, W, N, K, ldw, BN);
     if (st != 0) return st;
     static bool configured = false;
+    static int sms = 148;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
         if (e != cudaSuccess) return (int)e;
         e = cudaFuncSetAttribute(gemm_tcgen05_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
         if (e != cudaSuccess) return (int)e;
+        int dev = 0, n = 0;
+        if (cudaGetDevice(&dev) == cudaSuccess &&
+            cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0)
+            sms = n;
         configured = true;
     }
+    const int grid = (int)(tiles < sms ? tiles : sms);
     if (out_f32)
         gemm_tcgen05_kernel<float><<<grid, kThreads, kSmemBytes, stream>>>(map_a, map_w, (float*)C, ldc, M, N, K, epilogue);
     else
