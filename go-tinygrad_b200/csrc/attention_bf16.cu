@@ -23,9 +23,16 @@ namespace {
 
 constexpr float kLog2e = 1.4426950408889634f;
 
+// 2^x by the special-function unit; 2^(-inf) = 0.
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+
 // ============================================================= prefill
 template <int DP>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, DP <= 64 ? 4 : 1)
 attention_prefill_kernel(const bf16* __restrict__ q, int ldq, bf16* __restrict__ out, int ldo,
                          const bf16* __restrict__ kc, const bf16* __restrict__ vc, long long page_stride,
                          const int* __restrict__ block_table, int table_stride,
@@ -121,28 +128,36 @@ attention_prefill_kernel(const bf16* __restrict__ q, int ldq, bf16* __restrict__
                 mma_bf16_16816(s[jj * 2 + 1], qf[kk], b2, b3);
             }
         }
-        // ---- mask, streaming softmax
+        // ---- mask (only the pages that cross this warp's diagonal or window edge),
+        //      streaming softmax on raw scores: p = 2^(s * scale*log2e - m)
+        const bool all_visible = (j * kPageTokens + kPageTokens - 1 <= pos0) &&
+                                 (window <= 0 || j * kPageTokens > pos0 + 8 - window);
+        if (!all_visible) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int key = j * kPageTokens + i * 8 + t4 * 2 + (e & 1);
+                    const int pos = pos0 + (e >> 1) * 8;
+                    const bool ok = key <= pos && (window <= 0 || key > pos - window);
+                    if (!ok) s[i][e] = -INFINITY;
+                }
+            }
+        }
         float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int key = j * kPageTokens + i * 8 + t4 * 2 + (e & 1);
-                const int pos = pos0 + (e >> 1) * 8;
-                const bool ok = key <= pos && (window <= 0 || key > pos - window);
-                const float v = ok ? s[i][e] * sl2 : -INFINITY;
-                s[i][e] = v;
-                mx[e >> 1] = fmaxf(mx[e >> 1], v);
-            }
+            for (int e = 0; e < 4; ++e) mx[e >> 1] = fmaxf(mx[e >> 1], s[i][e]);
         }
         float corr[2], m_use[2];
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
             mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
             mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
-            const float m_new = fmaxf(m_row[r], mx[r]);
+            const float m_new = fmaxf(m_row[r], mx[r] * sl2);          // scale > 0: max commutes with it
             m_use[r] = m_new == -INFINITY ? 0.f : m_new;
-            corr[r] = exp2f(m_row[r] - m_use[r]);
+            corr[r] = fast_exp2(m_row[r] - m_use[r]);
             m_row[r] = m_new;
             l_row[r] *= corr[r];
         }
@@ -150,7 +165,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, int ldq, bf16* __restrict__
         for (int i = 0; i < 8; ++i) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                const float p = exp2f(s[i][e] - m_use[e >> 1]);
+                const float p = fast_exp2(fmaf(s[i][e], sl2, -m_use[e >> 1]));
                 s[i][e] = p;
                 l_row[e >> 1] += p;
             }

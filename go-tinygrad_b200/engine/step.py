@@ -19,6 +19,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import List, Optional, Sequence
 
+import numpy as np
 import torch
 
 from ..cache import Cache
@@ -37,22 +38,57 @@ class StepError(ValueError):
     """The batch handed to `step` is not valid."""
 
 
+class _Staging:
+    """Pinned host buffers the step's metadata is assembled in before its one
+    upload.  Two buffers take turns; a buffer is reused only after the copy that
+    last read it has completed."""
+
+    def __init__(self, device: torch.device):
+        self.device = device
+        self.buffers = [None, None]
+        self.events = [None, None]
+        self.turn = 0
+
+    def upload(self, flat: np.ndarray) -> torch.Tensor:
+        n = int(flat.shape[0])
+        if self.device.type != "cuda":
+            return torch.from_numpy(flat).to(self.device)
+        i = self.turn
+        self.turn ^= 1
+        if self.events[i] is not None:
+            self.events[i].synchronize()
+        buf = self.buffers[i]
+        if buf is None or buf.numel() < n:
+            buf = self.buffers[i] = torch.empty(max(4096, 2 * n), dtype=torch.int32, pin_memory=True)
+        buf[:n].numpy()[:] = flat
+        meta = torch.empty(n, dtype=torch.int32, device=self.device)
+        meta.copy_(buf[:n], non_blocking=True)
+        ev = self.events[i] = self.events[i] or torch.cuda.Event()
+        ev.record()
+        return meta
+
+
+def _staging(model: Model) -> _Staging:
+    st = getattr(model, "_step_staging", None)
+    if st is None:
+        st = model._step_staging = _Staging(model.rt.device)
+    return st
+
+
 def build_context(model: Model, cache: Cache, entries: Sequence[StepEntry]):
     """Validate the batch, reserve cache pages and upload the step's metadata in
     one copy.  Returns (context, wanted row indices on the device or None)."""
     if not entries:
         raise StepError("a step needs at least one sequence")
     vocab = model.plan.vocab_size
-    tokens: List[int] = []
-    positions: List[int] = []
-    token_seq: List[int] = []
+    tok_parts, pos_parts, seq_parts, want_parts = [], [], [], []
     cu = [0]
     slots: List[int] = []
     start: List[int] = []
-    want_rows: List[int] = []
     seen = set()
     for b, e in enumerate(entries):
-        n = len(e.tokens)
+        toks = np.asarray(e.tokens, dtype=np.int64).reshape(-1)
+        n = int(toks.shape[0])
         if n == 0:
             raise StepError(f"sequence {b} of the batch brings no tokens")
         if e.slot in seen:
@@ -60,31 +96,30 @@ def build_context(model: Model, cache: Cache, entries: Sequence[StepEntry]):
         seen.add(e.slot)
         if not cache.slots.is_held(e.slot):
             raise StepError(f"slot {e.slot} is not open")
+        if toks.min() < 0 or toks.max() >= vocab:
+            bad = toks[(toks < 0) | (toks >= vocab)][0]
+            raise StepError(f"token id {int(bad)} is outside the vocabulary of {vocab}")
         s0 = cache.length(e.slot)
-        for t in e.tokens:
-            if not 0 <= int(t) < vocab:
-                raise StepError(f"token id {t} is outside the vocabulary of {vocab}")
-        for w in e.want:
-            if not 0 <= int(w) < n:
-                raise StepError(f"wanted place {w} is outside the {n} tokens of sequence {b}")
-            want_rows.append(cu[-1] + int(w))
-        tokens.extend(int(t) for t in e.tokens)
-        positions.extend(range(s0, s0 + n))
-        token_seq.extend([b] * n)
+        if len(e.want):
+            want = np.asarray(e.want, dtype=np.int64).reshape(-1)
+            if want.min() < 0 or want.max() >= n:
+                bad = want[(want < 0) | (want >= n)][0]
+                raise StepError(f"wanted place {int(bad)} is outside the {n} tokens of sequence {b}")
+            want_parts.append(want + cu[-1])
+        tok_parts.append(toks)
+        pos_parts.append(np.arange(s0, s0 + n, dtype=np.int64))
+        seq_parts.append(np.full(n, b, dtype=np.int64))
         cu.append(cu[-1] + n)
         slots.append(e.slot)
         start.append(s0)
-    cache.reserve_many([(e.slot, cache.length(e.slot) + len(e.tokens)) for e in entries])
+    cache.reserve_many([(e.slot, s + len(e.tokens)) for e, s in zip(entries, start)])
     cache.flush_tables()
 
-    n_tok, n_seq, n_want = len(tokens), len(entries), len(want_rows)
-    flat = tokens + positions + token_seq + cu + slots + start + want_rows
-    host = torch.tensor(flat, dtype=torch.int32)
-    dev = model.rt.device
-    if dev.type == "cuda":
-        meta = host.pin_memory().to(dev, non_blocking=True)
-    else:
-        meta = host.to(dev)
+    n_tok, n_seq = cu[-1], len(entries)
+    n_want = sum(int(w.shape[0]) for w in want_parts)
+    flat = np.concatenate(tok_parts + pos_parts + seq_parts +
+                          [np.asarray(cu), np.asarray(slots), np.asarray(start)] + want_parts).astype(np.int32)
+    meta = _staging(model).upload(flat)
     o = 0
 
     def take(k):
