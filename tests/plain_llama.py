@@ -104,10 +104,8 @@ def rms_norm(x, w, eps):
     x = np.asarray(x, dtype=F32)
     out = np.empty_like(x)
     for r in range(x.shape[0]):
-        ss = F32(0.0)
         row = x[r]
-        for v in row:
-            ss = F32(ss + F32(v * v))
+        ss = np.cumsum(row * row, dtype=F32)[-1]      # the float32 running sum, left to right
         s = F32(1.0) / F32(math.sqrt(float(F32(ss / F32(row.shape[0])) + F32(eps))))
         out[r] = (w.astype(F32) * row) * s
     return out

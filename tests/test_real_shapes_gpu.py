@@ -1,0 +1,79 @@
+"""The engine at the layer sizes of the models it is measured on (SmolLM2-1.7B,
+Llama-3.2-1B, Llama-3.1-8B), with one or two layers and a small vocabulary so
+that the plain implementation stays cheap.  These shapes reach the kernels the
+tiny configurations do not: the tcgen05 product, cluster-split rows of 8192 and
+14336, heads of 128, groups of four query heads per key/value head."""
+import math
+
+import numpy as np
+import pytest
+
+import go_tinygrad_b200 as lib
+import plain_llama
+from go_tinygrad_b200.engine import StepEntry, step
+
+pytestmark = pytest.mark.gpu
+
+LLAMA3 = lambda factor: {"rope_type": "llama3", "factor": factor, "low_freq_factor": 1.0,
+                         "high_freq_factor": 4.0, "original_max_position_embeddings": 8192}
+BASE = {"architectures": ["LlamaForCausalLM"], "model_type": "llama", "rms_norm_eps": 1e-5,
+        "max_position_embeddings": 8192}
+SHAPES = {
+    "smollm2": dict(BASE, num_hidden_layers=2, hidden_size=2048, num_attention_heads=32, num_key_value_heads=32,
+                    head_dim=64, intermediate_size=8192, vocab_size=4096, rope_theta=130000.0, rope_scaling=None,
+                    tie_word_embeddings=True),
+    "llama32": dict(BASE, num_hidden_layers=1, hidden_size=2048, num_attention_heads=32, num_key_value_heads=8,
+                    head_dim=64, intermediate_size=8192, vocab_size=4099, rope_theta=500000.0,
+                    rope_scaling=LLAMA3(32.0), tie_word_embeddings=True),
+    "llama31": dict(BASE, num_hidden_layers=1, hidden_size=4096, num_attention_heads=32, num_key_value_heads=8,
+                    head_dim=128, intermediate_size=14336, vocab_size=4000, rope_theta=500000.0,
+                    rope_scaling=LLAMA3(8.0), tie_word_embeddings=False),
+}
+
+
+@pytest.fixture(scope="module", params=list(SHAPES))
+def shaped(request, tmp_path_factory):
+    name = request.param
+    folder = str(tmp_path_factory.mktemp(f"shape_{name}"))
+    lib.write_random_model(folder, SHAPES[name], seed=11, dtype="bfloat16", std=0.02, norm_std=0.05)
+    cfg, w = plain_llama.read_model(folder)
+    rng = np.random.default_rng(3)
+    prompts = [rng.integers(0, cfg["vocab_size"], n).tolist() for n in (150, 70)]
+    want = [plain_llama.forward(cfg, w, p) for p in prompts]
+    return name, folder, prompts, want
+
+
+def check(got, want, dtype, widest, what):
+    """Dot products of `widest` terms: float32 rounding grows with its square root."""
+    got, want = np.asarray(got, np.float64), np.asarray(want, np.float64)
+    assert np.isfinite(got).all(), what
+    scale = max(1.0, np.abs(want).max())
+    err = np.abs(got - want)
+    if dtype == "float32":
+        lim_max, lim_mean = 5e-5 * scale * math.sqrt(widest / 256), 5e-6 * scale * math.sqrt(widest / 256)
+    else:
+        lim_max, lim_mean = 5e-2 * scale, 6e-3 * scale
+    assert err.max() <= lim_max and err.mean() <= lim_mean, \
+        f"{what}: max {err.max():.3e} (limit {lim_max:.3e}), mean {err.mean():.3e} (limit {lim_mean:.3e})"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_real_layer_shapes(shaped, dtype):
+    name, folder, prompts, want = shaped
+    widest = SHAPES[name]["intermediate_size"]
+    model = lib.Model.load(folder, dtype=dtype, device="cuda")
+    cache = model.new_cache(max_tokens=64 * 6)
+    slots = [cache.open_sequence() for _ in prompts]
+    # the prompts without their last four tokens, together; then one token each
+    heads = [len(p) - 4 for p in prompts]
+    got = step(model, cache, [StepEntry(s, p[:h], [0, h // 2, h - 1]) for s, p, h in zip(slots, prompts, heads)])
+    got = got.float().cpu().numpy()
+    for i, (w, h) in enumerate(zip(want, heads)):
+        check(got[3 * i: 3 * i + 3], w[[0, h // 2, h - 1]], dtype, widest, f"{name} {dtype} prompt {i}")
+    for t in range(4):
+        got = step(model, cache, [StepEntry(s, [p[h + t]], [0]) for s, p, h in zip(slots, prompts, heads)])
+        got = got.float().cpu().numpy()
+        for i, (w, h) in enumerate(zip(want, heads)):
+            check(got[i], w[h + t], dtype, widest, f"{name} {dtype} decoded token {t} of prompt {i}")
+    from go_tinygrad_b200.kernels import ops
+    assert ops.bounded_wait_failures() == 0
