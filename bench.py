@@ -173,7 +173,7 @@ def run_own(args):
             cache.advance(s, context - total)
         cache.flush_tables()
         db = DecodeBatch(model, cache, slots, list(range(batch)), lib.Sampler(0.0, 0),
-                         use_graph=not args.eager)
+                         use_graph=not args.eager, chained=not args.no_chain)
         tokens = torch.randint(0, vocab, (batch,), generator=gen).tolist()
         sampler = ClockSampler()
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -288,6 +288,8 @@ def main():
                     help="run one part only and print a short line (for profilers)")
     ap.add_argument("--eager", action="store_true",
                     help="launch the decode step kernel by kernel instead of replaying a graph")
+    ap.add_argument("--no-chain", action="store_true",
+                    help="decode kernels wait for their predecessor to finish before they are launched")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":

@@ -231,6 +231,8 @@ attention_decode_kernel(const bf16* __restrict__ q, int ldq, bf16* __restrict__ 
                         const int* __restrict__ slots, const int* __restrict__ positions,
                         int n_heads, int n_kv, int hd, float scale, int window,
                         int n_splits, float* __restrict__ part_o, float* __restrict__ part_ml) {
+    chain_wait();
+    chain_release();
     constexpr int CPR = DP / 8;
     constexpr int TILE_BYTES = 64 * DP * 2;
     constexpr int STAGE_BYTES = 2 * TILE_BYTES;
@@ -422,6 +424,8 @@ attention_decode_kernel(const bf16* __restrict__ q, int ldq, bf16* __restrict__ 
 template <int DP>
 __global__ void attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                          bf16* __restrict__ out, int ldo, int n_heads, int hd, int n_splits) {
+    chain_wait();
+    chain_release();
     const int bh = blockIdx.x;                 // sequence * n_heads + head
     const int b = bh / n_heads, head = bh % n_heads;
     const int d = threadIdx.x;
@@ -485,13 +489,12 @@ int launch_decode(const bf16* q, int ldq, bf16* out, int ldo, const bf16* kc, co
     }
     const int group = n_heads / n_kv;
     dim3 grid(n_splits, n_kv * ((group + 15) / 16), B);
-    attention_decode_kernel<DP><<<grid, 128, smem, stream>>>(q, ldq, out, ldo, kc, vc, page_stride,
-        block_table, table_stride, slots, positions, n_heads, n_kv, hd, scale, window,
-        n_splits, part_o, part_ml);
-    int st = launch_status();
+    int st = launch_chained(attention_decode_kernel<DP>, grid, dim3(128), smem, stream, q, ldq, out, ldo, kc, vc,
+                            page_stride, block_table, table_stride, slots, positions, n_heads, n_kv, hd, scale,
+                            window, n_splits, part_o, part_ml);
     if (st != 0 || n_splits == 1) return st;
-    attention_combine_kernel<DP><<<B * n_heads, DP, 0, stream>>>(part_o, part_ml, out, ldo, n_heads, hd, n_splits);
-    return launch_status();
+    return launch_chained(attention_combine_kernel<DP>, dim3(B * n_heads), dim3(DP), 0, stream,
+                          (const float*)part_o, (const float*)part_ml, out, ldo, n_heads, hd, n_splits);
 }
 }  // namespace
 

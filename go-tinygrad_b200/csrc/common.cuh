@@ -75,3 +75,36 @@ struct KVPages {
 static inline int launch_status() {
     return (int)cudaGetLastError();
 }
+
+// ---- programmatic dependent launch -------------------------------------------
+// A kernel launched through launch_chained() may begin while the kernel before it
+// in the stream is still running: its blocks become resident and run up to
+// chain_wait(), which returns once that kernel has completed and its writes are
+// visible.  Before chain_wait() a kernel may only do work that depends on nothing
+// a previous kernel wrote (index arithmetic, barrier set-up, copies of weights).
+// chain_release() lets the kernel after this one begin in the same way; it is
+// issued after chain_wait(), so at most two kernels overlap.  Launched without
+// the attribute (the switch off, or a plain <<<>>> launch) both are no-ops.
+__device__ __forceinline__ void chain_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void chain_release() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+
+// One switch per compiled library (each .cu file is its own library).
+static int g_chained_launch = 0;
+GTG_API void gtg_set_chained_launch(int on) { g_chained_launch = on ? 1 : 0; }
+
+template <typename... Params, typename... Args>
+static inline int launch_chained(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem,
+                                 cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_chained_launch ? 1 : 0;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<Params>(args)...);
+    return e != cudaSuccess ? (int)e : launch_status();
+}

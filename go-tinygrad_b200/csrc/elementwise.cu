@@ -13,6 +13,8 @@
 template <typename T>
 __global__ void embed_kernel(const int* __restrict__ tokens, const T* __restrict__ table,
                              float* __restrict__ out, int H, int V) {
+    chain_wait();
+    chain_release();
     const int n = blockIdx.x;
     int tok = tokens[n];
     tok = tok < 0 ? 0 : (tok >= V ? V - 1 : tok);
@@ -23,12 +25,13 @@ __global__ void embed_kernel(const int* __restrict__ tokens, const T* __restrict
 
 GTG_API int gtg_embed(int dtype, const int* tokens, const void* table, float* out,
                       int N, int H, int V, cudaStream_t stream) {
+    int st = 0;
     if (N <= 0) return 0;
     const int threads = H >= 1024 ? 256 : 128;
-    if (dtype == 0) embed_kernel<float><<<N, threads, 0, stream>>>(tokens, (const float*)table, out, H, V);
-    else if (dtype == 1) embed_kernel<bf16><<<N, threads, 0, stream>>>(tokens, (const bf16*)table, out, H, V);
+    if (dtype == 0) st = launch_chained(embed_kernel<float>, dim3(N), dim3(threads), 0, stream, tokens, (const float*)table, out, H, V);
+    else if (dtype == 1) st = launch_chained(embed_kernel<bf16>, dim3(N), dim3(threads), 0, stream, tokens, (const bf16*)table, out, H, V);
     else return kErrBadArgument;
-    return launch_status();
+    return st;
 }
 
 // ------------------------------------------------- residual add + RMSNorm
@@ -40,6 +43,8 @@ template <typename T>
 __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __restrict__ pending,
                                    const float* __restrict__ weight, float eps,
                                    T* __restrict__ out, const int* __restrict__ rows, int H) {
+    chain_wait();
+    chain_release();
     extern __shared__ float smem[];
     float* row = smem;          // H floats
     float* scratch = smem + H;  // 33 floats
@@ -71,6 +76,8 @@ __global__ void __launch_bounds__(1024)
 add_rmsnorm_bf16_vec_kernel(float* __restrict__ residual, const bf16* __restrict__ pending,
                             const float* __restrict__ weight, float eps, bf16* __restrict__ out,
                             const int* __restrict__ rows, int H) {
+    chain_wait();
+    chain_release();
     __shared__ float scratch[33];
     const int i_out = blockIdx.x;
     const int r = rows ? rows[i_out] : i_out;
@@ -118,12 +125,13 @@ add_rmsnorm_bf16_vec_kernel(float* __restrict__ residual, const bf16* __restrict
 GTG_API int gtg_add_rmsnorm(int dtype, float* residual, const void* pending, const float* weight,
                             float eps, void* out, const int* rows, int R, int H,
                             cudaStream_t stream) {
+    int st = 0;
     if (R <= 0) return 0;
     if (dtype == 1 && H % 8 == 0 && H <= 8192 && ((uintptr_t)residual % 16) == 0 && ((uintptr_t)out % 16) == 0 &&
         ((uintptr_t)weight % 16) == 0 && ((uintptr_t)pending % 16) == 0) {
         int t = ((H / 8) + 31) / 32 * 32;
-        add_rmsnorm_bf16_vec_kernel<<<R, t, 0, stream>>>(residual, (const bf16*)pending, weight, eps, (bf16*)out, rows, H);
-        return launch_status();
+        st = launch_chained(add_rmsnorm_bf16_vec_kernel, dim3(R), dim3(t), 0, stream, residual, (const bf16*)pending, weight, eps, (bf16*)out, rows, H);
+        return st;
     }
     int threads = 32;
     while (threads < 1024 && threads * 4 < H) threads *= 2;
@@ -135,15 +143,15 @@ GTG_API int gtg_add_rmsnorm(int dtype, float* residual, const void* pending, con
             e = cudaFuncSetAttribute(add_rmsnorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (e != cudaSuccess) return (int)e;
         }
-        add_rmsnorm_kernel<float><<<R, threads, smem, stream>>>(residual, (const float*)pending, weight, eps, (float*)out, rows, H);
+        st = launch_chained(add_rmsnorm_kernel<float>, dim3(R), dim3(threads), smem, stream, residual, (const float*)pending, weight, eps, (float*)out, rows, H);
     } else if (dtype == 1) {
         if (smem > 48 * 1024) {
             e = cudaFuncSetAttribute(add_rmsnorm_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (e != cudaSuccess) return (int)e;
         }
-        add_rmsnorm_kernel<bf16><<<R, threads, smem, stream>>>(residual, (const bf16*)pending, weight, eps, (bf16*)out, rows, H);
+        st = launch_chained(add_rmsnorm_kernel<bf16>, dim3(R), dim3(threads), smem, stream, residual, (const bf16*)pending, weight, eps, (bf16*)out, rows, H);
     } else return kErrBadArgument;
-    return launch_status();
+    return st;
 }
 
 // ------------------------------------------------------------------ SwiGLU
@@ -151,6 +159,8 @@ GTG_API int gtg_add_rmsnorm(int dtype, float* residual, const void* pending, con
 // (backends/simd/vec.go:52-59).  `gu` holds the gate columns then the up columns.
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int M, int I) {
+    chain_wait();
+    chain_release();
     const size_t total = (size_t)M * I;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
          idx += (size_t)gridDim.x * blockDim.x) {
@@ -164,14 +174,15 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
 }
 
 GTG_API int gtg_swiglu(int dtype, const void* gu, void* out, int M, int I, cudaStream_t stream) {
+    int st = 0;
     if (M <= 0 || I <= 0) return 0;
     const size_t total = (size_t)M * I;
     int blocks = (int)((total + 255) / 256);
     if (blocks > 148 * 16) blocks = 148 * 16;
-    if (dtype == 0) swiglu_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gu, (float*)out, M, I);
-    else if (dtype == 1) swiglu_kernel<bf16><<<blocks, 256, 0, stream>>>((const bf16*)gu, (bf16*)out, M, I);
+    if (dtype == 0) st = launch_chained(swiglu_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)gu, (float*)out, M, I);
+    else if (dtype == 1) st = launch_chained(swiglu_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (const bf16*)gu, (bf16*)out, M, I);
     else return kErrBadArgument;
-    return launch_status();
+    return st;
 }
 
 // ------------------------------------------------------------ rotary table
@@ -180,6 +191,8 @@ GTG_API int gtg_swiglu(int dtype, const void* gu, void* out, int M, int I, cudaS
 // (model/llama.go:855-862).  Computed once per step for the step's tokens.
 __global__ void rope_table_kernel(const int* __restrict__ positions, const double* __restrict__ inv_freq,
                                   float2* __restrict__ cos_sin, int N, int half) {
+    chain_wait();
+    chain_release();
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= N * half) return;
     const int n = idx / half, i = idx - n * half;
@@ -191,10 +204,11 @@ __global__ void rope_table_kernel(const int* __restrict__ positions, const doubl
 
 GTG_API int gtg_rope_table(const int* positions, const double* inv_freq, float* cos_sin,
                            int N, int half, cudaStream_t stream) {
+    int st = 0;
     if (N <= 0 || half <= 0) return 0;
     const int total = N * half;
-    rope_table_kernel<<<(total + 127) / 128, 128, 0, stream>>>(positions, inv_freq, (float2*)cos_sin, N, half);
-    return launch_status();
+    st = launch_chained(rope_table_kernel, dim3((total + 127) / 128), dim3(128), 0, stream, positions, inv_freq, (float2*)cos_sin, N, half);
+    return st;
 }
 
 // ------------------------------------------- rotation + write into the cache
@@ -211,6 +225,8 @@ __global__ void rope_kv_store_kernel(T* __restrict__ qkv, int ld, const float2* 
                                      const int* __restrict__ block_table, int table_stride,
                                      const int* __restrict__ token_seq, const int* __restrict__ slots,
                                      const int* __restrict__ positions) {
+    chain_wait();
+    chain_release();
     const int n = blockIdx.x;
     const int half = hd >> 1;
     const int pos = positions[n];
@@ -254,6 +270,8 @@ __global__ void rope_kv_store_bf16_vec_kernel(bf16* __restrict__ qkv, int ld, co
                                               const int* __restrict__ block_table, int table_stride,
                                               const int* __restrict__ token_seq, const int* __restrict__ slots,
                                               const int* __restrict__ positions) {
+    chain_wait();
+    chain_release();
     const int n = blockIdx.x;
     const int half = hd >> 1, chunks = half >> 3;
     const int pos = positions[n];
@@ -303,6 +321,7 @@ GTG_API int gtg_rope_kv_store(int dtype, void* qkv, int ld, const float* cos_sin
                               const int* block_table, int table_stride,
                               const int* token_seq, const int* slots, const int* positions,
                               int N, cudaStream_t stream) {
+    int st = 0;
     if (N <= 0) return 0;
     if (hd <= 0 || (hd & 1)) return kErrBadArgument;
     if (dtype == 1 && hd % 16 == 0 && ld % 8 == 0 && page_stride % 8 == 0 && ((uintptr_t)qkv % 16) == 0 &&
@@ -310,21 +329,21 @@ GTG_API int gtg_rope_kv_store(int dtype, void* qkv, int ld, const float* cos_sin
         const int vec_items = (n_heads + 2 * n_kv_store) * (hd / 16);
         int t = 32;
         while (t < 256 && t < vec_items) t *= 2;
-        rope_kv_store_bf16_vec_kernel<<<N, t, 0, stream>>>((bf16*)qkv, ld, (const float2*)cos_sin, n_heads, n_kv_store, hd,
+        st = launch_chained(rope_kv_store_bf16_vec_kernel, dim3(N), dim3(t), 0, stream, (bf16*)qkv, ld, (const float2*)cos_sin, n_heads, n_kv_store, hd,
             (bf16*)kc, (bf16*)vc, page_stride, block_table, table_stride, token_seq, slots, positions);
-        return launch_status();
+        return st;
     }
     const int items = (n_heads + 2 * n_kv_store) * (hd / 2);
     int threads = 64;
     while (threads < 512 && threads < items) threads *= 2;
     if (dtype == 0)
-        rope_kv_store_kernel<float><<<N, threads, 0, stream>>>((float*)qkv, ld, (const float2*)cos_sin, n_heads, n_kv_store, hd,
+        st = launch_chained(rope_kv_store_kernel<float>, dim3(N), dim3(threads), 0, stream, (float*)qkv, ld, (const float2*)cos_sin, n_heads, n_kv_store, hd,
             (float*)kc, (float*)vc, page_stride, block_table, table_stride, token_seq, slots, positions);
     else if (dtype == 1)
-        rope_kv_store_kernel<bf16><<<N, threads, 0, stream>>>((bf16*)qkv, ld, (const float2*)cos_sin, n_heads, n_kv_store, hd,
+        st = launch_chained(rope_kv_store_kernel<bf16>, dim3(N), dim3(threads), 0, stream, (bf16*)qkv, ld, (const float2*)cos_sin, n_heads, n_kv_store, hd,
             (bf16*)kc, (bf16*)vc, page_stride, block_table, table_stride, token_seq, slots, positions);
     else return kErrBadArgument;
-    return launch_status();
+    return st;
 }
 
 // --------------------------------------------------- advance a decode batch
@@ -332,13 +351,16 @@ GTG_API int gtg_rope_kv_store(int dtype, void* qkv, int ld, const float* cos_sin
 // becomes the next input, every position moves on by one and so does every
 // sequence's count of generated tokens (which keys its next random draw).
 __global__ void advance_kernel(int* tokens, int* positions, int* steps, const int* sampled, int B) {
+    chain_wait();
+    chain_release();
     const int b = blockIdx.x * blockDim.x + threadIdx.x;
     if (b < B) { tokens[b] = sampled[b]; positions[b] += 1; steps[b] += 1; }
 }
 
 GTG_API int gtg_advance(int* tokens, int* positions, int* steps, const int* sampled, int B,
                         cudaStream_t stream) {
+    int st = 0;
     if (B <= 0) return 0;
-    advance_kernel<<<(B + 127) / 128, 128, 0, stream>>>(tokens, positions, steps, sampled, B);
-    return launch_status();
+    st = launch_chained(advance_kernel, dim3((B + 127) / 128), dim3(128), 0, stream, tokens, positions, steps, sampled, B);
+    return st;
 }

@@ -103,6 +103,8 @@ gemm_skinny_kernel(const bf16* __restrict__ X, int ldx, const bf16* __restrict__
     const uint32_t bar = smem_u32(&bar_storage), tile_addr = smem_u32(tile);
     if (threadIdx.x == 0) mbar_init(bar, 1);
     __syncthreads();
+    chain_wait();
+    chain_release();
     const bf16* xrow[NT];
 #pragma unroll
     for (int j = 0; j < NT; ++j) xrow[j] = X + (size_t)min(j * 8 + g, M - 1) * ldx + t * 8;
@@ -220,13 +222,15 @@ int launch_typed(const bf16* X, int ldx, const bf16* W, int ldw, OutT* C, int ld
         configured = true;
     }
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 1;
     attr[0].val.clusterDim.y = ranks;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = g_chained_launch ? 2 : 1;
     cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_skinny_kernel<NT, OutT>, X, ldx, W, ldw, C, ldc, M, N, K, k_slice, epi);
     if (e != cudaSuccess) return (int)e;
     return launch_status();
@@ -263,6 +267,11 @@ gemm_stream_kernel(const bf16* __restrict__ X, int ldx, const bf16* __restrict__
                       (uint32_t)k_len * 2u, bar);
     };
     if (threadIdx.x == 0 && (int)blockIdx.x < row_tiles) issue(blockIdx.x, 0);
+
+    // The weights depend on no earlier kernel, so their first copies are already in
+    // flight; the activations do.
+    chain_wait();
+    chain_release();
 
     // this thread's fragments of the activations: 8 k blocks x NT token tiles
     uint4 xf[kBlocksPerWarp][NT];
@@ -362,13 +371,15 @@ int launch_stream(const bf16* X, int ldx, const bf16* W, int ldw, OutT* C, int l
     cfg.blockDim = dim3(kWarps * 32, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 1;
     attr[0].val.clusterDim.y = ranks;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = g_chained_launch ? 2 : 1;
     cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_stream_kernel<NT, OutT>, X, ldx, W, ldw, C, ldc, M, N, K, k_slice, epi);
     if (e != cudaSuccess) return (int)e;
     return launch_status();

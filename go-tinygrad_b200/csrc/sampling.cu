@@ -14,6 +14,8 @@ constexpr int kThreads = 256;
 
 __global__ void __launch_bounds__(kThreads)
 argmax_kernel(const float* __restrict__ logits, int ld, int V, int* __restrict__ out) {
+    chain_wait();
+    chain_release();
     __shared__ float bv[kThreads];
     __shared__ int bi[kThreads];
     const float* row = logits + (size_t)blockIdx.x * ld;
@@ -59,6 +61,8 @@ __global__ void __launch_bounds__(kThreads)
 sample_temperature_kernel(const float* __restrict__ logits, int ld, int V, float inv_temperature,
                           unsigned long long seed, const int* __restrict__ sequence_ids,
                           const int* __restrict__ steps, int* __restrict__ out) {
+    chain_wait();
+    chain_release();
     __shared__ float scratch[33];
     __shared__ float seg_sum[kThreads];
     __shared__ int chosen_seg;
@@ -121,8 +125,7 @@ sample_temperature_kernel(const float* __restrict__ logits, int ld, int V, float
 GTG_API int gtg_argmax(const float* logits, int ld, int R, int V, int* out, cudaStream_t stream) {
     if (R <= 0) return 0;
     if (V <= 0 || ld < V) return kErrBadArgument;
-    argmax_kernel<<<R, kThreads, 0, stream>>>(logits, ld, V, out);
-    return launch_status();
+    return launch_chained(argmax_kernel, dim3(R), dim3(kThreads), 0, stream, logits, ld, V, out);
 }
 
 GTG_API int gtg_sample_temperature(const float* logits, int ld, int R, int V, float temperature,
@@ -130,7 +133,6 @@ GTG_API int gtg_sample_temperature(const float* logits, int ld, int R, int V, fl
                                    const int* steps, int* out, cudaStream_t stream) {
     if (R <= 0) return 0;
     if (V <= 0 || ld < V || !(temperature > 0.f)) return kErrBadArgument;
-    sample_temperature_kernel<<<R, kThreads, 0, stream>>>(logits, ld, V, 1.0f / temperature, seed,
-                                                          sequence_ids, steps, out);
-    return launch_status();
+    return launch_chained(sample_temperature_kernel, dim3(R), dim3(kThreads), 0, stream, logits, ld, V,
+                          1.0f / temperature, seed, sequence_ids, steps, out);
 }

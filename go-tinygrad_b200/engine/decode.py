@@ -31,7 +31,7 @@ from .step import logits_at, run_layers
 
 class DecodeBatch:
     def __init__(self, model: Model, cache: Cache, slots: Sequence[int], requests: Sequence[int],
-                 sampler: Sampler, use_graph: bool = True):
+                 sampler: Sampler, use_graph: bool = True, chained: bool = True):
         self.model, self.cache, self.sampler = model, cache, sampler
         self.slots = list(slots)
         B = self.B = len(self.slots)
@@ -53,6 +53,7 @@ class DecodeBatch:
         self.h_out = torch.zeros(B, dtype=torch.int32, pin_memory=pin)
         self.logits: Optional[torch.Tensor] = None
         self.use_graph = use_graph and dev.type == "cuda"
+        self.chained = chained and dev.type == "cuda"     # kernels of the step overlap their launch gaps
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self._runs = 0
 
@@ -74,9 +75,10 @@ class DecodeBatch:
 
     def _forward(self) -> None:
         ctx = self._context()
-        stream = run_layers(self.model, self.cache, ctx)
-        self.logits = logits_at(self.model, stream, ctx, self.rows)
-        self.sampler.pick(self.logits, self.requests, self.steps, out=self.sampled)
+        with ops.chained_launches(self.chained):
+            stream = run_layers(self.model, self.cache, ctx)
+            self.logits = logits_at(self.model, stream, ctx, self.rows)
+            self.sampler.pick(self.logits, self.requests, self.steps, out=self.sampled)
 
     def _launch(self) -> None:
         """Run the step for the state now on the device; grows every sequence by one."""

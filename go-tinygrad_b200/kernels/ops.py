@@ -53,6 +53,41 @@ class KernelError(RuntimeError):
     """A kernel refused its arguments or its launch failed."""
 
 
+_chained = False
+
+
+def _apply_chained(lib) -> None:
+    setter = getattr(lib, "gtg_set_chained_launch", None)
+    if setter is not None:
+        setter.argtypes, setter.restype = [c_int], None
+        setter(1 if _chained else 0)
+
+
+class chained_launches:
+    """Within this context the small kernels of a step are launched so that each
+    may begin (up to the point where it needs its predecessor's results) while
+    the one before it is still running -- programmatic dependent launch.  It is
+    meant for decode steps, where launch and drain gaps are a large share of the
+    time; the launches may be recorded into a CUDA graph."""
+
+    def __init__(self, on: bool = True):
+        self.on = bool(on)
+
+    def __enter__(self):
+        global _chained
+        self.before = _chained
+        _chained = self.on
+        for lib in build._LOADED.values():
+            _apply_chained(lib)
+        return self
+
+    def __exit__(self, *exc):
+        global _chained
+        _chained = self.before
+        for lib in build._LOADED.values():
+            _apply_chained(lib)
+
+
 def _fn(symbol: str):
     f = _FUNCS.get(symbol)
     if f is None:
@@ -60,7 +95,9 @@ def _fn(symbol: str):
         if not torch.cuda.is_available():
             raise KernelError(f"{symbol}: no CUDA device; this library runs on the GPU only "
                               f"and has no CPU path")
-        f = getattr(build.library(lib_name), symbol)
+        lib = build.library(lib_name)
+        _apply_chained(lib)
+        f = getattr(lib, symbol)
         f.argtypes = argtypes
         f.restype = _RESTYPES.get(symbol, c_int)
         _FUNCS[symbol] = f
