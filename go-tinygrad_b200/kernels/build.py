@@ -35,6 +35,7 @@ LIBRARIES: Dict[str, str] = {
     "gemm_bf16_mma": "gemm_bf16_mma.cu",
     "gemm_bf16_skinny": "gemm_bf16_skinny.cu",
     "gemm_bf16_tcgen05": "gemm_bf16_tcgen05.cu",
+    "gemm_bf16_swapab": "gemm_bf16_swapab.cu",
     "attention_bf16": "attention_bf16.cu",
     "attention_decode_static": "attention_decode_static.cu",
 }

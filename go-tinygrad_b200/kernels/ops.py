@@ -33,6 +33,9 @@ _SIGNATURES = {
     "gtg_gemm_bf16_skinny_status": ("gemm_bf16_skinny", []),
     "gtg_gemm_bf16_tcgen05": ("gemm_bf16_tcgen05", [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _P]),
     "gtg_gemm_bf16_tcgen05_status": ("gemm_bf16_tcgen05", []),
+    "gtg_gemm_bf16_swapab": ("gemm_bf16_swapab", [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _P, _P]),
+    "gtg_gemm_bf16_swapab_scratch_floats": ("gemm_bf16_swapab", [_I, _I, _I]),
+    "gtg_gemm_bf16_swapab_status": ("gemm_bf16_swapab", []),
     "gtg_attention_simple": ("attention_simple", [_I, _P, _I, _P, _I, _P, _P, _L, _P, _I, _P, _P, _P,
                                                   _I, _I, _I, _I, _F, _I, _P]),
     "gtg_attention_bf16_supports": ("attention_bf16", [_I]),
@@ -44,7 +47,8 @@ _SIGNATURES = {
     "gtg_argmax": ("sampling", [_P, _I, _I, _I, _P, _P]),
     "gtg_sample_temperature": ("sampling", [_P, _I, _I, _I, _F, _U, _P, _P, _P, _P]),
 }
-_RESTYPES = {"gtg_attention_decode_scratch_floats": c_longlong}
+_RESTYPES = {"gtg_attention_decode_scratch_floats": c_longlong,
+             "gtg_gemm_bf16_swapab_scratch_floats": c_longlong}
 
 _FUNCS = {}
 
@@ -235,7 +239,8 @@ def advance(tokens: torch.Tensor, positions: torch.Tensor, steps: torch.Tensor,
 
 
 # ---------------------------------------------------------------- matrix products
-SKINNY_MAX_ROWS = 64
+SKINNY_MAX_ROWS = 64          # most rows the weight-streaming kernels take
+STREAM_MAX_ROWS = 16          # up to here: warp-level MMA fed by bulk copies; beyond: tcgen05 with swapped operands
 TILED_KIND = "tcgen05"        # what "auto" uses beyond SKINNY_MAX_ROWS rows
 
 
@@ -252,8 +257,9 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, kind: str = "aut
     """out[M,N] = x[M,K] . w[N,K]^T.  float32 operands take the true 32-bit
     kernel; bfloat16 operands accumulate in float and write bfloat16 or float32.
     `kind` picks the bfloat16 kernel: "auto" (by the number of rows), "skinny"
-    (weight streaming, up to 64 rows), "tcgen05" (TMA + tensor memory) or "tiled"
-    (warp-level MMA).  epilogue="swiglu" (bfloat16, not "tiled"): w is laid out by
+    (weight streaming, up to 64 rows), "swapab" (weight streaming on tcgen05 with
+    the tokens as the N dimension, up to 64 rows), "tcgen05" (TMA + tensor memory)
+    or "tiled" (warp-level MMA).  epilogue="swiglu" (bfloat16, not "tiled"): w is laid out by
     `interleave_gate_up` and out[M, N/2] = silu(gate) * up, computed from the
     float accumulators."""
     _rows2d(x, "linear: x"); _rows2d(w, "linear: w"); _rows2d(out, "linear: out")
@@ -275,17 +281,24 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, kind: str = "aut
           f"linear(bfloat16): the inner size {K} and the row strides must be multiples of 8")
     # few rows (a decode step): stream the weights once; many rows: tiled product
     if kind == "auto":
-        kind = "skinny" if M <= SKINNY_MAX_ROWS else TILED_KIND
-    symbol = {"skinny": "gtg_gemm_bf16_skinny", "tiled": "gtg_gemm_bf16_mma",
+        kind = "skinny" if M <= STREAM_MAX_ROWS else "swapab" if M <= SKINNY_MAX_ROWS else TILED_KIND
+    symbol = {"skinny": "gtg_gemm_bf16_skinny", "tiled": "gtg_gemm_bf16_mma", "swapab": "gtg_gemm_bf16_swapab",
               "tcgen05": "gtg_gemm_bf16_tcgen05"}.get(kind)
     _need(symbol is not None, f"linear: unknown kind {kind!r}")
-    if kind == "skinny":
-        _need(M <= SKINNY_MAX_ROWS, f"linear: the weight-streaming kernel takes at most {SKINNY_MAX_ROWS} rows")
+    if kind in ("skinny", "swapab"):
+        _need(M <= SKINNY_MAX_ROWS, f"linear: the weight-streaming kernels take at most {SKINNY_MAX_ROWS} rows")
     out_f32 = 1 if out.dtype == torch.float32 else 0
     if kind == "tiled":
         _need(epilogue == "none", "linear: the warp-level kernel has no fused epilogue")
         code = _fn(symbol)(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0),
                            out_f32, M, N, K, _stream())
+    elif kind == "swapab":
+        if epilogue == "swiglu":
+            _need(N % 16 == 0, f"linear: the fused SwiGLU needs a multiple of 16 rows of w, got {N}")
+        scratch = torch.empty(int(_fn("gtg_gemm_bf16_swapab_scratch_floats")(M, N, K)), dtype=torch.float32,
+                              device=x.device)
+        code = _fn(symbol)(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0),
+                           out_f32, M, N, K, 1 if epilogue == "swiglu" else 0, _ptr(scratch), _stream())
     else:
         if epilogue == "swiglu":
             _need(N % 16 == 0, f"linear: the fused SwiGLU needs a multiple of 16 rows of w, got {N}")
@@ -298,7 +311,7 @@ def bounded_wait_failures() -> int:
     """Non-zero if a kernel ever gave up a bounded wait on its own asynchronous
     copies (it then returned without a result).  Reading it synchronises."""
     total = 0
-    for symbol in ("gtg_gemm_bf16_skinny_status", "gtg_gemm_bf16_tcgen05_status"):
+    for symbol in ("gtg_gemm_bf16_skinny_status", "gtg_gemm_bf16_tcgen05_status", "gtg_gemm_bf16_swapab_status"):
         if _SIGNATURES[symbol][0] in build._LOADED:        # only libraries that have run can have failed
             total += int(_fn(symbol)())
     return total

@@ -199,14 +199,14 @@ def test_linear_float32_does_not_depend_on_the_batch():
 
 
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
-@pytest.mark.parametrize("kind", ["skinny", "tiled", "tcgen05"])
+@pytest.mark.parametrize("kind", ["skinny", "swapab", "tiled", "tcgen05"])
 @pytest.mark.parametrize("M,N,K", [(1, 17, 8), (5, 96, 264), (64, 391, 96), (130, 130, 40),
                                    (257, 1000, 2048), (3, 2048, 8192), (8, 6144, 2048),
                                    (300, 144, 96), (9, 50, 1000), (17, 33, 72), (40, 1001, 2056),
                                    (33, 16, 8200)])
 def test_linear_bfloat16(out_dtype, kind, M, N, K):
-    if kind == "skinny" and M > ops.SKINNY_MAX_ROWS:
-        pytest.skip("more rows than the weight-streaming kernel takes")
+    if kind in ("skinny", "swapab") and M > ops.SKINNY_MAX_ROWS:
+        pytest.skip("more rows than the weight-streaming kernels take")
     x, w = rnd(M, K, dtype=torch.bfloat16, seed=1), rnd(N, K, dtype=torch.bfloat16, seed=2)
     out = torch.empty(M, N, dtype=out_dtype, device=DEV)
     ops.linear(x, w, out, kind=kind)
@@ -245,13 +245,13 @@ def test_linear_skinny_long_rows_split_over_a_cluster(M, N, K):
     assert ops.bounded_wait_failures() == 0
 
 
-@pytest.mark.parametrize("kind", ["skinny", "tcgen05"])
+@pytest.mark.parametrize("kind", ["skinny", "swapab", "tcgen05"])
 @pytest.mark.parametrize("M,I,K", [(1, 8, 96), (8, 264, 96), (16, 1000, 2048), (33, 24, 8192), (64, 264, 264),
                                    (200, 264, 96), (130, 1000, 2048)])
 def test_linear_with_fused_swiglu(kind, M, I, K):
     """The product over interleaved gate/up rows writes silu(gate) * up directly."""
-    if kind == "skinny" and M > ops.SKINNY_MAX_ROWS:
-        pytest.skip("more rows than the weight-streaming kernel takes")
+    if kind in ("skinny", "swapab") and M > ops.SKINNY_MAX_ROWS:
+        pytest.skip("more rows than the weight-streaming kernels take")
     x = rnd(M, K, dtype=torch.bfloat16, seed=1, scale=0.5)
     gate, up = rnd(I, K, dtype=torch.bfloat16, seed=2, scale=0.2), rnd(I, K, dtype=torch.bfloat16, seed=3, scale=0.2)
     w = ops.interleave_gate_up(gate, up)
