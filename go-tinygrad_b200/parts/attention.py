@@ -87,6 +87,8 @@ class GQAttention(Mixer):
             waves = -(-blocks // slots)
             per_split = -(-pages // s)
             score = blocks / (waves * slots) * per_split / (per_split + 1.0)
+            if s > 1:
+                score *= 0.93               # the partial results and the kernel that merges them
             if score > best_score + 1e-9:
                 best, best_score = s, score
         return best
