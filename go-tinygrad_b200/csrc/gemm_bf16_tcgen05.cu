@@ -32,7 +32,9 @@ constexpr int kThreads = 192;
 constexpr int kABytes = BM * BK * 2, kBBytes = BN * BK * 2, kStageBytes = kABytes + kBBytes;
 constexpr int kTmemCols = 512;                     // two accumulators of BN columns
 constexpr unsigned kSpinLimit = 1u << 22;
-constexpr int kSmemBytes = STAGES * kStageBytes + 1024 /* alignment slack */ + 256 /* barriers */;
+constexpr int kStoreBytes = 32 * 128;              // one staged box: 32 rows x 64 bfloat16
+constexpr int kSmemBytes = STAGES * kStageBytes + 1024 /* barriers */ + 4 * 2 * kStoreBytes /* staging */ +
+                           1024 /* alignment slack */;
 
 __device__ int g_status = 0;
 
@@ -127,6 +129,7 @@ __device__ __forceinline__ void store_values(OutT* dst, const uint32_t* v, int n
 template <typename OutT>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                    const __grid_constant__ CUtensorMap map_c, int use_store_map,
                     OutT* __restrict__ C, int ldc, int M, int N, int K, int epi) {
     extern __shared__ unsigned char smem_raw[];
     const uint32_t base = (smem_addr(smem_raw) + 1023u) & ~1023u;        // tiles need 1024-byte alignment
@@ -210,6 +213,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     } else {
         // ------------------------------------------------------------ epilogue
         const bool vec_ok = (ldc % 8 == 0) && ((reinterpret_cast<uintptr_t>(C) & 15) == 0);
+        // bfloat16 rows that TMA can address: the warp stages 32 rows x 64 columns in
+        // shared memory (128-byte rows, swizzled like the tensor map) and one lane
+        // stores the box; the store clips rows and columns beyond M and the output
+        // width.  Otherwise every lane stores its own row directly.
+        const bool staged = use_store_map && sizeof(OutT) == 2;
+        unsigned char* stage_base = aligned + STAGES * kStageBytes + 1024 + warp * (2 * kStoreBytes);
+        uint32_t groups = 0;                               // 64-column boxes stored so far by this warp
         int t = 0;
         for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++t) {
             const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
@@ -218,27 +228,85 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::);
             const int row = m0 + warp * 32 + lane;
             const uint32_t tmem_row = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(acc * BN);
+            if (staged) {
+                const int per_box = epi ? 4 : 2;           // accumulator chunks of 32 columns per 64 output columns
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-                uint32_t v[32];
-                tmem_ld32(tmem_row + (uint32_t)(c * 32), v);
-                asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-                const int col = n0 + c * 32;
-                if (row >= M || col >= N) continue;
-                if (epi == 0) {
-                    store_values<OutT, 32>(C + (size_t)row * ldc + col, v, min(32, N - col), vec_ok);
-                } else {
-                    // SwiGLU: the 32 columns are two blocks of 8 gate features followed by
-                    // their 8 up features; 16 outputs land at column col/2
-                    uint32_t o[16];
+                for (int c0 = 0; c0 < BN / 32; c0 += per_box, ++groups) {
+                    unsigned char* buf = stage_base + (groups & 1u) * kStoreBytes;
+                    if (groups >= 2) {                     // the box stored from this buffer two rounds ago has been read
+                        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;\n" ::: "memory");
+                        __syncwarp();
+                    }
+                    for (int cc = 0; cc < per_box; ++cc) {
+                        uint32_t v[32];
+                        tmem_ld32(tmem_row + (uint32_t)((c0 + cc) * 32), v);
+                        asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+                        if (epi == 0) {
+                            // 32 columns = four 16-byte pieces, at pieces 4*cc .. 4*cc+3 of the row
 #pragma unroll
-                    for (int blk = 0; blk < 2; ++blk)
+                            for (int piece = 0; piece < 4; ++piece) {
+                                uint32_t p[4];
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            const float g = __uint_as_float(v[16 * blk + j]), u = __uint_as_float(v[16 * blk + 8 + j]);
-                            o[8 * blk + j] = __float_as_uint(g / (1.0f + __expf(-g)) * u);
+                                for (int q = 0; q < 4; ++q) {
+                                    __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[8 * piece + 2 * q]),
+                                                                             __uint_as_float(v[8 * piece + 2 * q + 1]));
+                                    p[q] = *reinterpret_cast<uint32_t*>(&h);
+                                }
+                                const int chunk = 4 * cc + piece;
+                                *reinterpret_cast<uint4*>(buf + lane * 128 + ((chunk ^ (lane & 7)) << 4)) =
+                                    make_uint4(p[0], p[1], p[2], p[3]);
+                            }
+                        } else {
+                            // SwiGLU: two blocks of 8 gate + 8 up features -> 16 outputs = two pieces
+#pragma unroll
+                            for (int blk = 0; blk < 2; ++blk) {
+                                uint32_t p[4];
+#pragma unroll
+                                for (int q = 0; q < 4; ++q) {
+                                    const float g0 = __uint_as_float(v[16 * blk + 2 * q]), u0 = __uint_as_float(v[16 * blk + 8 + 2 * q]);
+                                    const float g1 = __uint_as_float(v[16 * blk + 2 * q + 1]), u1 = __uint_as_float(v[16 * blk + 9 + 2 * q]);
+                                    __nv_bfloat162 h = __floats2bfloat162_rn(g0 / (1.0f + __expf(-g0)) * u0,
+                                                                             g1 / (1.0f + __expf(-g1)) * u1);
+                                    p[q] = *reinterpret_cast<uint32_t*>(&h);
+                                }
+                                const int chunk = 2 * cc + blk;
+                                *reinterpret_cast<uint4*>(buf + lane * 128 + ((chunk ^ (lane & 7)) << 4)) =
+                                    make_uint4(p[0], p[1], p[2], p[3]);
+                            }
                         }
-                    store_values<OutT, 16>(C + (size_t)row * ldc + (col >> 1), o, min(16, (N - col) / 2), vec_ok);
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // generic writes -> TMA reads
+                    __syncwarp();
+                    if (lane == 0) {
+                        const int out_col = epi ? ((n0 + c0 * 32) >> 1) : (n0 + c0 * 32);
+                        asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];\n"
+                                     ::"l"(&map_c), "r"(smem_addr(buf)), "r"(out_col), "r"(m0 + warp * 32) : "memory");
+                        asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
+                    }
+                }
+            } else {
+#pragma unroll 1
+                for (int c = 0; c < BN / 32; ++c) {
+                    uint32_t v[32];
+                    tmem_ld32(tmem_row + (uint32_t)(c * 32), v);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+                    const int col = n0 + c * 32;
+                    if (row >= M || col >= N) continue;
+                    if (epi == 0) {
+                        store_values<OutT, 32>(C + (size_t)row * ldc + col, v, min(32, N - col), vec_ok);
+                    } else {
+                        // SwiGLU: the 32 columns are two blocks of 8 gate features followed by
+                        // their 8 up features; 16 outputs land at column col/2
+                        uint32_t o[16];
+#pragma unroll
+                        for (int blk = 0; blk < 2; ++blk)
+#pragma unroll
+                            for (int q = 0; q < 8; ++q) {
+                                const float g = __uint_as_float(v[16 * blk + q]), u = __uint_as_float(v[16 * blk + 8 + q]);
+                                o[8 * blk + q] = __float_as_uint(g / (1.0f + __expf(-g)) * u);
+                            }
+                        store_values<OutT, 16>(C + (size_t)row * ldc + (col >> 1), o, min(16, (N - col) / 2), vec_ok);
+                    }
                 }
             }
             // all of this warp's reads of the accumulator are done: hand it back
@@ -246,6 +314,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             __syncwarp();
             if (lane == 0) mbar_arrive(acc_empty_bar(acc));
         }
+        if (staged && lane == 0) asm volatile("cp.async.bulk.wait_group 0;\n" ::: "memory");   // stores have landed
     }
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::);
     __syncthreads();
@@ -310,6 +379,13 @@ GTG_API int gtg_gemm_bf16_tcgen05(const void* A, int lda, const void* W, int ldw
     if (st != 0) return st;
     st = make_map(&map_w, W, N, K, ldw, BN);
     if (st != 0) return st;
+    // the store map: C as [M, output width] bfloat16 in boxes of 64 x 32 (when its rows allow it)
+    const int n_out = epilogue ? N / 2 : N;
+    CUtensorMap map_c = map_a;
+    int use_store_map = 0;
+    if (!out_f32 && ldc % 8 == 0 && ((uintptr_t)C % 16) == 0) {
+        if (make_map(&map_c, C, M, n_out, ldc, 32) == 0) use_store_map = 1;
+    }
     static bool configured = false;
     static int sms = 148;
     if (!configured) {
@@ -325,8 +401,8 @@ GTG_API int gtg_gemm_bf16_tcgen05(const void* A, int lda, const void* W, int ldw
     }
     const int grid = (int)(tiles < sms ? tiles : sms);
     if (out_f32)
-        gemm_tcgen05_kernel<float><<<grid, kThreads, kSmemBytes, stream>>>(map_a, map_w, (float*)C, ldc, M, N, K, epilogue);
+        gemm_tcgen05_kernel<float><<<grid, kThreads, kSmemBytes, stream>>>(map_a, map_w, map_c, use_store_map, (float*)C, ldc, M, N, K, epilogue);
     else
-        gemm_tcgen05_kernel<bf16><<<grid, kThreads, kSmemBytes, stream>>>(map_a, map_w, (bf16*)C, ldc, M, N, K, epilogue);
+        gemm_tcgen05_kernel<bf16><<<grid, kThreads, kSmemBytes, stream>>>(map_a, map_w, map_c, use_store_map, (bf16*)C, ldc, M, N, K, epilogue);
     return launch_status();
 }
