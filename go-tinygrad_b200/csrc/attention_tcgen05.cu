@@ -1,0 +1,435 @@
+// Causal grouped-query prefill attention on the fifth-generation tensor cores,
+// for heads of 64 channels, over the paged cache.
+//
+// One CTA per (128-query tile, query head, sequence).  Per cache page (64 keys):
+//   S  = Q K^T      tcgen05.mma 128 x 64 x 64, Q and the key page in shared memory
+//                   (TMA, 128-byte swizzle, both K-major), S in TMEM (two tiles)
+//   P  = softmax    four warps, one thread per query row: tcgen05.ld its 64 scores,
+//                   mask (diagonal and window-edge pages only), running max and sum
+//                   in float, write the row of P as bfloat16 into shared memory in
+//                   the operand layout (no shuffles: a row lives in one thread)
+//   O += P V        tcgen05.mma 128 x 64 x 64 with the value page as the MN-major B
+//                   operand -- the page's [key][channel] rows are that layout as
+//                   they lie in the cache -- accumulating in TMEM over all pages
+// The running maximum m of a row is only raised when the page's maximum exceeds it
+// by more than 2^8; until then P = exp2(s - m) is taken against the older m (at
+// most 256, exact in float and as good as any other scale in bfloat16) and the sum
+// uses the same m, so the quotient O / l is unchanged.  Raising m multiplies the
+// row of O in TMEM by exp2(m_old - m_new) (tcgen05.ld / st by the row's thread, after
+// the previous page's product has completed); it happens in the first pages and
+// rarely later, so the steady state has no dependence of the softmax on the PV
+// products.  Roles: warps 0-3 softmax and output, warp 4 issues the TMA loads (four
+// stages of key+value pages), warp 5 allocates TMEM and issues the MMAs; the next
+// page's S is issued before this page's P is waited for, so it runs under this
+// page's softmax.  Every mbarrier wait is bounded (status word as in the products).
+#include "common.cuh"
+#include <cuda.h>
+#include <math.h>
+
+namespace {
+constexpr int BQ = 128;                 // query rows per CTA
+constexpr int HD = 64;                  // head size this kernel serves
+constexpr int kThreads = 192;
+constexpr int kStages = 4;              // key+value pages in flight
+constexpr int kQBytes = BQ * HD * 2, kPageBytes = kPageTokens * HD * 2, kPBytes = BQ * kPageTokens * 2;
+constexpr int kTmemCols = 256;          // S twice (64 each), O (64); a power of two
+constexpr unsigned kSpinLimit = 1u << 22;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kRaiseBy = 8.0f;        // the running maximum follows only jumps above 2^8
+// shared memory: Q | stages of (K, V) | P[2] | barriers.  Two CTAs fit one SM.
+constexpr int kOffKV = kQBytes, kOffP = kOffKV + kStages * 2 * kPageBytes;
+constexpr int kOffBar = kOffP + 2 * kPBytes;
+constexpr int kSmemBytes = kOffBar + 256;
+
+__device__ int g_status = 0;
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    for (unsigned i = 0; i < kSpinLimit; ++i) {
+        uint32_t done;
+        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+                     "selp.u32 %0, 1, 0, p;\n}\n" : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+        if (done) return true;
+        if ((i & 1023u) == 1023u && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    atomicExch(&g_status, 1);
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
+}
+// Operand descriptor for a tile of 128-byte rows with 128-byte swizzle whose 8-row
+// groups are 1024 bytes apart.  Read K-major (rows = M/N index, the 64 values of a
+// row = k) or MN-major (rows = k index, the 64 values of a row = N index): which
+// one is said by the instruction descriptor, the bytes are laid out the same.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+// kind::f16, float accumulator, bfloat16 operands; A K-major; B K-major or MN-major.
+__host__ __device__ constexpr uint32_t umma_idesc(int m, int n, int b_mn_major) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)b_mn_major << 16) |
+           ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+                 ::"r"(tmem_d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t addr, uint32_t* r) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+                 "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(addr));
+}
+__device__ __forceinline__ void tmem_st32(uint32_t addr, const uint32_t* r) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+                 "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+                 "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n"
+                 ::"r"(addr),
+                   "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+                   "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+                   "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+                   "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+                 : "memory");
+}
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// map_q: the step's [tokens, row width] activations, boxes of 64 channels x 128 rows.
+// map_kv: one cache entry as rows of 64 channels, row = ((page*2 + k|v)*n_kv + head)*64 + token.
+// grid: (query heads, sequences, query tiles), the longest tiles first.
+__global__ void __launch_bounds__(kThreads, 2)
+attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
+                            bf16* __restrict__ out, int ldo,
+                            const int* __restrict__ block_table, int table_stride,
+                            const int* __restrict__ cu_seqlens, const int* __restrict__ slots,
+                            const int* __restrict__ start_pos,
+                            int n_heads, int n_kv, float scale, int window) {
+    extern __shared__ __align__(1024) unsigned char smem[];
+    const int h = blockIdx.x, b = blockIdx.y;
+    const int tile = gridDim.z - 1 - blockIdx.z;
+    const int q_begin = cu_seqlens[b];
+    const int q_len = cu_seqlens[b + 1] - q_begin;
+    if (tile * BQ >= q_len) return;                              // before any barrier or TMEM use
+    const uint32_t base = smem_addr(smem);
+    if (base & 1023u) {                                          // the swizzled tiles need this alignment
+        if (threadIdx.x == 0) atomicExch(&g_status, 2);
+        return;
+    }
+    const uint32_t bars = base + kOffBar;
+    const uint32_t q_full = bars;
+    auto kv_full = [&](int s) { return bars + 8u + 8u * s; };
+    auto kv_empty = [&](int s) { return bars + 40u + 8u * s; };
+    auto s_full = [&](int s) { return bars + 72u + 8u * s; };
+    auto p_full = [&](int s) { return bars + 88u + 8u * s; };
+    auto pv_done = [&](int s) { return bars + 104u + 8u * s; };
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + kOffBar + 128);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kOffBar + 136);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int start = start_pos[b];
+    const int kvh = h / (n_heads / n_kv);
+    const int* table = block_table + (size_t)slots[b] * table_stride;
+    const int rows_here = min(BQ, q_len - tile * BQ);
+    const int k_max = start + tile * BQ + rows_here - 1;         // last key any row of the tile sees
+    const int k_min = window > 0 ? max(0, start + tile * BQ - window + 1) : 0;
+    const int j_lo = k_min / kPageTokens, j_hi = k_max / kPageTokens;
+    const int n_pages = j_hi - j_lo + 1;
+
+    if (threadIdx.x == 0) {
+        mbar_init(q_full, 1);
+        for (int s = 0; s < kStages; ++s) { mbar_init(kv_full(s), 1); mbar_init(kv_empty(s), 1); }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(s_full(s), 1);
+            mbar_init(p_full(s), 4);                             // one arrival per softmax warp
+            mbar_init(pv_done(s), 1);
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::);
+    }
+    if (warp == 5) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n"
+                     ::"r"(smem_addr(tmem_holder)), "r"(kTmemCols));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::);
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::);
+    const uint32_t tmem_s = *tmem_holder, tmem_o = tmem_s + 128;   // S of page i at columns 64 * (i & 1)
+
+    if (warp == 4) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            mbar_expect_tx(q_full, kQBytes);
+            tma_load_2d(base, &map_q, h * HD, q_begin + tile * BQ, q_full);
+            for (int i = 0; i < n_pages; ++i) {
+                const int s = i % kStages;
+                if (!mbar_wait(kv_empty(s), (((uint32_t)i / kStages) & 1u) ^ 1u, abort_flag)) break;
+                const int page = table[j_lo + i];
+                const int row_k = ((page * 2 + 0) * n_kv + kvh) * kPageTokens;
+                const int row_v = ((page * 2 + 1) * n_kv + kvh) * kPageTokens;
+                const uint32_t dst = base + kOffKV + s * 2 * kPageBytes;
+                mbar_expect_tx(kv_full(s), 2 * kPageBytes);
+                tma_load_2d(dst, &map_kv, 0, row_k, kv_full(s));
+                tma_load_2d(dst + kPageBytes, &map_kv, 0, row_v, kv_full(s));
+            }
+        }
+    } else if (warp == 5) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            const uint32_t idesc_s = umma_idesc(BQ, kPageTokens, 0);      // S[128 x 64 keys], key page K-major
+            const uint32_t idesc_pv = umma_idesc(BQ, HD, 1);              // O[128 x 64 channels], value page MN-major
+            bool ok = mbar_wait(q_full, 0, abort_flag);
+            auto issue_s = [&](int i) {
+                const int s = i % kStages;
+                if (!mbar_wait(kv_full(s), ((uint32_t)i / kStages) & 1u, abort_flag)) return false;
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::);
+                const uint64_t dq = umma_desc(base), dk = umma_desc(base + kOffKV + s * 2 * kPageBytes);
+#pragma unroll
+                for (int kk = 0; kk < HD / 16; ++kk)
+                    umma(tmem_s + 64 * (i & 1), dq + 2 * kk, dk + 2 * kk, idesc_s, kk > 0 ? 1u : 0u);
+                umma_commit(s_full(i & 1));
+                return true;
+            };
+            if (ok) ok = issue_s(0);
+            for (int i = 0; i < n_pages && ok; ++i) {
+                // the next page's scores run under this page's softmax: their TMEM tile was
+                // released by p_full of page i - 1
+                if (i + 1 < n_pages) ok = issue_s(i + 1);
+                if (!ok) break;
+                ok = mbar_wait(p_full(i & 1), ((uint32_t)i >> 1) & 1u, abort_flag);   // P_i written, S_i read, O rescaled
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::);
+                const int s = i % kStages;
+                const uint64_t dp = umma_desc(base + kOffP + (i & 1) * kPBytes);
+                const uint64_t dv = umma_desc(base + kOffKV + s * 2 * kPageBytes + kPageBytes);
+#pragma unroll
+                for (int kk = 0; kk < kPageTokens / 16; ++kk)              // 16 keys per step: P 32 bytes on, V two 8-key groups on
+                    umma(tmem_o, dp + 2 * kk, dv + (uint64_t)(2 * 1024 >> 4) * kk, idesc_pv, (i > 0 || kk > 0) ? 1u : 0u);
+                umma_commit(kv_empty(s));                                   // K_i and V_i have been read
+                umma_commit(pv_done(i & 1));                                // P_i has been read, O holds pages 0..i
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ softmax + output (thread = query row)
+        const unsigned full = 0xffffffffu;
+        const int r = warp * 32 + lane;                          // row of the tile, TMEM lane
+        const int pos = start + tile * BQ + r;                   // position of this query
+        const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
+        const float sl2 = scale * kLog2e;
+        float m_run = -INFINITY, l_run = 0.f;
+        uint32_t sv[64];
+        bool ok = true;
+        for (int i = 0; i < n_pages; ++i) {
+            const int j = j_lo + i;
+            ok = __all_sync(full, mbar_wait(s_full(i & 1), ((uint32_t)i >> 1) & 1u, abort_flag));
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::);
+            tmem_ld32(tmem_s + 64 * (i & 1) + lane_off, sv);
+            tmem_ld32(tmem_s + 64 * (i & 1) + lane_off + 32, sv + 32);
+            asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+            const bool all_visible = (j * kPageTokens + kPageTokens - 1 <= pos) &&
+                                     (window <= 0 || j * kPageTokens > pos - window);
+            if (!all_visible) {
+#pragma unroll
+                for (int c = 0; c < 64; ++c) {
+                    const int key = j * kPageTokens + c;
+                    const bool vis = key <= pos && (window <= 0 || key > pos - window);
+                    if (!vis) sv[c] = __float_as_uint(-INFINITY);
+                }
+            }
+            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < 64; c += 4) {
+                mx0 = fmaxf(mx0, __uint_as_float(sv[c]));
+                mx1 = fmaxf(mx1, __uint_as_float(sv[c + 1]));
+                mx2 = fmaxf(mx2, __uint_as_float(sv[c + 2]));
+                mx3 = fmaxf(mx3, __uint_as_float(sv[c + 3]));
+            }
+            const float m_page = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * sl2;
+            if (i == 0) {
+                m_run = m_page;                                  // the first product overwrites O
+            } else {
+                const bool raise = m_page > m_run + kRaiseBy;    // also: the first visible key of a row
+                if (__any_sync(full, raise)) {
+                    float corr = 1.0f;
+                    if (raise) {
+                        corr = fast_exp2(m_run - m_page);        // 0 when the row had seen nothing
+                        m_run = m_page;
+                        l_run *= corr;
+                    }
+                    // O holds pages 0..i-1 once the previous product has completed
+                    ok = __all_sync(full, mbar_wait(pv_done((i - 1) & 1), ((uint32_t)(i - 1) >> 1) & 1u, abort_flag));
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;\n" ::);
+                    uint32_t ov[32];
+#pragma unroll
+                    for (int half = 0; half < 2; ++half) {
+                        tmem_ld32(tmem_o + lane_off + 32 * half, ov);
+                        asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+                        for (int d = 0; d < 32; ++d) ov[d] = __float_as_uint(__uint_as_float(ov[d]) * corr);
+                        tmem_st32(tmem_o + lane_off + 32 * half, ov);
+                    }
+                    asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+                }
+            }
+            const float m_use = m_run == -INFINITY ? 0.f : m_run;
+            // P_i goes where P_{i-2} was: its product must have completed
+            if (i >= 2) {
+                ok = __all_sync(full, mbar_wait(pv_done(i & 1), ((uint32_t)(i - 2) >> 1) & 1u, abort_flag));
+                if (!ok) break;
+            }
+            unsigned char* prow = smem + kOffP + (i & 1) * kPBytes + r * 128;
+            float l0 = 0.f, l1 = 0.f;
+            // the row of P: 64 bfloat16 = eight 16-byte pieces, piece c at (c ^ (r & 7))
+#pragma unroll
+            for (int piece = 0; piece < 8; ++piece) {
+                uint32_t pk[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const float p0 = fast_exp2(fmaf(__uint_as_float(sv[8 * piece + 2 * q]), sl2, -m_use));
+                    const float p1 = fast_exp2(fmaf(__uint_as_float(sv[8 * piece + 2 * q + 1]), sl2, -m_use));
+                    l0 += p0;
+                    l1 += p1;
+                    __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
+                    pk[q] = *reinterpret_cast<uint32_t*>(&hh);
+                }
+                *reinterpret_cast<uint4*>(prow + ((piece ^ (r & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            }
+            l_run += l0 + l1;
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // P written by threads, read by the tensor core
+            asm volatile("tcgen05.fence::before_thread_sync;\n" ::);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(p_full(i & 1));
+        }
+        if (ok) ok = __all_sync(full, mbar_wait(pv_done((n_pages - 1) & 1), ((uint32_t)(n_pages - 1) >> 1) & 1u, abort_flag));
+        if (ok) {
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::);
+            tmem_ld32(tmem_o + lane_off, sv);
+            tmem_ld32(tmem_o + lane_off + 32, sv + 32);
+            asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+            if (r < rows_here) {
+                const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+                bf16* dst = out + (size_t)(q_begin + tile * BQ + r) * ldo + h * HD;
+#pragma unroll
+                for (int piece = 0; piece < 8; ++piece) {
+                    uint32_t pk[4];
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        __nv_bfloat162 hh = __floats2bfloat162_rn(__uint_as_float(sv[8 * piece + 2 * q]) * inv,
+                                                                  __uint_as_float(sv[8 * piece + 2 * q + 1]) * inv);
+                        pk[q] = *reinterpret_cast<uint32_t*>(&hh);
+                    }
+                    *reinterpret_cast<uint4*>(dst + 8 * piece) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::);
+    __syncthreads();
+    if (warp == 5) {
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::);
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_s), "r"(kTmemCols));
+    }
+}
+
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiled encode_fn() {
+    static EncodeTiled fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiled)p;
+    }
+    return fn;
+}
+// rows x cols bfloat16, `ld` elements between rows, boxes of 64 columns x box_rows.
+int make_map(CUtensorMap* map, const void* ptr, long long rows, int cols, long long ld, int box_rows) {
+    EncodeTiled enc = encode_fn();
+    if (!enc) return kErrUnsupported;
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    const cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : kErrBadArgument;
+}
+}  // namespace
+
+GTG_API int gtg_attention_tcgen05_status() {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_status, sizeof(int)) != cudaSuccess) return -1;
+    return v;
+}
+
+// What this kernel serves: heads of 64 channels whose keys and values lie in one
+// cache entry as [page][k|v][head][token][channel] (values right after the keys).
+GTG_API int gtg_attention_tcgen05_supports(int hd) { return hd == HD; }
+
+// q: [n_tokens, ldq] with head h at columns h*64; kc, vc: the entry's key and value
+// bases; page_stride: elements between pages.  n_pages: pages of the entry's pool.
+GTG_API int gtg_attention_prefill_tcgen05(const void* q, int ldq, int n_tokens, void* out, int ldo,
+                                          const void* kc, const void* vc, long long page_stride, int n_pages,
+                                          const int* block_table, int table_stride,
+                                          const int* cu_seqlens, const int* slots, const int* start_pos,
+                                          int B, int max_q_len, int n_heads, int n_kv, int hd,
+                                          float scale, int window, cudaStream_t stream) {
+    if (B <= 0 || max_q_len <= 0) return 0;
+    if (hd != HD) return kErrUnsupported;
+    if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv != 0) return kErrBadArgument;
+    if (ldq % 8 || ldo % 8 || ((uintptr_t)q % 16) || ((uintptr_t)out % 16) || ((uintptr_t)kc % 16)) return kErrUnsupported;
+    // keys then values of a page, contiguous: the layout the row arithmetic above assumes
+    const long long kv_rows = 2LL * n_kv * kPageTokens;
+    if (page_stride != kv_rows * HD || (const bf16*)vc != (const bf16*)kc + (long long)n_kv * kPageTokens * HD)
+        return kErrUnsupported;
+    if (B > 65535 || (max_q_len + BQ - 1) / BQ > 65535 || (long long)n_pages * kv_rows > 0x7fffffffLL) return kErrUnsupported;
+    CUtensorMap map_q, map_kv;
+    int st = make_map(&map_q, q, n_tokens, n_heads * HD, ldq, BQ);
+    if (st != 0) return st;
+    st = make_map(&map_kv, kc, (long long)n_pages * kv_rows, HD, HD, kPageTokens);
+    if (st != 0) return st;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    dim3 grid(n_heads, B, (max_q_len + BQ - 1) / BQ);
+    attention_prefill_tc_kernel<<<grid, kThreads, kSmemBytes, stream>>>(map_q, map_kv, (bf16*)out, ldo, block_table,
+        table_stride, cu_seqlens, slots, start_pos, n_heads, n_kv, scale, window);
+    return launch_status();
+}

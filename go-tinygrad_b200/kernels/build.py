@@ -37,6 +37,7 @@ LIBRARIES: Dict[str, str] = {
     "gemm_bf16_tcgen05": "gemm_bf16_tcgen05.cu",
     "gemm_bf16_swapab": "gemm_bf16_swapab.cu",
     "attention_bf16": "attention_bf16.cu",
+    "attention_tcgen05": "attention_tcgen05.cu",
     "attention_decode_static": "attention_decode_static.cu",
 }
 # sources a library's file includes textually (they count for staleness)

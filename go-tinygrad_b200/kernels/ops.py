@@ -44,6 +44,10 @@ _SIGNATURES = {
                                                       _I, _I, _I, _I, _I, _F, _I, _P]),
     "gtg_attention_decode_bf16": ("attention_bf16", [_P, _I, _P, _I, _P, _P, _L, _P, _I, _P, _P,
                                                      _I, _I, _I, _I, _F, _I, _I, _P, _P]),
+    "gtg_attention_tcgen05_supports": ("attention_tcgen05", [_I]),
+    "gtg_attention_tcgen05_status": ("attention_tcgen05", []),
+    "gtg_attention_prefill_tcgen05": ("attention_tcgen05", [_P, _I, _I, _P, _I, _P, _P, _L, _I, _P, _I, _P, _P, _P,
+                                                            _I, _I, _I, _I, _I, _F, _I, _P]),
     "gtg_argmax": ("sampling", [_P, _I, _I, _I, _P, _P]),
     "gtg_sample_temperature": ("sampling", [_P, _I, _I, _I, _F, _U, _P, _P, _P, _P]),
 }
@@ -311,7 +315,8 @@ def bounded_wait_failures() -> int:
     """Non-zero if a kernel ever gave up a bounded wait on its own asynchronous
     copies (it then returned without a result).  Reading it synchronises."""
     total = 0
-    for symbol in ("gtg_gemm_bf16_skinny_status", "gtg_gemm_bf16_tcgen05_status", "gtg_gemm_bf16_swapab_status"):
+    for symbol in ("gtg_gemm_bf16_skinny_status", "gtg_gemm_bf16_tcgen05_status", "gtg_gemm_bf16_swapab_status",
+                   "gtg_attention_tcgen05_status"):
         if _SIGNATURES[symbol][0] in build._LOADED:        # only libraries that have run can have failed
             total += int(_fn(symbol)())
     return total
@@ -349,6 +354,29 @@ def attention_prefill_bf16(q, out, kv, cu_seqlens, slots, start_pos, n_seqs: int
                                              kv.table_stride, _ptr(cu_seqlens), _ptr(slots), _ptr(start_pos),
                                              n_seqs, max_q_len, n_heads, kv.n_kv_heads, kv.head_dim,
                                              float(scale), int(window), _stream()), "attention_prefill_bf16")
+
+
+def attention_tcgen05_supports(kv) -> bool:
+    """The tensor-core prompt attention serves heads of 64 channels whose keys and
+    values lie page by page as [k|v][head][token][channel]."""
+    return (kv.k.dtype == torch.bfloat16 and kv.head_dim == 64
+            and kv.page_stride == 2 * kv.n_kv_heads * 64 * 64
+            and kv.v.data_ptr() - kv.k.data_ptr() == kv.n_kv_heads * 64 * 64 * 2)
+
+
+def attention_prefill_tcgen05(q, out, kv, cu_seqlens, slots, start_pos, n_seqs: int, max_q_len: int,
+                              n_heads: int, scale: float, window: int = 0) -> None:
+    """Prompt attention on tcgen05 (128 queries x one head per thread block)."""
+    _rows2d(q, "attention: q"); _rows2d(out, "attention: out")
+    _need(q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16, "attention_prefill_tcgen05: bfloat16 only")
+    _need(attention_tcgen05_supports(kv),
+          "attention_prefill_tcgen05: needs head_dim 64 and keys and values of a page side by side")
+    _check(_fn("gtg_attention_prefill_tcgen05")(_ptr(q), q.stride(0), q.shape[0], _ptr(out), out.stride(0),
+                                                _ptr(kv.k), _ptr(kv.v), kv.page_stride, kv.k.shape[0],
+                                                _ptr(kv.block_table), kv.table_stride, _ptr(cu_seqlens),
+                                                _ptr(slots), _ptr(start_pos), n_seqs, max_q_len, n_heads,
+                                                kv.n_kv_heads, kv.head_dim, float(scale), int(window), _stream()),
+           "attention_prefill_tcgen05")
 
 
 def attention_decode_scratch_floats(n_seqs: int, n_heads: int, head_dim: int, n_splits: int) -> int:

@@ -116,6 +116,9 @@ class GQAttention(Mixer):
                         n, self.n_heads, self.head_dim, splits), dtype=torch.float32)
                 ops.attention_decode_bf16(q, mixed, kv, ctx.slots, ctx.positions, self.n_heads,
                                           self.scale, window, splits, scratch)
+            elif ops.attention_tcgen05_supports(kv) and qkv.stride(0) % 8 == 0:
+                ops.attention_prefill_tcgen05(q, mixed, kv, ctx.cu_seqlens, ctx.slots, ctx.start_pos,
+                                              ctx.n_seqs, ctx.max_q_len, self.n_heads, self.scale, window)
             else:
                 ops.attention_prefill_bf16(q, mixed, kv, ctx.cu_seqlens, ctx.slots, ctx.start_pos,
                                            ctx.n_seqs, ctx.max_q_len, self.n_heads, self.scale, window)
