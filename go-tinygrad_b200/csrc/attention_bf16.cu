@@ -231,7 +231,6 @@ attention_decode_kernel(const bf16* __restrict__ q, int ldq, bf16* __restrict__ 
                         const int* __restrict__ slots, const int* __restrict__ positions,
                         int n_heads, int n_kv, int hd, float scale, int window,
                         int n_splits, float* __restrict__ part_o, float* __restrict__ part_ml) {
-    chain_wait();
     chain_release();
     constexpr int CPR = DP / 8;
     constexpr int TILE_BYTES = 64 * DP * 2;
@@ -259,13 +258,6 @@ attention_decode_kernel(const bf16* __restrict__ q, int ldq, bf16* __restrict__ 
     const int p_begin = p_first + split * per_split;
     const int p_end = min(p_last + 1, p_begin + per_split);      // exclusive
 
-    // ---- queries of the group (rows beyond `rows` are zero)
-    for (int id = tid; id < 16 * CPR; id += 128) {
-        const int r = id / CPR, c = id % CPR;
-        const bool ok = r < rows && c * 8 < hd;
-        const bf16* src = ok ? q + (size_t)b * ldq + (h0 + r) * hd + c * 8 : q;
-        cp_async16(sQ + swz_offset<DP>(r, c), src, ok ? 16 : 0);
-    }
     auto load_page = [&](int stage, int p) {
         const size_t base = (size_t)table[p] * page_stride + (size_t)kvh * kPageTokens * hd;
         const uint32_t dk = sKV + stage * STAGE_BYTES, dv = dk + TILE_BYTES;
@@ -277,9 +269,24 @@ attention_decode_kernel(const bf16* __restrict__ q, int ldq, bf16* __restrict__ 
             cp_async16(dv + swz_offset<DP>(r, c), vc + off, ok ? 16 : 0);
         }
     };
+    // Pages before the newest one were completed by earlier steps: their copies may
+    // start while the kernels before this one (the projection, the rotation that
+    // writes the newest key and value) are still running.  Positions, slots and the
+    // block table were written before the projection began.
+#pragma unroll
+    for (int s = 0; s < kDecodeStages - 1; ++s)
+        if (p_begin + s < p_end && p_begin + s < p_last) load_page(s, p_begin + s);
+    chain_wait();
+    // ---- queries of the group (rows beyond `rows` are zero)
+    for (int id = tid; id < 16 * CPR; id += 128) {
+        const int r = id / CPR, c = id % CPR;
+        const bool ok = r < rows && c * 8 < hd;
+        const bf16* src = ok ? q + (size_t)b * ldq + (h0 + r) * hd + c * 8 : q;
+        cp_async16(sQ + swz_offset<DP>(r, c), src, ok ? 16 : 0);
+    }
 #pragma unroll
     for (int s = 0; s < kDecodeStages - 1; ++s) {
-        if (p_begin + s < p_end) load_page(s, p_begin + s);
+        if (p_begin + s < p_end && p_begin + s == p_last) load_page(s, p_last);
         cp_async_commit();
     }
 
@@ -424,8 +431,8 @@ attention_decode_kernel(const bf16* __restrict__ q, int ldq, bf16* __restrict__ 
 template <int DP>
 __global__ void attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                          bf16* __restrict__ out, int ldo, int n_heads, int hd, int n_splits) {
-    chain_wait();
     chain_release();
+    chain_wait();
     const int bh = blockIdx.x;                 // sequence * n_heads + head
     const int b = bh / n_heads, head = bh % n_heads;
     const int d = threadIdx.x;

@@ -77,14 +77,19 @@ static inline int launch_status() {
 }
 
 // ---- programmatic dependent launch -------------------------------------------
-// A kernel launched through launch_chained() may begin while the kernel before it
-// in the stream is still running: its blocks become resident and run up to
-// chain_wait(), which returns once that kernel has completed and its writes are
-// visible.  Before chain_wait() a kernel may only do work that depends on nothing
-// a previous kernel wrote (index arithmetic, barrier set-up, copies of weights).
-// chain_release() lets the kernel after this one begin in the same way; it is
-// issued after chain_wait(), so at most two kernels overlap.  Launched without
-// the attribute (the switch off, or a plain <<<>>> launch) both are no-ops.
+// A kernel launched through launch_chained() may begin while the kernels before it
+// in the stream are still running: its blocks become resident and run up to
+// chain_wait(), which returns once the kernel before it has completed and its
+// writes are visible.  Before chain_wait() a kernel may only do work that depends
+// on nothing a previous kernel wrote (index arithmetic, barrier set-up, copies of
+// weights).  chain_release() lets the kernel after this one begin in the same
+// way.  The weight-streaming products issue it after chain_wait(); the small
+// kernels between them (norms, rotation, merges, sampling) issue it first, so
+// that the next product's blocks can move in beside the previous product's last
+// blocks and start their weight copies while it drains.  Completion is still
+// ordered: every kernel waits for its predecessor, which waited for its own.
+// Launched without the attribute (the switch off, or a plain <<<>>> launch) both
+// are no-ops.
 __device__ __forceinline__ void chain_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 __device__ __forceinline__ void chain_release() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
 

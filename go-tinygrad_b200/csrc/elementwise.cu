@@ -13,7 +13,7 @@
 template <typename T>
 __global__ void embed_kernel(const int* __restrict__ tokens, const T* __restrict__ table,
                              float* __restrict__ out, int H, int V) {
-    chain_wait();
+    chain_wait();        // the step's metadata is written here or just before: nothing later may start early
     chain_release();
     const int n = blockIdx.x;
     int tok = tokens[n];
@@ -43,8 +43,8 @@ template <typename T>
 __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __restrict__ pending,
                                    const float* __restrict__ weight, float eps,
                                    T* __restrict__ out, const int* __restrict__ rows, int H) {
-    chain_wait();
     chain_release();
+    chain_wait();
     extern __shared__ float smem[];
     float* row = smem;          // H floats
     float* scratch = smem + H;  // 33 floats
@@ -76,8 +76,8 @@ __global__ void __launch_bounds__(1024)
 add_rmsnorm_bf16_vec_kernel(float* __restrict__ residual, const bf16* __restrict__ pending,
                             const float* __restrict__ weight, float eps, bf16* __restrict__ out,
                             const int* __restrict__ rows, int H) {
-    chain_wait();
     chain_release();
+    chain_wait();
     __shared__ float scratch[33];
     const int i_out = blockIdx.x;
     const int r = rows ? rows[i_out] : i_out;
@@ -159,8 +159,8 @@ GTG_API int gtg_add_rmsnorm(int dtype, float* residual, const void* pending, con
 // (backends/simd/vec.go:52-59).  `gu` holds the gate columns then the up columns.
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int M, int I) {
-    chain_wait();
     chain_release();
+    chain_wait();
     const size_t total = (size_t)M * I;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
          idx += (size_t)gridDim.x * blockDim.x) {
@@ -191,8 +191,8 @@ GTG_API int gtg_swiglu(int dtype, const void* gu, void* out, int M, int I, cudaS
 // (model/llama.go:855-862).  Computed once per step for the step's tokens.
 __global__ void rope_table_kernel(const int* __restrict__ positions, const double* __restrict__ inv_freq,
                                   float2* __restrict__ cos_sin, int N, int half) {
-    chain_wait();
     chain_release();
+    chain_wait();
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= N * half) return;
     const int n = idx / half, i = idx - n * half;
@@ -225,8 +225,8 @@ __global__ void rope_kv_store_kernel(T* __restrict__ qkv, int ld, const float2* 
                                      const int* __restrict__ block_table, int table_stride,
                                      const int* __restrict__ token_seq, const int* __restrict__ slots,
                                      const int* __restrict__ positions) {
-    chain_wait();
     chain_release();
+    chain_wait();
     const int n = blockIdx.x;
     const int half = hd >> 1;
     const int pos = positions[n];
@@ -270,8 +270,8 @@ __global__ void rope_kv_store_bf16_vec_kernel(bf16* __restrict__ qkv, int ld, co
                                               const int* __restrict__ block_table, int table_stride,
                                               const int* __restrict__ token_seq, const int* __restrict__ slots,
                                               const int* __restrict__ positions) {
-    chain_wait();
     chain_release();
+    chain_wait();
     const int n = blockIdx.x;
     const int half = hd >> 1, chunks = half >> 3;
     const int pos = positions[n];
@@ -351,7 +351,7 @@ GTG_API int gtg_rope_kv_store(int dtype, void* qkv, int ld, const float* cos_sin
 // becomes the next input, every position moves on by one and so does every
 // sequence's count of generated tokens (which keys its next random draw).
 __global__ void advance_kernel(int* tokens, int* positions, int* steps, const int* sampled, int B) {
-    chain_wait();
+    chain_wait();        // the step's metadata is written here or just before: nothing later may start early
     chain_release();
     const int b = blockIdx.x * blockDim.x + threadIdx.x;
     if (b < B) { tokens[b] = sampled[b]; positions[b] += 1; steps[b] += 1; }

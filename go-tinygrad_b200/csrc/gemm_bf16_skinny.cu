@@ -28,6 +28,7 @@
 // Any N; K a multiple of 8; output bfloat16 or float.
 #include "mma_helpers.cuh"
 #include <cooperative_groups.h>
+#include <cuda.h>
 
 namespace cg = cooperative_groups;
 
@@ -237,36 +238,63 @@ int launch_typed(const bf16* X, int ldx, const bf16* W, int ldw, OutT* C, int ld
 }
 
 // ---------------------------------------------------------------- persistent form
-// For M <= 16 and K <= 16384.  The grid is one cluster-row of CTAs per SM-sized
-// share of the GPU; CTA (c, rank) walks the row tiles c, c+G, c+2G, ... of its
-// slice of k with two staged tiles: while tile i is multiplied, reduced and
-// stored, the sixteen bulk copies of tile i+1 are already in flight.  The
-// activations of the slice are the same for every row tile, so each thread loads
-// its fragments of X once, into registers, before the loop.
+// For M <= 16, K <= 16384 and K a multiple of 64.  The grid is one cluster-row of
+// CTAs per SM-sized share of the GPU; CTA (c, rank) walks the row tiles c, c+G,
+// c+2G, ... of its slice of k.  A row tile arrives as one or two pieces of 1024
+// values of k, each by ONE tensor copy (TMA) through a ring of three staged
+// pieces: while a piece is multiplied, two more are in flight.  W is described to
+// the copy engine as [k/64][row][64 values] (the middle stride is the row pitch),
+// so a piece lands as sixteen blocks of 16 rows x 128 bytes with the 128-byte
+// swizzle, and the 16-byte fragment reads of rows g and g+1 fall in different
+// banks without padding.  The ring and the sums take less than half of an SM's
+// shared memory on purpose: under programmatic dependent launch the CTAs of the
+// next product of the step become resident beside these and fill their own ring
+// while this product drains, so the memory system stays busy across the boundary
+// between kernels.  The activations of the slice are the same for every row
+// tile, so each thread loads its fragments of X once, into registers.
+constexpr int kPieceK = 1024;                            // values of k per staged piece
+constexpr int kPieceBlocks = kPieceK / (kWarps * 32);    // k blocks of 32 per warp and piece
+constexpr int kPieceBytes = 16 * kPieceK * 2;
+constexpr int kRing = 3;
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];\n"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+
 template <int NT, typename OutT>
-__global__ void __launch_bounds__(kWarps * 32, 1)
-gemm_stream_kernel(const bf16* __restrict__ X, int ldx, const bf16* __restrict__ W, int ldw,
+__global__ void __launch_bounds__(kWarps * 32, 2)
+gemm_stream_kernel(const bf16* __restrict__ X, int ldx, const __grid_constant__ CUtensorMap map_w,
                    OutT* __restrict__ C, int ldc, int M, int N, int K, int k_slice, int epi) {
-    extern __shared__ __align__(128) unsigned char tiles[];     // two tiles of 16 rows, kRowStride apart
-    __shared__ float red[kWarps][16][NT * 8 + 1];               // later reused for the cluster's partial sums
-    __shared__ __align__(8) unsigned long long bar_storage[2];
+    extern __shared__ __align__(1024) unsigned char ring_raw[];
+    __shared__ float red[kWarps][16][NT * 8 + 1];               // also receives the cluster's partial sums
+    __shared__ __align__(8) unsigned long long bar_storage[kRing];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int rank = blockIdx.y, n_ranks = gridDim.y;
-    const int k_begin = rank * k_slice, k_len = min(K, k_begin + k_slice) - k_begin;   // one pass: k_len <= kPassK
+    const int k_begin = rank * k_slice, k_len = min(K, k_begin + k_slice) - k_begin;   // k_len <= kPassK
     const int row_tiles = (N + 15) / 16;
-    const uint32_t bar0 = smem_u32(&bar_storage[0]), tile0 = smem_u32(tiles);
-    if (threadIdx.x == 0) { mbar_init(bar0, 1); mbar_init(bar0 + 8, 1); }
+    const int n_pieces = k_len > kPieceK ? 2 : 1;               // pieces per row tile
+    const int my_tiles = (int)blockIdx.x < row_tiles ? (row_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+    const int n_items = my_tiles * n_pieces;
+    const uint32_t bar0 = smem_u32(&bar_storage[0]);
+    const uint32_t ring0 = (smem_u32(ring_raw) + 1023u) & ~1023u;   // the swizzle pattern repeats every 1024 bytes
+    const unsigned char* ring = ring_raw + (ring0 - smem_u32(ring_raw));
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kRing; ++s) mbar_init(bar0 + 8 * s, 1);
+    }
     __syncthreads();
 
-    auto issue = [&](int tile, int stage) {                     // thread 0 only
-        const uint32_t bar = bar0 + 8 * stage, dst = tile0 + stage * kTileBytes;
-        mbar_expect_tx(bar, 16u * (uint32_t)k_len * 2u);
-        for (int r = 0; r < 16; ++r)                            // rows beyond N repeat the last one; dropped at the store
-            bulk_copy(dst + r * kRowStride, W + (size_t)min(tile * 16 + r, N - 1) * ldw + k_begin,
-                      (uint32_t)k_len * 2u, bar);
+    auto issue = [&](int item) {                                // thread 0 only
+        const int stage = item % kRing;
+        const int tile = blockIdx.x + (item / n_pieces) * gridDim.x, piece = item % n_pieces;
+        const uint32_t bar = bar0 + 8 * stage;
+        mbar_expect_tx(bar, (uint32_t)kPieceBytes);             // rows beyond N and blocks beyond K arrive as zeros
+        tma_load_3d(ring0 + stage * kPieceBytes, &map_w, 0, tile * 16, (k_begin + piece * kPieceK) / 64, bar);
     };
-    if (threadIdx.x == 0 && (int)blockIdx.x < row_tiles) issue(blockIdx.x, 0);
+    if (threadIdx.x == 0) {
+        for (int item = 0; item < kRing && item < n_items; ++item) issue(item);
+    }
 
     // The weights depend on no earlier kernel, so their first copies are already in
     // flight; the activations do.
@@ -274,12 +302,12 @@ gemm_stream_kernel(const bf16* __restrict__ X, int ldx, const bf16* __restrict__
     chain_release();
 
     // this thread's fragments of the activations: 8 k blocks x NT token tiles
-    uint4 xf[kBlocksPerWarp][NT];
-    bool ok[kBlocksPerWarp];
+    uint4 xf[2 * kPieceBlocks][NT];
+    bool ok[2 * kPieceBlocks];
 #pragma unroll
-    for (int u = 0; u < kBlocksPerWarp; ++u) {
-        const int kl = (warp + u * kWarps) * 32 + t * 8;
-        ok[u] = kl < k_len;
+    for (int u = 0; u < 2 * kPieceBlocks; ++u) {
+        const int kl = (u / kPieceBlocks) * kPieceK + (warp + (u % kPieceBlocks) * kWarps) * 32 + t * 8;
+        ok[u] = kl < k_len;                                     // beyond it the piece holds a neighbour's k or zeros
 #pragma unroll
         for (int j = 0; j < NT; ++j)
             xf[u][j] = ok[u] ? ld_cached16(X + (size_t)min(j * 8 + g, M - 1) * ldx + k_begin + kl)
@@ -287,33 +315,42 @@ gemm_stream_kernel(const bf16* __restrict__ X, int ldx, const bf16* __restrict__
     }
 
     cg::cluster_group cluster = cg::this_cluster();
-    uint32_t phases = 0;                                        // bit s: parity of stage s
     bool failed = false;
-    for (int tile = blockIdx.x, it = 0; tile < row_tiles; tile += gridDim.x, ++it) {
-        const int stage = it & 1;
-        if (threadIdx.x == 0 && tile + (int)gridDim.x < row_tiles) issue(tile + gridDim.x, stage ^ 1);
-        if (!mbar_wait(bar0 + 8 * stage, (phases >> stage) & 1u)) failed = true;   // keep going: peers wait at the barriers below
-        phases ^= 1u << stage;
-        const unsigned char* tl = tiles + stage * kTileBytes;
-        float acc[NT][4];
+    float acc[NT][4];
+    for (int item = 0; item < n_items; ++item) {
+        const int stage = item % kRing, piece = item % n_pieces;
+        if (!mbar_wait(bar0 + 8 * stage, (uint32_t)(item / kRing) & 1u)) failed = true;   // keep going: peers wait at the barriers below
+        const unsigned char* tl = ring + stage * kPieceBytes;
+        if (piece == 0) {
 #pragma unroll
-        for (int j = 0; j < NT; ++j) { acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f; }
-#pragma unroll
-        for (int u = 0; u < kBlocksPerWarp; ++u) {
-            const int kl = (warp + u * kWarps) * 32 + t * 8;
-            uint4 wa = make_uint4(0, 0, 0, 0), wb = wa;
-            if (ok[u] && !failed) {
-                wa = *reinterpret_cast<const uint4*>(tl + g * kRowStride + kl * 2);
-                wb = *reinterpret_cast<const uint4*>(tl + (g + 8) * kRowStride + kl * 2);
-            }
-            const uint32_t a_lo[4] = {wa.x, wb.x, wa.y, wb.y};
-            const uint32_t a_hi[4] = {wa.z, wb.z, wa.w, wb.w};
-#pragma unroll
-            for (int j = 0; j < NT; ++j) {
-                mma_bf16_16816(acc[j], a_lo, xf[u][j].x, xf[u][j].y);
-                mma_bf16_16816(acc[j], a_hi, xf[u][j].z, xf[u][j].w);
-            }
+            for (int j = 0; j < NT; ++j) { acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f; }
         }
+        auto multiply = [&](int first) {
+#pragma unroll
+            for (int v = 0; v < kPieceBlocks; ++v) {
+                const int u = first + v;
+                const int blk32 = warp + v * kWarps;                       // 32 values of k: half of a 64-value block
+                // block [blk32/2] of 16 rows x 128 bytes; 16-byte chunk (blk32&1)*4 + t of row g, swizzled by the row
+                const unsigned char* at = tl + (blk32 >> 1) * 2048 + g * 128 + (((((blk32 & 1) << 2) | t) ^ (g & 7)) << 4);
+                uint4 wa = make_uint4(0, 0, 0, 0), wb = wa;
+                if (ok[u] && !failed) {
+                    wa = *reinterpret_cast<const uint4*>(at);
+                    wb = *reinterpret_cast<const uint4*>(at + 8 * 128);   // row g + 8: the same swizzle
+                }
+                const uint32_t a_lo[4] = {wa.x, wb.x, wa.y, wb.y};
+                const uint32_t a_hi[4] = {wa.z, wb.z, wa.w, wb.w};
+#pragma unroll
+                for (int j = 0; j < NT; ++j) {
+                    mma_bf16_16816(acc[j], a_lo, xf[u][j].x, xf[u][j].y);
+                    mma_bf16_16816(acc[j], a_hi, xf[u][j].z, xf[u][j].w);
+                }
+            }
+        };
+        if (piece == 0) multiply(0); else multiply(kPieceBlocks);   // register indices stay constant
+        __syncthreads();                                            // the piece has been read: its stage is free,
+        if (threadIdx.x == 0 && item + kRing < n_items) issue(item + kRing);   // and so is `red` (read before this barrier)
+        if (piece != n_pieces - 1) continue;
+        const int tile = blockIdx.x + (item / n_pieces) * gridDim.x;
 #pragma unroll
         for (int j = 0; j < NT; ++j) {
             red[warp][g][j * 8 + t * 2] = acc[j][0];
@@ -343,20 +380,51 @@ gemm_stream_kernel(const bf16* __restrict__ X, int ldx, const bf16* __restrict__
         }
         if (rank == 0 && mine_valid)                              // uniform per warp: whole warps are valid or not
             store_feature<OutT>(C, ldc, m, tile * 16, r, M, N, mine, epi);
-        __syncthreads();                                          // `red` and the stage are free again
     }
     if (failed && threadIdx.x == 0) atomicExch(&g_status, 1);
 }
 
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiled encode_fn() {
+    static EncodeTiled fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiled)p;
+    }
+    return fn;
+}
+
+// W[N, K] (row pitch ldw) as [K/64][N][64]: boxes of 16 blocks x 16 rows x 64 values.
+bool stream_map(CUtensorMap* map, const bf16* W, int ldw, int N, int K) {
+    EncodeTiled enc = encode_fn();
+    if (!enc) return false;
+    const cuuint64_t dims[3] = {64, (cuuint64_t)N, (cuuint64_t)(K / 64)};
+    const cuuint64_t strides[2] = {(cuuint64_t)ldw * 2, 128};
+    const cuuint32_t box[3] = {64, 16, kPieceK / 64};
+    const cuuint32_t elem[3] = {1, 1, 1};
+    return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<bf16*>(W), dims, strides, box, elem,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// kErrUnsupported when this form does not serve the sizes (the caller then takes the other one).
 template <int NT, typename OutT>
 int launch_stream(const bf16* X, int ldx, const bf16* W, int ldw, OutT* C, int ldc,
                   int M, int N, int K, int epi, cudaStream_t stream) {
+    if (K % 64) return kErrUnsupported;
     int ranks = 1;
     while (ranks < kMaxCluster && (K + ranks - 1) / ranks > kPassK) ranks *= 2;
-    const int k_slice = (((K + ranks - 1) / ranks) + 31) / 32 * 32;
+    const int k_slice = (((K + ranks - 1) / ranks) + 63) / 64 * 64;
     if (k_slice > kPassK) return kErrUnsupported;
+    CUtensorMap map_w;
+    if (!stream_map(&map_w, W, ldw, N, K)) return kErrUnsupported;
     const int row_tiles = (N + 15) / 16;
-    const int smem = 2 * kTileBytes;
+    const int smem = kRing * kPieceBytes + 1024;
     static bool configured = false;
     if (!configured) {
         cudaError_t ce = cudaFuncSetAttribute(gemm_stream_kernel<NT, OutT>,
@@ -364,7 +432,7 @@ int launch_stream(const bf16* X, int ldx, const bf16* W, int ldw, OutT* C, int l
         if (ce != cudaSuccess) return (int)ce;
         configured = true;
     }
-    int per_rank = 148 / ranks;                 // one CTA per SM
+    int per_rank = 2 * 148 / ranks;             // two CTAs per SM: six pieces in flight; a finished CTA makes room for the next kernel
     if (per_rank < 1) per_rank = 1;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(row_tiles < per_rank ? row_tiles : per_rank, ranks, 1);
@@ -380,7 +448,7 @@ int launch_stream(const bf16* X, int ldx, const bf16* W, int ldw, OutT* C, int l
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = g_chained_launch ? 2 : 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_stream_kernel<NT, OutT>, X, ldx, W, ldw, C, ldc, M, N, K, k_slice, epi);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_stream_kernel<NT, OutT>, X, ldx, map_w, C, ldc, M, N, K, k_slice, epi);
     if (e != cudaSuccess) return (int)e;
     return launch_status();
 }
@@ -390,8 +458,9 @@ int launch(const bf16* X, int ldx, const bf16* W, int ldw, void* C, int ldc, int
            int M, int N, int K, int epi, cudaStream_t stream) {
     if constexpr (NT <= 2) {
         if (K <= kMaxCluster * kPassK) {
-            if (out_f32) return launch_stream<NT, float>(X, ldx, W, ldw, (float*)C, ldc, M, N, K, epi, stream);
-            return launch_stream<NT, bf16>(X, ldx, W, ldw, (bf16*)C, ldc, M, N, K, epi, stream);
+            const int st = out_f32 ? launch_stream<NT, float>(X, ldx, W, ldw, (float*)C, ldc, M, N, K, epi, stream)
+                                   : launch_stream<NT, bf16>(X, ldx, W, ldw, (bf16*)C, ldc, M, N, K, epi, stream);
+            if (st != kErrUnsupported) return st;
         }
     }
     if (out_f32) return launch_typed<NT, float>(X, ldx, W, ldw, (float*)C, ldc, M, N, K, epi, stream);

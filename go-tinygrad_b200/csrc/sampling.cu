@@ -14,8 +14,8 @@ constexpr int kThreads = 256;
 
 __global__ void __launch_bounds__(kThreads)
 argmax_kernel(const float* __restrict__ logits, int ld, int V, int* __restrict__ out) {
-    chain_wait();
     chain_release();
+    chain_wait();
     __shared__ float bv[kThreads];
     __shared__ int bi[kThreads];
     const float* row = logits + (size_t)blockIdx.x * ld;
@@ -61,8 +61,8 @@ __global__ void __launch_bounds__(kThreads)
 sample_temperature_kernel(const float* __restrict__ logits, int ld, int V, float inv_temperature,
                           unsigned long long seed, const int* __restrict__ sequence_ids,
                           const int* __restrict__ steps, int* __restrict__ out) {
-    chain_wait();
     chain_release();
+    chain_wait();
     __shared__ float scratch[33];
     __shared__ float seg_sum[kThreads];
     __shared__ int chosen_seg;
