@@ -1,27 +1,30 @@
 // Causal grouped-query prefill attention on the fifth-generation tensor cores,
 // for heads of 64 channels, over the paged cache.
 //
-// One CTA per (128-query tile, query head, sequence).  Per cache page (64 keys):
-//   S  = Q K^T      tcgen05.mma 128 x 64 x 64, Q and the key page in shared memory
-//                   (TMA, 128-byte swizzle, both K-major), S in TMEM (two tiles)
-//   P  = softmax    four warps, one thread per query row: tcgen05.ld its 64 scores,
-//                   mask (diagonal and window-edge pages only), running max and sum
-//                   in float, write the row of P as bfloat16 into shared memory in
-//                   the operand layout (no shuffles: a row lives in one thread)
-//   O += P V        tcgen05.mma 128 x 64 x 64 with the value page as the MN-major B
-//                   operand -- the page's [key][channel] rows are that layout as
-//                   they lie in the cache -- accumulating in TMEM over all pages
-// The running maximum m of a row is only raised when the page's maximum exceeds it
-// by more than 2^8; until then P = exp2(s - m) is taken against the older m (at
-// most 256, exact in float and as good as any other scale in bfloat16) and the sum
-// uses the same m, so the quotient O / l is unchanged.  Raising m multiplies the
-// row of O in TMEM by exp2(m_old - m_new) (tcgen05.ld / st by the row's thread, after
-// the previous page's product has completed); it happens in the first pages and
-// rarely later, so the steady state has no dependence of the softmax on the PV
-// products.  Roles: warps 0-3 softmax and output, warp 4 issues the TMA loads (four
-// stages of key+value pages), warp 5 allocates TMEM and issues the MMAs; the next
-// page's S is issued before this page's P is waited for, so it runs under this
-// page's softmax.  Every mbarrier wait is bounded (status word as in the products).
+// One CTA per (128-query tile, query head, sequence).  Per step of two cache pages
+// (128 keys):
+//   S  = Q K^T      tcgen05.mma 128 x 128 x 64: Q and the two key pages in shared
+//                   memory (TMA, 128-byte swizzle, both K-major), S in TMEM
+//   P  = softmax    four warps, one thread per query row: tcgen05.ld its 128 scores
+//                   into registers and hand the TMEM tile back at once (the next
+//                   step's S runs under this step's softmax); mask (diagonal and
+//                   window-edge steps only), running max and sum in float; the row
+//                   of P goes back to TMEM as packed bfloat16 (tcgen05.st)
+//   O += P V        tcgen05.mma 128 x 64 x 128 with A = P read from TMEM and the
+//                   value pages as the MN-major B operand -- a page's
+//                   [key][channel] rows are that layout as they lie in the cache --
+//                   accumulating in TMEM over all steps
+// Neither P nor O passes through shared memory, whose bandwidth is what limits
+// 64-wide tiles on this machine.  The running maximum m of a row is only raised
+// when the step's maximum exceeds it by more than 2^8; until then P = exp2(s - m)
+// is taken against the older m (at most 256, exact in float and as good as any
+// other scale in bfloat16) and the sum uses the same m, so the quotient O / l is
+// unchanged.  Raising m multiplies the row of O in TMEM by exp2(m_old - m_new)
+// (tcgen05.ld / st by the row's thread, after the previous product has completed);
+// it happens in the first steps and rarely later.  Roles: warps 0-3 softmax and
+// output, warp 4 issues the TMA loads (three stages of 2 key + 2 value pages),
+// warp 5 allocates TMEM and issues the MMAs.  Every mbarrier wait is bounded
+// (status word as in the products).
 #include "common.cuh"
 #include <cuda.h>
 #include <math.h>
@@ -29,16 +32,18 @@
 namespace {
 constexpr int BQ = 128;                 // query rows per CTA
 constexpr int HD = 64;                  // head size this kernel serves
+constexpr int BK = 2 * kPageTokens;     // keys per step
 constexpr int kThreads = 192;
-constexpr int kStages = 4;              // key+value pages in flight
-constexpr int kQBytes = BQ * HD * 2, kPageBytes = kPageTokens * HD * 2, kPBytes = BQ * kPageTokens * 2;
-constexpr int kTmemCols = 256;          // S twice (64 each), O (64); a power of two
+constexpr int kStages = 3;              // steps of keys and values in flight
+constexpr int kQBytes = BQ * HD * 2, kPageBytes = kPageTokens * HD * 2;
+constexpr int kStageBytes = 4 * kPageBytes;      // K page A, K page B, V page A, V page B
+constexpr int kTmemCols = 256;          // S 128, O 64, P 64 (128 keys as bfloat16 pairs)
 constexpr unsigned kSpinLimit = 1u << 22;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRaiseBy = 8.0f;        // the running maximum follows only jumps above 2^8
-// shared memory: Q | stages of (K, V) | P[2] | barriers.  Two CTAs fit one SM.
-constexpr int kOffKV = kQBytes, kOffP = kOffKV + kStages * 2 * kPageBytes;
-constexpr int kOffBar = kOffP + 2 * kPBytes;
+// shared memory: Q | stages | barriers.  Two CTAs fit one SM.
+constexpr int kOffKV = kQBytes;
+constexpr int kOffBar = kOffKV + kStages * kStageBytes;
 constexpr int kSmemBytes = kOffBar + 256;
 
 __device__ int g_status = 0;
@@ -87,10 +92,17 @@ __host__ __device__ constexpr uint32_t umma_idesc(int m, int n, int b_mn_major) 
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)b_mn_major << 16) |
            ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
-__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+// D[tmem] (+)= A[shared] B[shared]
+__device__ __forceinline__ void umma_ss(uint32_t tmem_d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
     asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
                  "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
                  ::"r"(tmem_d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+}
+// D[tmem] (+)= A[tmem] B[shared]
+__device__ __forceinline__ void umma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
+                 ::"r"(tmem_d), "r"(tmem_a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
@@ -114,6 +126,16 @@ __device__ __forceinline__ void tmem_st32(uint32_t addr, const uint32_t* r) {
                    "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
                    "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
                    "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_ld8(uint32_t addr, uint32_t* r) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(addr));
+}
+__device__ __forceinline__ void tmem_st8(uint32_t addr, const uint32_t* r) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};\n"
+                 ::"r"(addr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
                  : "memory");
 }
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -144,12 +166,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         return;
     }
     const uint32_t bars = base + kOffBar;
-    const uint32_t q_full = bars;
-    auto kv_full = [&](int s) { return bars + 8u + 8u * s; };
-    auto kv_empty = [&](int s) { return bars + 40u + 8u * s; };
-    auto s_full = [&](int s) { return bars + 72u + 8u * s; };
-    auto p_full = [&](int s) { return bars + 88u + 8u * s; };
-    auto pv_done = [&](int s) { return bars + 104u + 8u * s; };
+    const uint32_t q_full = bars, s_full = bars + 8, s_free = bars + 16, p_full = bars + 24, pv_done = bars + 32;
+    auto kv_full = [&](int s) { return bars + 40u + 8u * s; };
+    auto kv_empty = [&](int s) { return bars + 40u + 8u * kStages + 8u * s; };
     uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + kOffBar + 128);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kOffBar + 136);
 
@@ -161,16 +180,15 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const int k_max = start + tile * BQ + rows_here - 1;         // last key any row of the tile sees
     const int k_min = window > 0 ? max(0, start + tile * BQ - window + 1) : 0;
     const int j_lo = k_min / kPageTokens, j_hi = k_max / kPageTokens;
-    const int n_pages = j_hi - j_lo + 1;
+    const int n_steps = (j_hi - j_lo + 2) / 2;                   // two pages per step
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
+        mbar_init(s_full, 1);
+        mbar_init(s_free, 4);                                    // one arrival per softmax warp
+        mbar_init(p_full, 4);
+        mbar_init(pv_done, 1);
         for (int s = 0; s < kStages; ++s) { mbar_init(kv_full(s), 1); mbar_init(kv_empty(s), 1); }
-        for (int s = 0; s < 2; ++s) {
-            mbar_init(s_full(s), 1);
-            mbar_init(p_full(s), 4);                             // one arrival per softmax warp
-            mbar_init(pv_done(s), 1);
-        }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::);
     }
@@ -182,59 +200,59 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::);
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::);
-    const uint32_t tmem_s = *tmem_holder, tmem_o = tmem_s + 128;   // S of page i at columns 64 * (i & 1)
+    const uint32_t tmem_s = *tmem_holder, tmem_o = tmem_s + 128, tmem_p = tmem_s + 192;
 
     if (warp == 4) {
         // ------------------------------------------------------------ TMA producer
         if (lane == 0) {
             mbar_expect_tx(q_full, kQBytes);
             tma_load_2d(base, &map_q, h * HD, q_begin + tile * BQ, q_full);
-            for (int i = 0; i < n_pages; ++i) {
+            for (int i = 0; i < n_steps; ++i) {
                 const int s = i % kStages;
                 if (!mbar_wait(kv_empty(s), (((uint32_t)i / kStages) & 1u) ^ 1u, abort_flag)) break;
-                const int page = table[j_lo + i];
-                const int row_k = ((page * 2 + 0) * n_kv + kvh) * kPageTokens;
-                const int row_v = ((page * 2 + 1) * n_kv + kvh) * kPageTokens;
-                const uint32_t dst = base + kOffKV + s * 2 * kPageBytes;
-                mbar_expect_tx(kv_full(s), 2 * kPageBytes);
-                tma_load_2d(dst, &map_kv, 0, row_k, kv_full(s));
-                tma_load_2d(dst + kPageBytes, &map_kv, 0, row_v, kv_full(s));
+                const int ja = j_lo + 2 * i;
+                // a missing second page is the first one again: finite values under keys that no row sees
+                const int page_a = table[ja], page_b = ja + 1 <= j_hi ? table[ja + 1] : page_a;
+                const uint32_t dst = base + kOffKV + s * kStageBytes;
+                mbar_expect_tx(kv_full(s), kStageBytes);
+                tma_load_2d(dst, &map_kv, 0, ((page_a * 2 + 0) * n_kv + kvh) * kPageTokens, kv_full(s));
+                tma_load_2d(dst + kPageBytes, &map_kv, 0, ((page_b * 2 + 0) * n_kv + kvh) * kPageTokens, kv_full(s));
+                tma_load_2d(dst + 2 * kPageBytes, &map_kv, 0, ((page_a * 2 + 1) * n_kv + kvh) * kPageTokens, kv_full(s));
+                tma_load_2d(dst + 3 * kPageBytes, &map_kv, 0, ((page_b * 2 + 1) * n_kv + kvh) * kPageTokens, kv_full(s));
             }
         }
     } else if (warp == 5) {
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
-            const uint32_t idesc_s = umma_idesc(BQ, kPageTokens, 0);      // S[128 x 64 keys], key page K-major
-            const uint32_t idesc_pv = umma_idesc(BQ, HD, 1);              // O[128 x 64 channels], value page MN-major
+            const uint32_t idesc_s = umma_idesc(BQ, BK, 0);               // S[128 x 128 keys], key pages K-major
+            const uint32_t idesc_pv = umma_idesc(BQ, HD, 1);              // O[128 x 64 channels], value pages MN-major
             bool ok = mbar_wait(q_full, 0, abort_flag);
             auto issue_s = [&](int i) {
                 const int s = i % kStages;
                 if (!mbar_wait(kv_full(s), ((uint32_t)i / kStages) & 1u, abort_flag)) return false;
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::);
-                const uint64_t dq = umma_desc(base), dk = umma_desc(base + kOffKV + s * 2 * kPageBytes);
+                const uint64_t dq = umma_desc(base), dk = umma_desc(base + kOffKV + s * kStageBytes);
 #pragma unroll
-                for (int kk = 0; kk < HD / 16; ++kk)
-                    umma(tmem_s + 64 * (i & 1), dq + 2 * kk, dk + 2 * kk, idesc_s, kk > 0 ? 1u : 0u);
-                umma_commit(s_full(i & 1));
+                for (int kk = 0; kk < HD / 16; ++kk) umma_ss(tmem_s, dq + 2 * kk, dk + 2 * kk, idesc_s, kk > 0 ? 1u : 0u);
+                umma_commit(s_full);
                 return true;
             };
             if (ok) ok = issue_s(0);
-            for (int i = 0; i < n_pages && ok; ++i) {
-                // the next page's scores run under this page's softmax: their TMEM tile was
-                // released by p_full of page i - 1
-                if (i + 1 < n_pages) ok = issue_s(i + 1);
-                if (!ok) break;
-                ok = mbar_wait(p_full(i & 1), ((uint32_t)i >> 1) & 1u, abort_flag);   // P_i written, S_i read, O rescaled
+            for (int i = 0; i < n_steps && ok; ++i) {
+                if (i + 1 < n_steps) {                                     // S_i is in registers: the tile takes S_{i+1}
+                    ok = mbar_wait(s_free, (uint32_t)i & 1u, abort_flag) && issue_s(i + 1);
+                    if (!ok) break;
+                }
+                ok = mbar_wait(p_full, (uint32_t)i & 1u, abort_flag);     // P_i is in TMEM, O rescaled if it had to be
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::);
                 const int s = i % kStages;
-                const uint64_t dp = umma_desc(base + kOffP + (i & 1) * kPBytes);
-                const uint64_t dv = umma_desc(base + kOffKV + s * 2 * kPageBytes + kPageBytes);
+                const uint64_t dv = umma_desc(base + kOffKV + s * kStageBytes + 2 * kPageBytes);
 #pragma unroll
-                for (int kk = 0; kk < kPageTokens / 16; ++kk)              // 16 keys per step: P 32 bytes on, V two 8-key groups on
-                    umma(tmem_o, dp + 2 * kk, dv + (uint64_t)(2 * 1024 >> 4) * kk, idesc_pv, (i > 0 || kk > 0) ? 1u : 0u);
+                for (int kk = 0; kk < BK / 16; ++kk)                       // 16 keys per step: 8 columns of P, two 8-key groups of V
+                    umma_ts(tmem_o, tmem_p + 8 * kk, dv + (uint64_t)(2 * 1024 >> 4) * kk, idesc_pv, (i > 0 || kk > 0) ? 1u : 0u);
                 umma_commit(kv_empty(s));                                   // K_i and V_i have been read
-                umma_commit(pv_done(i & 1));                                // P_i has been read, O holds pages 0..i
+                umma_commit(pv_done);                                       // P_i has been read, O holds steps 0..i
             }
         }
     } else {
@@ -245,29 +263,31 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
         const float sl2 = scale * kLog2e;
         float m_run = -INFINITY, l_run = 0.f;
-        uint32_t sv[64];
+        uint32_t sv[BK];
         bool ok = true;
-        for (int i = 0; i < n_pages; ++i) {
-            const int j = j_lo + i;
-            ok = __all_sync(full, mbar_wait(s_full(i & 1), ((uint32_t)i >> 1) & 1u, abort_flag));
+        for (int i = 0; i < n_steps; ++i) {
+            const int key0 = (j_lo + 2 * i) * kPageTokens;       // position of the step's first key
+            ok = __all_sync(full, mbar_wait(s_full, (uint32_t)i & 1u, abort_flag));
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::);
-            tmem_ld32(tmem_s + 64 * (i & 1) + lane_off, sv);
-            tmem_ld32(tmem_s + 64 * (i & 1) + lane_off + 32, sv + 32);
+#pragma unroll
+            for (int c = 0; c < BK / 32; ++c) tmem_ld32(tmem_s + lane_off + 32 * c, sv + 32 * c);
             asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-            const bool all_visible = (j * kPageTokens + kPageTokens - 1 <= pos) &&
-                                     (window <= 0 || j * kPageTokens > pos - window);
+            asm volatile("tcgen05.fence::before_thread_sync;\n" ::);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(s_free);                  // S_i is in registers: the tile takes S_{i+1}
+            const bool all_visible = (key0 + BK - 1 <= pos) && (window <= 0 || key0 > pos - window);
             if (!all_visible) {
 #pragma unroll
-                for (int c = 0; c < 64; ++c) {
-                    const int key = j * kPageTokens + c;
+                for (int c = 0; c < BK; ++c) {
+                    const int key = key0 + c;
                     const bool vis = key <= pos && (window <= 0 || key > pos - window);
                     if (!vis) sv[c] = __float_as_uint(-INFINITY);
                 }
             }
             float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-            for (int c = 0; c < 64; c += 4) {
+            for (int c = 0; c < BK; c += 4) {
                 mx0 = fmaxf(mx0, __uint_as_float(sv[c]));
                 mx1 = fmaxf(mx1, __uint_as_float(sv[c + 1]));
                 mx2 = fmaxf(mx2, __uint_as_float(sv[c + 2]));
@@ -278,59 +298,52 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 m_run = m_page;                                  // the first product overwrites O
             } else {
                 const bool raise = m_page > m_run + kRaiseBy;    // also: the first visible key of a row
-                if (__any_sync(full, raise)) {
+                const bool any_raise = __any_sync(full, raise);
+                // P_i goes where P_{i-1} was, and O may only be touched between products
+                ok = __all_sync(full, mbar_wait(pv_done, (uint32_t)(i - 1) & 1u, abort_flag));
+                if (!ok) break;
+                if (any_raise) {
                     float corr = 1.0f;
                     if (raise) {
                         corr = fast_exp2(m_run - m_page);        // 0 when the row had seen nothing
                         m_run = m_page;
                         l_run *= corr;
                     }
-                    // O holds pages 0..i-1 once the previous product has completed
-                    ok = __all_sync(full, mbar_wait(pv_done((i - 1) & 1), ((uint32_t)(i - 1) >> 1) & 1u, abort_flag));
-                    if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;\n" ::);
-                    uint32_t ov[32];
-#pragma unroll
-                    for (int half = 0; half < 2; ++half) {
-                        tmem_ld32(tmem_o + lane_off + 32 * half, ov);
+                    uint32_t ov[8];                              // few registers: the scores are live
+#pragma unroll 1
+                    for (int part = 0; part < HD / 8; ++part) {
+                        tmem_ld8(tmem_o + lane_off + 8 * part, ov);
                         asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 #pragma unroll
-                        for (int d = 0; d < 32; ++d) ov[d] = __float_as_uint(__uint_as_float(ov[d]) * corr);
-                        tmem_st32(tmem_o + lane_off + 32 * half, ov);
+                        for (int d = 0; d < 8; ++d) ov[d] = __float_as_uint(__uint_as_float(ov[d]) * corr);
+                        tmem_st8(tmem_o + lane_off + 8 * part, ov);
                     }
-                    asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
                 }
             }
             const float m_use = m_run == -INFINITY ? 0.f : m_run;
-            // P_i goes where P_{i-2} was: its product must have completed
-            if (i >= 2) {
-                ok = __all_sync(full, mbar_wait(pv_done(i & 1), ((uint32_t)(i - 2) >> 1) & 1u, abort_flag));
-                if (!ok) break;
-            }
-            unsigned char* prow = smem + kOffP + (i & 1) * kPBytes + r * 128;
             float l0 = 0.f, l1 = 0.f;
-            // the row of P: 64 bfloat16 = eight 16-byte pieces, piece c at (c ^ (r & 7))
+            // the row of P: 128 bfloat16 as 64 packed columns, written 32 columns at a time
 #pragma unroll
-            for (int piece = 0; piece < 8; ++piece) {
-                uint32_t pk[4];
+            for (int half = 0; half < 2; ++half) {
 #pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const float p0 = fast_exp2(fmaf(__uint_as_float(sv[8 * piece + 2 * q]), sl2, -m_use));
-                    const float p1 = fast_exp2(fmaf(__uint_as_float(sv[8 * piece + 2 * q + 1]), sl2, -m_use));
+                for (int c = 0; c < 32; ++c) {
+                    const float p0 = fast_exp2(fmaf(__uint_as_float(sv[64 * half + 2 * c]), sl2, -m_use));
+                    const float p1 = fast_exp2(fmaf(__uint_as_float(sv[64 * half + 2 * c + 1]), sl2, -m_use));
                     l0 += p0;
                     l1 += p1;
                     __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
-                    pk[q] = *reinterpret_cast<uint32_t*>(&hh);
+                    sv[64 * half + c] = *reinterpret_cast<uint32_t*>(&hh);   // the scores at and below this index are done with
                 }
-                *reinterpret_cast<uint4*>(prow + ((piece ^ (r & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                tmem_st32(tmem_p + lane_off + 32 * half, sv + 64 * half);
             }
             l_run += l0 + l1;
-            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // P written by threads, read by the tensor core
+            asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::);
             __syncwarp();
-            if (lane == 0) mbar_arrive(p_full(i & 1));
+            if (lane == 0) mbar_arrive(p_full);
         }
-        if (ok) ok = __all_sync(full, mbar_wait(pv_done((n_pages - 1) & 1), ((uint32_t)(n_pages - 1) >> 1) & 1u, abort_flag));
+        if (ok) ok = __all_sync(full, mbar_wait(pv_done, (uint32_t)(n_steps - 1) & 1u, abort_flag));
         if (ok) {
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::);
             tmem_ld32(tmem_o + lane_off, sv);
@@ -341,14 +354,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 bf16* dst = out + (size_t)(q_begin + tile * BQ + r) * ldo + h * HD;
 #pragma unroll
                 for (int piece = 0; piece < 8; ++piece) {
-                    uint32_t pk[4];
+                    uint32_t o4[4];
 #pragma unroll
                     for (int q = 0; q < 4; ++q) {
                         __nv_bfloat162 hh = __floats2bfloat162_rn(__uint_as_float(sv[8 * piece + 2 * q]) * inv,
                                                                   __uint_as_float(sv[8 * piece + 2 * q + 1]) * inv);
-                        pk[q] = *reinterpret_cast<uint32_t*>(&hh);
+                        o4[q] = *reinterpret_cast<uint32_t*>(&hh);
                     }
-                    *reinterpret_cast<uint4*>(dst + 8 * piece) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                    *reinterpret_cast<uint4*>(dst + 8 * piece) = make_uint4(o4[0], o4[1], o4[2], o4[3]);
                 }
             }
         }
