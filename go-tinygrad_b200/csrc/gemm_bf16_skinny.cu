@@ -417,13 +417,15 @@ template <int NT, typename OutT>
 int launch_stream(const bf16* X, int ldx, const bf16* W, int ldw, OutT* C, int ldc,
                   int M, int N, int K, int epi, cudaStream_t stream) {
     if (K % 64) return kErrUnsupported;
+    const int row_tiles = (N + 15) / 16;
     int ranks = 1;
     while (ranks < kMaxCluster && (K + ranks - 1) / ranks > kPassK) ranks *= 2;
+    // few rows: split k further (down to one piece per rank) until every SM has two blocks to run
+    while (ranks < kMaxCluster && row_tiles * ranks < 2 * 148 && (K + 2 * ranks - 1) / (2 * ranks) >= kPieceK) ranks *= 2;
     const int k_slice = (((K + ranks - 1) / ranks) + 63) / 64 * 64;
     if (k_slice > kPassK) return kErrUnsupported;
     CUtensorMap map_w;
     if (!stream_map(&map_w, W, ldw, N, K)) return kErrUnsupported;
-    const int row_tiles = (N + 15) / 16;
     const int smem = kRing * kPieceBytes + 1024;
     static bool configured = false;
     if (!configured) {
