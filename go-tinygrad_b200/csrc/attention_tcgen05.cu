@@ -201,6 +201,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::);
     const uint32_t tmem_s = *tmem_holder, tmem_o = tmem_s + 128, tmem_p = tmem_s + 192;
+    chain_wait();                                                // queries, keys and values come from the kernel before
+    chain_release();
 
     if (warp == 4) {
         // ------------------------------------------------------------ TMA producer
@@ -442,7 +444,7 @@ GTG_API int gtg_attention_prefill_tcgen05(const void* q, int ldq, int n_tokens, 
         configured = true;
     }
     dim3 grid(n_heads, B, (max_q_len + BQ - 1) / BQ);
-    attention_prefill_tc_kernel<<<grid, kThreads, kSmemBytes, stream>>>(map_q, map_kv, (bf16*)out, ldo, block_table,
-        table_stride, cu_seqlens, slots, start_pos, n_heads, n_kv, scale, window);
-    return launch_status();
+    return launch_chained(attention_prefill_tc_kernel, grid, dim3(kThreads), (size_t)kSmemBytes, stream, map_q, map_kv,
+                          (bf16*)out, ldo, block_table, table_stride, cu_seqlens, slots, start_pos, n_heads, n_kv,
+                          scale, window);
 }

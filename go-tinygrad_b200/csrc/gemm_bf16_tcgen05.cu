@@ -162,6 +162,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::);
     const uint32_t tmem_base = *tmem_holder;
+    // Barriers and tensor memory are set up; from here on the kernel reads and
+    // writes what the kernel before it may still be using.
+    chain_wait();
+    chain_release();
 
     if (warp == 4) {
         // ------------------------------------------------------------ producer
@@ -401,8 +405,8 @@ GTG_API int gtg_gemm_bf16_tcgen05(const void* A, int lda, const void* W, int ldw
     }
     const int grid = (int)(tiles < sms ? tiles : sms);
     if (out_f32)
-        gemm_tcgen05_kernel<float><<<grid, kThreads, kSmemBytes, stream>>>(map_a, map_w, map_c, use_store_map, (float*)C, ldc, M, N, K, epilogue);
-    else
-        gemm_tcgen05_kernel<bf16><<<grid, kThreads, kSmemBytes, stream>>>(map_a, map_w, map_c, use_store_map, (bf16*)C, ldc, M, N, K, epilogue);
-    return launch_status();
+        return launch_chained(gemm_tcgen05_kernel<float>, dim3(grid), dim3(kThreads), (size_t)kSmemBytes, stream,
+                              map_a, map_w, map_c, use_store_map, (float*)C, ldc, M, N, K, epilogue);
+    return launch_chained(gemm_tcgen05_kernel<bf16>, dim3(grid), dim3(kThreads), (size_t)kSmemBytes, stream,
+                          map_a, map_w, map_c, use_store_map, (bf16*)C, ldc, M, N, K, epilogue);
 }

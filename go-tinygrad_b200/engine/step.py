@@ -23,6 +23,7 @@ import numpy as np
 import torch
 
 from ..cache import Cache
+from ..kernels import ops
 from ..parts.base import ResidualStream, StepContext
 from .model import Model
 
@@ -162,8 +163,11 @@ def step(model: Model, cache: Cache, entries: Sequence[StepEntry]) -> torch.Tens
     if not model.loaded:
         raise StepError("the model has no weights loaded")
     ctx, rows = build_context(model, cache, entries)
-    stream = run_layers(model, cache, ctx)
-    logits = logits_at(model, stream, ctx, rows)
+    # each kernel may set itself up while its predecessor drains (kernels that take
+    # no part in this are launched the plain way and order themselves fully)
+    with ops.chained_launches(model.rt.device.type == "cuda"):
+        stream = run_layers(model, cache, ctx)
+        logits = logits_at(model, stream, ctx, rows)
     for e in entries:
         cache.advance(e.slot, len(e.tokens))
     return logits

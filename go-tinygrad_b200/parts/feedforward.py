@@ -3,7 +3,10 @@ g / (1 + exp(-g)) (model/llama.go:1361-1401, backends/simd/vec.go:52-59).
 
 Parameters: ``hidden_size``, ``intermediate_size`` and the tensor names
 ``gate``, ``up``, ``down``.  Gate and up are fused at load into one matrix
-[2 * intermediate, hidden] (gate rows first) so that one product serves both.
+[2 * intermediate, hidden] so that one product serves both: in float32 the gate
+rows come first and a second kernel applies the activation; in bfloat16 the rows
+alternate in blocks of 8 gate and 8 up features and the product's epilogue
+applies the activation to its float accumulators.
 """
 from __future__ import annotations
 
