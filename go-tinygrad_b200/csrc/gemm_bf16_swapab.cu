@@ -7,16 +7,18 @@
 // are its N dimension, so both operands go from shared memory to the tensor core
 // once.  The accumulator [128 features x 64 tokens] lives in TMEM.
 //
-//   kernel 1  one CTA per (128-row tile of W, slice of k of at most 512).  One
-//             thread issues all TMA loads of the slice at once (up to eight
-//             64-wide k blocks, each with a barrier of its own: no ring, no
-//             reuse), one thread issues the MMAs as the blocks land, four warps
-//             write the float partial sums to a workspace [slice, token, feature].
+//   kernel 1  persistent, one CTA per SM.  A unit of work is (128-row tile of W,
+//             slice of k); CTA c takes units c, c+G, c+2G ...  One thread keeps a
+//             ring of eight 24 KB stages (a 128 x 64 block of W and the 64 x 64
+//             block of X under it) full by TMA, across units; one thread issues
+//             the MMAs as the stages land; four warps move finished accumulators
+//             (two in TMEM, so a unit's epilogue runs under the next unit's MMAs)
+//             to a float workspace [slice, token, feature].
 //   kernel 2  adds the slices in order, applies the optional SwiGLU over
 //             interleaved gate/up features, converts and stores C.
-// The number of slices is chosen so that about two CTAs per SM exist even for
-// products with few output features.  Waits are bounded as in the other tcgen05
-// kernel; no cluster multicast is used.
+// The number of slices balances two costs: CTAs without work in the last round,
+// and the workspace traffic, which grows with every slice.  Waits are bounded as
+// in the other tcgen05 kernel; no cluster multicast is used.
 #include "common.cuh"
 #include <cuda.h>
 
@@ -24,10 +26,11 @@ namespace {
 constexpr int BR = 128;                       // rows of W per CTA (MMA M)
 constexpr int BT = 64;                        // tokens per CTA (MMA N)
 constexpr int BK = 64;
-constexpr int kMaxBlocks = 8;                 // k blocks per CTA: a slice of at most 512
+constexpr int kStages = 8;                    // ring of k blocks
 constexpr int kWBytes = BR * BK * 2, kXBytes = BT * BK * 2, kBlockBytes = kWBytes + kXBytes;
 constexpr int kThreads = 192;
-constexpr int kTmemCols = 64;
+constexpr int kTmemCols = 128;                // two accumulators of 64 columns
+constexpr int kSmemBytes = kStages * kBlockBytes + 1024 + 256;
 constexpr unsigned kSpinLimit = 1u << 22;
 
 __device__ int g_status = 0;
@@ -38,6 +41,9 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
 }
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
     for (unsigned i = 0; i < kSpinLimit; ++i) {
@@ -87,27 +93,30 @@ __device__ __forceinline__ void tmem_ld32(uint32_t addr, uint32_t* r) {
                  : "r"(addr));
 }
 
-// grid (row tiles, slices).  part[slice][token][feature] (float), feature stride N.
+// part[slice][token][feature] (float), feature stride N.
 __global__ void __launch_bounds__(kThreads)
 swapab_partial_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-                      float* __restrict__ part, int M, int N, int K, int k_slice) {
+                      float* __restrict__ part, int M, int N, int K, int k_slice, int slices) {
     extern __shared__ unsigned char smem_raw[];
     const uint32_t base = (smem_addr(smem_raw) + 1023u) & ~1023u;
     unsigned char* aligned = smem_raw + (base - smem_addr(smem_raw));
-    const int k_begin = blockIdx.y * k_slice;
-    const int k_len = min(K, k_begin + k_slice) - k_begin;
-    const int n_kb = (k_len + BK - 1) / BK;                  // 1..kMaxBlocks
-    const int max_kb = (k_slice + BK - 1) / BK;              // the shared memory is sized for this many
-    const uint32_t bars = base + max_kb * kBlockBytes;       // full[kMaxBlocks], acc_full
-    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(aligned + max_kb * kBlockBytes + 128);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(aligned + max_kb * kBlockBytes + 136);
-    const uint32_t acc_bar = bars + 8u * kMaxBlocks;
+    const uint32_t bars = base + kStages * kBlockBytes;      // full[kStages], empty[kStages], acc_full[2], acc_empty[2]
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto empty_bar = [&](int s) { return bars + 8u * (kStages + s); };
+    auto acc_full = [&](int a) { return bars + 8u * (2 * kStages + a); };
+    auto acc_empty = [&](int a) { return bars + 8u * (2 * kStages + 2 + a); };
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(aligned + kStages * kBlockBytes + 192);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(aligned + kStages * kBlockBytes + 200);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * BR;
+    const int n_units = ((N + BR - 1) / BR) * slices;
+    auto unit_k = [&](int unit, int* k_begin) {              // k blocks of the unit's slice
+        *k_begin = (unit % slices) * k_slice;
+        return (min(K, *k_begin + k_slice) - *k_begin + BK - 1) / BK;
+    };
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kMaxBlocks; ++s) mbar_init(bars + 8u * s, 1);
-        mbar_init(acc_bar, 1);
+        for (int s = 0; s < kStages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(acc_full(a), 1); mbar_init(acc_empty(a), 4); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::);
     }
@@ -122,41 +131,85 @@ swapab_partial_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     const uint32_t tmem_base = *tmem_holder;
 
     if (warp == 4) {
+        // ------------------------------------------------------------ producer
         if (lane == 0) {
-            // weights first: they depend on no earlier kernel
-            for (int kb = 0; kb < n_kb; ++kb) {
-                mbar_expect_tx(bars + 8u * kb, kBlockBytes);
-                tma_load_2d(base + kb * kBlockBytes, &map_w, k_begin + kb * BK, n0, bars + 8u * kb);
+            // The first ring fill: the weights depend on no earlier kernel, so their
+            // copies start before the wait; the activations follow it.
+            uint32_t it = 0;
+            bool waited = false, ok = true;
+            int held[kStages][2];                            // (k, stage) of W copies whose X copy is still owed
+            int n_held = 0;
+            for (int unit = blockIdx.x; unit < n_units && ok; unit += gridDim.x) {
+                int k_begin;
+                const int n_kb = unit_k(unit, &k_begin);
+                const int n0 = (unit / slices) * BR;
+                for (int kb = 0; kb < n_kb; ++kb, ++it) {
+                    const int s = it % kStages;
+                    if (!waited && it == kStages) {          // the ring is full of weights: now the activations
+                        chain_wait();
+                        for (int h = 0; h < n_held; ++h)
+                            tma_load_2d(base + held[h][1] * kBlockBytes + kWBytes, &map_x, held[h][0], 0, full_bar(held[h][1]));
+                        waited = true;
+                    }
+                    if (!mbar_wait(empty_bar(s), ((it / kStages) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+                    mbar_expect_tx(full_bar(s), kBlockBytes);
+                    tma_load_2d(base + s * kBlockBytes, &map_w, k_begin + kb * BK, n0, full_bar(s));
+                    if (waited) {
+                        tma_load_2d(base + s * kBlockBytes + kWBytes, &map_x, k_begin + kb * BK, 0, full_bar(s));
+                    } else {
+                        held[n_held][0] = k_begin + kb * BK;
+                        held[n_held][1] = s;
+                        ++n_held;
+                    }
+                }
             }
-            chain_wait();
-            for (int kb = 0; kb < n_kb; ++kb)
-                tma_load_2d(base + kb * kBlockBytes + kWBytes, &map_x, k_begin + kb * BK, 0, bars + 8u * kb);
+            if (!waited) {                                   // fewer blocks than stages in all
+                chain_wait();
+                for (int h = 0; h < n_held; ++h)
+                    tma_load_2d(base + held[h][1] * kBlockBytes + kWBytes, &map_x, held[h][0], 0, full_bar(held[h][1]));
+            }
         }
     } else if (warp == 5) {
+        // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             const uint32_t idesc = umma_idesc(BR, BT);
-            for (int kb = 0; kb < n_kb; ++kb) {
-                if (!mbar_wait(bars + 8u * kb, 0, abort_flag)) break;
+            uint32_t it = 0, done = 0;
+            bool ok = true;
+            for (int unit = blockIdx.x; unit < n_units && ok; unit += gridDim.x, ++done) {
+                int k_begin;
+                const int n_kb = unit_k(unit, &k_begin);
+                const int a = done & 1;
+                if (!mbar_wait(acc_empty(a), ((done >> 1) & 1u) ^ 1u, abort_flag)) break;
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::);
-                const uint64_t da = umma_desc(base + kb * kBlockBytes);
-                const uint64_t db = umma_desc(base + kb * kBlockBytes + kWBytes);
+                for (int kb = 0; kb < n_kb; ++kb, ++it) {
+                    const int s = it % kStages;
+                    if (!mbar_wait(full_bar(s), (it / kStages) & 1u, abort_flag)) { ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;\n" ::);
+                    const uint64_t da = umma_desc(base + s * kBlockBytes);
+                    const uint64_t db = umma_desc(base + s * kBlockBytes + kWBytes);
 #pragma unroll
-                for (int j = 0; j < BK / 16; ++j)
-                    umma(tmem_base, da + 2 * j, db + 2 * j, idesc, (kb > 0 || j > 0) ? 1u : 0u);
+                    for (int j = 0; j < BK / 16; ++j)
+                        umma(tmem_base + 64 * a, da + 2 * j, db + 2 * j, idesc, (kb > 0 || j > 0) ? 1u : 0u);
+                    umma_commit(empty_bar(s));               // the stage is free once these MMAs have read it
+                }
+                if (ok) umma_commit(acc_full(a));
             }
-            umma_commit(acc_bar);
         }
     } else {
-        chain_wait();                                   // the workspace may still be read by an earlier kernel
-        const bool ready = mbar_wait(acc_bar, 0, abort_flag);
-        asm volatile("tcgen05.fence::after_thread_sync;\n" ::);
-        if (ready) {
-            const int feature = n0 + warp * 32 + lane;
-            float* dst = part + (size_t)blockIdx.y * M * N + feature;
+        // ------------------------------------------------------------ epilogue: TMEM -> workspace
+        chain_wait();                                       // the workspace may still be read by an earlier kernel
+        uint32_t done = 0;
+        for (int unit = blockIdx.x; unit < n_units; unit += gridDim.x, ++done) {
+            const int a = done & 1;
+            const bool ready = mbar_wait(acc_full(a), (done >> 1) & 1u, abort_flag);
+            if (!__all_sync(0xffffffffu, ready)) break;
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::);
+            const int feature = (unit / slices) * BR + warp * 32 + lane;
+            float* dst = part + (size_t)(unit % slices) * M * N + feature;
 #pragma unroll 1
             for (int c = 0; c < BT / 32; ++c) {
                 uint32_t v[32];
-                tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(c * 32), v);
+                tmem_ld32(tmem_base + 64 * a + ((uint32_t)(warp * 32) << 16) + (uint32_t)(c * 32), v);
                 asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
                 if (feature < N) {
 #pragma unroll
@@ -166,6 +219,9 @@ swapab_partial_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
                     }
                 }
             }
+            asm volatile("tcgen05.fence::before_thread_sync;\n" ::);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty(a));
         }
     }
     chain_release();
@@ -232,15 +288,27 @@ int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int ld, int box
     return r == CUDA_SUCCESS ? 0 : kErrBadArgument;
 }
 
-void plan(int N, int K, int* slices, int* k_slice) {
-    const int row_tiles = (N + BR - 1) / BR;
-    int s = (K + kMaxBlocks * BK - 1) / (kMaxBlocks * BK);          // slices of at most 512
-    const int want = (2 * 148 + row_tiles - 1) / row_tiles;         // about two CTAs per SM
-    const int most = (K + BK - 1) / BK;                             // a slice holds at least one k block
-    if (s < want) s = want < most ? want : most;
-    int ks = ((K + s - 1) / s + BK - 1) / BK * BK;
-    *k_slice = ks;
-    *slices = (K + ks - 1) / ks;
+// Slices of k per row tile.  More slices fill the last round of the persistent
+// grid better but add workspace traffic (every slice writes and re-reads M x 128
+// floats per tile against 128 x k_slice weights): take the count with the least
+// estimated time.
+void plan(int M, int N, int K, int* slices, int* k_slice) {
+    const int row_tiles = (N + BR - 1) / BR, k_blocks = (K + BK - 1) / BK, grid = 148;
+    int best = 1;
+    double best_cost = 1e30;
+    for (int s = 1; s <= k_blocks && s <= 64; ++s) {
+        const int per = (k_blocks + s - 1) / s;                 // k blocks per slice
+        const int real = (k_blocks + per - 1) / per;            // slices that exist with this size
+        if (real != s) continue;
+        const long long units = (long long)row_tiles * s;
+        const long long rounds = (units + grid - 1) / grid;
+        const double weights = (double)per * BK * 2 * BR, spill = 2.0 * M * 4 * BR;   // bytes per unit
+        const double cost = (double)rounds * (weights + spill + 4096.0);              // + a fixed cost per unit
+        if (cost < best_cost) { best_cost = cost; best = s; }
+    }
+    const int per = (k_blocks + best - 1) / best;
+    *k_slice = per * BK;
+    *slices = best;
 }
 }  // namespace
 
@@ -253,7 +321,7 @@ GTG_API int gtg_gemm_bf16_swapab_status() {
 // Floats of workspace a call needs.
 GTG_API long long gtg_gemm_bf16_swapab_scratch_floats(int M, int N, int K) {
     int slices, k_slice;
-    plan(N, K, &slices, &k_slice);
+    plan(M, N, K, &slices, &k_slice);
     return (long long)slices * M * N;
 }
 
@@ -268,23 +336,28 @@ GTG_API int gtg_gemm_bf16_swapab(const void* X, int ldx, const void* W, int ldw,
     if (K <= 0 || ldx < K || ldw < K || ldc < (epilogue ? N / 2 : N) || scratch == nullptr) return kErrBadArgument;
     if (K % 8 || ldx % 8 || ldw % 8 || ((uintptr_t)X % 16) || ((uintptr_t)W % 16)) return kErrUnsupported;
     int slices, k_slice;
-    plan(N, K, &slices, &k_slice);
-    if (slices > 65535) return kErrUnsupported;
+    plan(M, N, K, &slices, &k_slice);
     CUtensorMap map_w, map_x;
     int st = make_map(&map_w, W, N, K, ldw, BR);
     if (st != 0) return st;
     st = make_map(&map_x, X, M, K, ldx, BT);
     if (st != 0) return st;
-    const int smem = ((k_slice + BK - 1) / BK) * kBlockBytes + 1024 + 256;
     static bool configured = false;
+    static int sms = 148;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(swapab_partial_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             kMaxBlocks * kBlockBytes + 1024 + 256);
+        cudaError_t e = cudaFuncSetAttribute(swapab_partial_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
         if (e != cudaSuccess) return (int)e;
+        int dev = 0, n = 0;
+        if (cudaGetDevice(&dev) == cudaSuccess &&
+            cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0)
+            sms = n;
         configured = true;
     }
-    st = launch_chained(swapab_partial_kernel, dim3((N + BR - 1) / BR, slices), dim3(kThreads), (size_t)smem, stream,
-                        map_w, map_x, scratch, M, N, K, k_slice);
+    const long long units = (long long)((N + BR - 1) / BR) * slices;
+    if (units > 0x7fffffff) return kErrUnsupported;
+    const int grid = (int)(units < sms ? units : sms);
+    st = launch_chained(swapab_partial_kernel, dim3(grid), dim3(kThreads), (size_t)kSmemBytes, stream,
+                        map_w, map_x, scratch, M, N, K, k_slice, slices);
     if (st != 0) return st;
     const int n_out = epilogue ? N / 2 : N;
     int blocks = (int)(((long long)M * n_out + 255) / 256);
