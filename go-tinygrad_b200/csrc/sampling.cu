@@ -12,34 +12,53 @@
 namespace {
 constexpr int kThreads = 256;
 
-__global__ void __launch_bounds__(kThreads)
+constexpr int kArgmaxThreads = 1024;
+
+// (a, ia) <- the better of (a, ia) and (b, ib): the larger value, the lower index on a tie.
+__device__ __forceinline__ void argmax_merge(float& a, int& ia, float b, int ib) {
+    if (b > a || (b == a && ib < ia)) { a = b; ia = ib; }
+}
+
+// One block per row; each thread scans its elements in increasing index order
+// (16 bytes at a time when the row allows it), then warps and the block merge.
+__global__ void __launch_bounds__(kArgmaxThreads)
 argmax_kernel(const float* __restrict__ logits, int ld, int V, int* __restrict__ out) {
     chain_release();
     chain_wait();
-    __shared__ float bv[kThreads];
-    __shared__ int bi[kThreads];
+    __shared__ float bv[kArgmaxThreads / 32];
+    __shared__ int bi[kArgmaxThreads / 32];
     const float* row = logits + (size_t)blockIdx.x * ld;
     float best = -INFINITY;
     int idx = V;                      // "nothing yet": any real index beats it on a tie
-    for (int i = threadIdx.x; i < V; i += kThreads) {
-        const float v = row[i];
+    auto see = [&](float v, int i) {
         if (v > best || (idx == V && !(v != v))) { best = v; idx = i; }
+    };
+    const bool vec = (ld % 4 == 0) && ((reinterpret_cast<uintptr_t>(logits) & 15) == 0);
+    const int V4 = vec ? V / 4 : 0;
+    for (int i = threadIdx.x; i < V4; i += kArgmaxThreads) {
+        const float4 v = reinterpret_cast<const float4*>(row)[i];
+        see(v.x, 4 * i); see(v.y, 4 * i + 1); see(v.z, 4 * i + 2); see(v.w, 4 * i + 3);
     }
-    bv[threadIdx.x] = best;
-    bi[threadIdx.x] = idx;
+    for (int i = 4 * V4 + threadIdx.x; i < V; i += kArgmaxThreads) see(row[i], i);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+        argmax_merge(best, idx, ov, oi);
+    }
+    if ((threadIdx.x & 31) == 0) { bv[threadIdx.x >> 5] = best; bi[threadIdx.x >> 5] = idx; }
     __syncthreads();
-    for (int s = kThreads / 2; s > 0; s >>= 1) {
-        if (threadIdx.x < s) {
-            const float ov = bv[threadIdx.x + s];
-            const int oi = bi[threadIdx.x + s];
-            if (ov > bv[threadIdx.x] || (ov == bv[threadIdx.x] && oi < bi[threadIdx.x])) {
-                bv[threadIdx.x] = ov;
-                bi[threadIdx.x] = oi;
-            }
+    if (threadIdx.x < 32) {
+        best = bv[threadIdx.x];
+        idx = bi[threadIdx.x];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+            argmax_merge(best, idx, ov, oi);
         }
-        __syncthreads();
+        if (threadIdx.x == 0) out[blockIdx.x] = idx < V ? idx : 0;
     }
-    if (threadIdx.x == 0) out[blockIdx.x] = bi[0] < V ? bi[0] : 0;
 }
 
 __device__ __forceinline__ unsigned long long mix64(unsigned long long z) {
@@ -125,7 +144,7 @@ sample_temperature_kernel(const float* __restrict__ logits, int ld, int V, float
 GTG_API int gtg_argmax(const float* logits, int ld, int R, int V, int* out, cudaStream_t stream) {
     if (R <= 0) return 0;
     if (V <= 0 || ld < V) return kErrBadArgument;
-    return launch_chained(argmax_kernel, dim3(R), dim3(kThreads), 0, stream, logits, ld, V, out);
+    return launch_chained(argmax_kernel, dim3(R), dim3(kArgmaxThreads), 0, stream, logits, ld, V, out);
 }
 
 GTG_API int gtg_sample_temperature(const float* logits, int ld, int R, int V, float temperature,
