@@ -218,6 +218,18 @@ def test_linear_bfloat16(out_dtype, kind, M, N, K):
     assert ops.bounded_wait_failures() == 0
 
 
+@pytest.mark.parametrize("M,N,K", [(40, 38000, 136), (64, 19100, 520), (17, 300, 16384)])
+def test_linear_swapab_many_units_per_block(M, N, K):
+    """More (row tile, slice) units than SMs: every persistent block walks several
+    units, its ring wraps and its two accumulators alternate."""
+    x, w = rnd(M, K, dtype=torch.bfloat16, seed=1), rnd(N, K, dtype=torch.bfloat16, seed=2)
+    out = torch.empty(M, N, dtype=torch.float32, device=DEV)
+    ops.linear(x, w, out, kind="swapab")
+    want = (x.double() @ w.double().T).float()
+    torch.testing.assert_close(out, want, rtol=1e-4, atol=2e-3 * math.sqrt(K / 64))
+    assert ops.bounded_wait_failures() == 0
+
+
 def test_linear_strided_operands():
     """Inputs and outputs that are column slices of wider buffers."""
     xb, w = rnd(9, 304, dtype=torch.bfloat16), rnd(50, 96, dtype=torch.bfloat16, seed=3)

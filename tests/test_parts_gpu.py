@@ -14,9 +14,9 @@ from go_tinygrad_b200.cache import Cache, StateRequest
 from go_tinygrad_b200.config import Architecture, LlamaConfig, register_architecture, unregister_architecture
 from go_tinygrad_b200.engine import Model, StepEntry, step
 from go_tinygrad_b200.models.llama import llama_plan
-from go_tinygrad_b200.parts import (LayerSpec, Mixer, ModelPlan, PartSpec, ResidualStream, Runtime,
-                                    ScheduleEntry, StepContext, build_part, register_part,
-                                    unregister_part)
+from go_tinygrad_b200.parts import (FeedForward, LayerSpec, Mixer, ModelPlan, PartSpec, PositionEncoding,
+                                    ResidualStream, Runtime, ScheduleEntry, StepContext, build_part,
+                                    register_part, unregister_part)
 from go_tinygrad_b200.weights import TensorSource, WeightSpec
 from conftest import TINY, assert_close, make_prompts
 
@@ -296,3 +296,129 @@ def test_a_layer_named_twice_and_a_layer_that_reads_another_cache(model_folders,
     with pytest.raises(ValueError, match="does not run before"):
         ModelPlan(base.hidden_size, base.vocab_size, base.embedding, base.layers,
                   (ScheduleEntry(0, cache=1), ScheduleEntry(1)), base.final_norm, base.head).check()
+
+
+# ------------------------------------------- a toy feed-forward with routing, another position encoding
+class LearnedPositions(PositionEncoding):
+    """x_t += P[position_t]: a table of learned absolute positions added to the
+    embedded tokens; queries and keys are not rotated."""
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.n, self.size, self.name = int(self.param("max_position")), int(self.param("hidden_size")), self.param("weight")
+
+    def weight_specs(self):
+        return [WeightSpec(self.name, (self.n, self.size), role="table")]
+
+    def load(self, tensors, rt):
+        self.table = tensors[self.name].to(device=rt.device, dtype=torch.float32)
+
+    def on_embedding(self, stream, ctx):
+        stream.residual += self.table[ctx.positions.long()]
+
+
+class Top1Experts(FeedForward):
+    """Router logits r = R x in float32; the expert e = argmax r (first maximum)
+    alone runs: y = softmax(r)[e] * D_e relu(U_e x).  Plain torch, a test's toy."""
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.h, self.i, self.e = (int(self.param(k)) for k in ("hidden_size", "intermediate_size", "n_experts"))
+        self.prefix = self.param("prefix")
+
+    def weight_specs(self):
+        specs = [WeightSpec(self.prefix + "router.weight", (self.e, self.h))]
+        for e in range(self.e):
+            specs += [WeightSpec(f"{self.prefix}experts.{e}.up.weight", (self.i, self.h)),
+                      WeightSpec(f"{self.prefix}experts.{e}.down.weight", (self.h, self.i))]
+        return specs
+
+    def load(self, tensors, rt):
+        self.router = tensors[self.prefix + "router.weight"].to(device=rt.device, dtype=torch.float32)
+        self.up = [rt.matrix(tensors[f"{self.prefix}experts.{e}.up.weight"]) for e in range(self.e)]
+        self.down = [rt.matrix(tensors[f"{self.prefix}experts.{e}.down.weight"]) for e in range(self.e)]
+
+    def forward(self, x, ctx):
+        logits = x.float() @ self.router.T
+        choice = logits.argmax(dim=1)
+        weight = torch.softmax(logits, dim=1).gather(1, choice[:, None])
+        out = torch.zeros(x.shape, dtype=torch.float32, device=x.device)
+        for e in range(self.e):
+            rows = (choice == e).nonzero().flatten()
+            if rows.numel():
+                hidden = torch.relu(x[rows].float() @ self.up[e].float().T)
+                out[rows] = hidden @ self.down[e].float().T
+        return (out * weight).to(x.dtype)
+
+
+N_EXPERTS = 3
+
+
+def routed_plan(cfg):
+    """Llama's plan with learned absolute positions instead of rotation and the
+    feed-forward of layer 1 replaced by routed experts."""
+    base = llama_plan(cfg)
+    layers = []
+    for i, layer in enumerate(base.layers):
+        mixer = PartSpec(layer.mixer.kind, dict(layer.mixer.params, position=PartSpec("none")))
+        ff = layer.feed_forward
+        if i == 1:
+            ff = PartSpec("top1_experts", {"hidden_size": cfg.hidden_size, "intermediate_size": 40,
+                                           "n_experts": N_EXPERTS, "prefix": f"model.layers.{i}.moe."})
+        layers.append(LayerSpec(layer.block, layer.mixer_norm, mixer, layer.feed_forward_norm, ff))
+    embedding = PartSpec(base.embedding.kind, dict(base.embedding.params, position=PartSpec(
+        "learned_positions", {"max_position": 96, "hidden_size": cfg.hidden_size, "weight": "model.positions.weight"})))
+    return ModelPlan(base.hidden_size, base.vocab_size, embedding, tuple(layers), base.schedule,
+                     base.final_norm, base.head, base.stop_tokens, 96)
+
+
+def plain_routed_forward(cfg, w, tokens):
+    positions = list(range(len(tokens)))
+    no_rotation = np.zeros(cfg["head_dim"] // 2)                # angle 0: cos 1, sin 0
+    x = plain.embed(w["model.embed_tokens.weight"], tokens) + w["model.positions.weight"][positions].astype(np.float32)
+    for i in range(cfg["num_hidden_layers"]):
+        p = f"model.layers.{i}."
+        n = plain.rms_norm(x, w[p + "input_layernorm.weight"], cfg["rms_norm_eps"])
+        x = (x + plain.attention_block(n, positions, p, cfg, no_rotation, w)).astype(np.float32)
+        n2 = plain.rms_norm(x, w[p + "post_attention_layernorm.weight"], cfg["rms_norm_eps"])
+        if i != 1:
+            x = x + plain.swiglu_mlp(n2, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"],
+                                     w[p + "mlp.down_proj.weight"])
+            continue
+        logits = plain.linear(n2, w[p + "moe.router.weight"])
+        y = np.zeros_like(x)
+        for t in range(len(tokens)):
+            e = int(np.argmax(logits[t]))
+            prob = np.exp(logits[t] - logits[t].max())
+            prob = prob[e] / prob.sum()
+            hidden = np.maximum(plain.linear(n2[t:t + 1], w[p + f"moe.experts.{e}.up.weight"]), 0)
+            y[t] = prob * plain.linear(hidden, w[p + f"moe.experts.{e}.down.weight"])[0]
+        x = (x + y).astype(np.float32)
+    return plain.lm_head(x, cfg, w)
+
+
+def test_a_routed_feed_forward_and_learned_positions_without_touching_the_library(tmp_path):
+    register_part("position", "learned_positions")(LearnedPositions)
+    register_part("feed_forward", "top1_experts")(Top1Experts)
+    arch = register_architecture(Architecture(("ToyRoutedForCausalLM",), LlamaConfig.from_json, routed_plan))
+    try:
+        raw = dict(TINY["B"], architectures=["ToyRoutedForCausalLM"], model_type="toy_routed")
+        folder = str(tmp_path / "routed")
+        lib.write_random_model(folder, raw, seed=9, dtype="float32", std=0.1, norm_std=0.05)
+        cfg, w = plain.read_model(folder)
+        assert f"model.layers.1.moe.experts.{N_EXPERTS - 1}.down.weight" in w and "model.layers.1.mlp.up_proj.weight" not in w
+        model = Model.load(folder, dtype="float32", device="cuda")
+        assert type(model.blocks[1].ff) is Top1Experts
+        cache = model.new_cache(max_tokens=64 * 4, max_slots=2)
+        p, q = make_prompts("B", [40, 23], seed=77)
+        want_p, want_q = plain_routed_forward(cfg, w, p), plain_routed_forward(cfg, w, q)
+        sp, sq = cache.open_sequence(), cache.open_sequence()
+        got = step(model, cache, [StepEntry(sp, p[:25], list(range(25))), StepEntry(sq, q, list(range(23)))]).cpu().numpy()
+        assert_close(got[:25], want_p[:25], "float32", "routed whole")
+        assert_close(got[25:], want_q, "float32", "routed second sequence")
+        rest = [step(model, cache, [StepEntry(sp, [p[t]], [0])]).cpu().numpy() for t in range(25, 40)]
+        assert_close(np.concatenate(rest), want_p[25:], "float32", "routed one by one")
+    finally:
+        unregister_architecture(arch)
+        unregister_part("position", "learned_positions")
+        unregister_part("feed_forward", "top1_experts")
