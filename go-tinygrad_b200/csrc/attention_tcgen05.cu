@@ -143,6 +143,13 @@ __device__ __forceinline__ float fast_exp2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
     return y;
 }
+// The same, kept in program order among its like (volatile), so that a batch of
+// them stays a batch in the machine code.
+__device__ __forceinline__ float exp2_in_order(float x) {
+    float y;
+    asm volatile("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
 
 // map_q: the step's [tokens, row width] activations, boxes of 64 channels x 128 rows.
 // map_kv: one cache entry as rows of 64 channels, row = ((page*2 + k|v)*n_kv + head)*64 + token.
@@ -287,24 +294,24 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     if (!vis) sv[c] = __float_as_uint(-INFINITY);
                 }
             }
-            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+            float mx[8];
 #pragma unroll
-            for (int c = 0; c < BK; c += 4) {
-                mx0 = fmaxf(mx0, __uint_as_float(sv[c]));
-                mx1 = fmaxf(mx1, __uint_as_float(sv[c + 1]));
-                mx2 = fmaxf(mx2, __uint_as_float(sv[c + 2]));
-                mx3 = fmaxf(mx3, __uint_as_float(sv[c + 3]));
+            for (int e = 0; e < 8; ++e) mx[e] = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < BK; c += 8) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) mx[e] = fmaxf(mx[e], __uint_as_float(sv[c + e]));
             }
-            const float m_page = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * sl2;
+            const float m_page = fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])),
+                                       fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7]))) * sl2;
             if (i == 0) {
                 m_run = m_page;                                  // the first product overwrites O
             } else {
                 const bool raise = m_page > m_run + kRaiseBy;    // also: the first visible key of a row
-                const bool any_raise = __any_sync(full, raise);
-                // P_i goes where P_{i-1} was, and O may only be touched between products
-                ok = __all_sync(full, mbar_wait(pv_done, (uint32_t)(i - 1) & 1u, abort_flag));
-                if (!ok) break;
-                if (any_raise) {
+                if (__any_sync(full, raise)) {
+                    // O may only be touched between products (rare after the first steps)
+                    ok = __all_sync(full, mbar_wait(pv_done, (uint32_t)(i - 1) & 1u, abort_flag));
+                    if (!ok) break;
                     float corr = 1.0f;
                     if (raise) {
                         corr = fast_exp2(m_run - m_page);        // 0 when the row had seen nothing
@@ -325,20 +332,37 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             }
             const float m_use = m_run == -INFINITY ? 0.f : m_run;
             float l0 = 0.f, l1 = 0.f;
-            // the row of P: 128 bfloat16 as 64 packed columns, written 32 columns at a time
+            // the row of P: 128 bfloat16 as 64 packed columns, written 32 columns at a time.
+            // Eight exponentials are issued back to back (the special-function unit takes
+            // one warp instruction every 8 cycles and answers after some tens of cycles)
+            // before the first of them is used.
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
 #pragma unroll
-                for (int c = 0; c < 32; ++c) {
-                    const float p0 = fast_exp2(fmaf(__uint_as_float(sv[64 * half + 2 * c]), sl2, -m_use));
-                    const float p1 = fast_exp2(fmaf(__uint_as_float(sv[64 * half + 2 * c + 1]), sl2, -m_use));
-                    l0 += p0;
-                    l1 += p1;
-                    __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
-                    sv[64 * half + c] = *reinterpret_cast<uint32_t*>(&hh);   // the scores at and below this index are done with
+                for (int c = 0; c < 32; c += 4) {
+                    float p[8];
+#pragma unroll
+                    for (int e = 0; e < 8; ++e)
+                        p[e] = fmaf(__uint_as_float(sv[64 * half + 2 * c + e]), sl2, -m_use);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) p[e] = exp2_in_order(p[e]);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        l0 += p[2 * e];
+                        l1 += p[2 * e + 1];
+                        __nv_bfloat162 hh = __floats2bfloat162_rn(p[2 * e], p[2 * e + 1]);
+                        sv[64 * half + c + e] = *reinterpret_cast<uint32_t*>(&hh);   // the scores at and below this index are done with
+                    }
                 }
-                tmem_st32(tmem_p + lane_off + 32 * half, sv + 64 * half);
             }
+            // P_i goes where P_{i-1} was: its product must have read it (it has, long ago,
+            // unless the tensor pipe is the slower side)
+            if (i > 0) {
+                ok = __all_sync(full, mbar_wait(pv_done, (uint32_t)(i - 1) & 1u, abort_flag));
+                if (!ok) break;
+            }
+            tmem_st32(tmem_p + lane_off, sv);
+            tmem_st32(tmem_p + lane_off + 32, sv + 64);
             l_run += l0 + l1;
             asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::);
