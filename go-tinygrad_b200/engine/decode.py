@@ -13,7 +13,13 @@ random draw) and the sampled tokens.  Two ways to drive it:
     nothing crosses the bus (a kernel moves them; for timing the step itself).
 
 The first run of a batch executes eagerly (it loads and configures kernels,
-which a capture must not do), the second is captured.
+which a capture must not do), the second is captured.  A recording fixes what
+the parts chose from the batch's longest sequence (into how many blocks the
+keys of a sequence are split): it is made for a length a little ahead of the
+current one and made again when the sequences have outgrown it, or when the
+object is given much shorter sequences (`rebind`).  Which sequences the batch
+holds is data (slots and request ids in a device buffer), so one recording
+serves every set of as many sequences.
 """
 from __future__ import annotations
 
@@ -56,6 +62,19 @@ class DecodeBatch:
         self.chained = chained and dev.type == "cuda"     # kernels of the step overlap their launch gaps
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self._runs = 0
+        self._planned_len = 0                             # the longest sequence the recording was made for
+
+    AHEAD = 1.2                                           # a recording is planned for this much more than the current length
+
+    def rebind(self, slots: Sequence[int], requests: Sequence[int]) -> None:
+        """The same number of sequences, other slots and request ids: the
+        recorded step is kept."""
+        if len(slots) != self.B or len(requests) != self.B:
+            raise ValueError(f"this decode batch holds {self.B} sequences")
+        self.slots = list(slots)
+        B = self.B
+        fixed = torch.tensor(list(slots) + list(requests), dtype=torch.int32)
+        self.meta[5 * B + 1:7 * B + 1].copy_(fixed.to(self.meta.device))
 
     # ------------------------------------------------------------------ state
     def set_state(self, tokens: Sequence[int], steps: Sequence[int]) -> None:
@@ -71,7 +90,7 @@ class DecodeBatch:
         return StepContext(rt=self.model.rt, n_tokens=self.B, n_seqs=self.B, tokens=self.tokens,
                            positions=self.positions, token_seq=self.token_seq, cu_seqlens=self.cu,
                            slots=self.slot_ids, start_pos=self.positions, max_q_len=1,
-                           max_kv_len=max(self.cache.length(s) for s in self.slots) + 1, is_decode=True)
+                           max_kv_len=self._planned_len, is_decode=True)
 
     def _forward(self) -> None:
         ctx = self._context()
@@ -84,6 +103,12 @@ class DecodeBatch:
         """Run the step for the state now on the device; grows every sequence by one."""
         self.cache.reserve_many([(s, self.cache.length(s) + 1) for s in self.slots])
         self.cache.flush_tables()
+        longest = max(self.cache.length(s) for s in self.slots) + 1
+        if self.graph is None or not self.use_graph:
+            self._planned_len = max(longest, int(longest * self.AHEAD))
+        elif longest > self._planned_len * 1.17 or longest * 2 < self._planned_len:
+            self.graph = None                             # outgrown (or far too long a plan): record again
+            self._planned_len = max(longest, int(longest * self.AHEAD))
         if not self.use_graph:
             self._forward()
         elif self.graph is not None:

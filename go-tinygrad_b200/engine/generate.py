@@ -68,6 +68,7 @@ def generate(model: Model, prompts: Sequence[Sequence[int]],
                            max_sequence=max_seq)
     sampler = Sampler(temperature, seed)
     results: List[Optional[GenerationResult]] = [None] * n
+    decoders = {}                       # batch size -> DecodeBatch
 
     for batch in batches:
         seqs = [SequenceProgress(i, lengths[i], limits[i], stop_set, max_seq) for i in batch]
@@ -91,9 +92,13 @@ def generate(model: Model, prompts: Sequence[Sequence[int]],
                 if not running:
                     break
                 now = tuple(s.request for s in running)
-                if now != members:          # the batch shrank: a new fixed set of sequences
-                    decode = DecodeBatch(model, cache, [slots[r] for r in now], now, sampler,
-                                         use_graph=use_graph)
+                if now != members:          # the batch shrank: another fixed set of sequences
+                    decode = decoders.get(len(now))
+                    if decode is None:      # one recorded step per batch size serves every set of that size
+                        decode = decoders[len(now)] = DecodeBatch(model, cache, [slots[r] for r in now], now,
+                                                                  sampler, use_graph=use_graph)
+                    else:
+                        decode.rebind([slots[r] for r in now], now)
                     members = now
                 picked = decode.step_host([s.tokens[-1] for s in running], [len(s.tokens) for s in running])
                 for s, tok in zip(running, picked):
