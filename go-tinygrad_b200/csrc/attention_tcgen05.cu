@@ -1,50 +1,60 @@
 // Causal grouped-query prefill attention on the fifth-generation tensor cores,
-// for heads of 64 channels, over the paged cache.
+// for heads of 64 or 128 channels, over the paged cache.
 //
-// One CTA per (128-query tile, query head, sequence).  Per step of two cache pages
-// (128 keys):
-//   S  = Q K^T      tcgen05.mma 128 x 128 x 64: Q and the two key pages in shared
-//                   memory (TMA, 128-byte swizzle, both K-major), S in TMEM
-//   P  = softmax    four warps, one thread per query row: tcgen05.ld its 128 scores
+// One CTA per (128-query tile, query head, sequence).  Per step of BK keys (two
+// cache pages = 128 keys for heads of 64 channels, one page for heads of 128):
+//   S  = Q K^T      tcgen05.mma 128 x BK x head size: Q and the key pages in shared
+//                   memory (TMA, 128-byte swizzle, both K-major, 64 channels per
+//                   swizzled block), S in TMEM
+//   P  = softmax    four warps, one thread per query row: tcgen05.ld its BK scores
 //                   into registers and hand the TMEM tile back at once (the next
 //                   step's S runs under this step's softmax); mask (diagonal and
 //                   window-edge steps only), running max and sum in float; the row
 //                   of P goes back to TMEM as packed bfloat16 (tcgen05.st)
-//   O += P V        tcgen05.mma 128 x 64 x 128 with A = P read from TMEM and the
-//                   value pages as the MN-major B operand -- a page's
+//   O += P V        tcgen05.mma 128 x head size x BK with A = P read from TMEM and
+//                   the value pages as the MN-major B operand -- a page's
 //                   [key][channel] rows are that layout as they lie in the cache --
 //                   accumulating in TMEM over all steps
 // Neither P nor O passes through shared memory, whose bandwidth is what limits
-// 64-wide tiles on this machine.  The running maximum m of a row is only raised
+// small tiles on this machine.  The running maximum m of a row is only raised
 // when the step's maximum exceeds it by more than 2^8; until then P = exp2(s - m)
 // is taken against the older m (at most 256, exact in float and as good as any
 // other scale in bfloat16) and the sum uses the same m, so the quotient O / l is
 // unchanged.  Raising m multiplies the row of O in TMEM by exp2(m_old - m_new)
 // (tcgen05.ld / st by the row's thread, after the previous product has completed);
 // it happens in the first steps and rarely later.  Roles: warps 0-3 softmax and
-// output, warp 4 issues the TMA loads (three stages of 2 key + 2 value pages),
-// warp 5 allocates TMEM and issues the MMAs.  Every mbarrier wait is bounded
-// (status word as in the products).
+// output, warp 4 issues the TMA loads (a ring of key + value pages), warp 5
+// allocates TMEM and issues the MMAs.  Two CTAs share an SM (256 TMEM columns
+// each).  Every mbarrier wait is bounded (status word as in the products).
 #include "common.cuh"
 #include <cuda.h>
 #include <math.h>
 
 namespace {
 constexpr int BQ = 128;                 // query rows per CTA
-constexpr int HD = 64;                  // head size this kernel serves
-constexpr int BK = 2 * kPageTokens;     // keys per step
 constexpr int kThreads = 192;
-constexpr int kStages = 3;              // steps of keys and values in flight
-constexpr int kQBytes = BQ * HD * 2, kPageBytes = kPageTokens * HD * 2;
-constexpr int kStageBytes = 4 * kPageBytes;      // K page A, K page B, V page A, V page B
-constexpr int kTmemCols = 256;          // S 128, O 64, P 64 (128 keys as bfloat16 pairs)
+constexpr int kBlockBytes = kPageTokens * 64 * 2;   // 64 tokens x 64 channels: one swizzled block of a page
+constexpr int kTmemCols = 256;
 constexpr unsigned kSpinLimit = 1u << 22;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRaiseBy = 8.0f;        // the running maximum follows only jumps above 2^8
-// shared memory: Q | stages | barriers.  Two CTAs fit one SM.
-constexpr int kOffKV = kQBytes;
-constexpr int kOffBar = kOffKV + kStages * kStageBytes;
-constexpr int kSmemBytes = kOffBar + 256;
+
+// Sizes that follow from the head size.
+template <int HD> struct Shape {
+    static constexpr int BK = HD == 64 ? 128 : 64;             // keys per step
+    static constexpr int kPages = BK / kPageTokens;            // cache pages per step
+    static constexpr int kHalves = HD / 64;                    // 64-channel blocks per row
+    static constexpr int kStages = HD == 64 ? 3 : 2;           // steps of keys and values in flight
+    static constexpr int kQBytes = BQ * HD * 2;
+    static constexpr int kTileBytes = BK * HD * 2;             // the keys (or the values) of a step
+    static constexpr int kStageBytes = 2 * kTileBytes;
+    static constexpr int kOffKV = kQBytes;
+    static constexpr int kOffBar = kOffKV + kStages * kStageBytes;
+    static constexpr int kSmemBytes = kOffBar + 256;
+    // TMEM columns: S (BK floats), O (HD floats), P (BK bfloat16 as pairs)
+    static constexpr int kColO = BK, kColP = BK + HD;
+    static_assert(BK + HD + BK / 2 <= kTmemCols, "tensor memory");
+};
 
 __device__ int g_status = 0;
 
@@ -74,14 +84,16 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
                  ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
 }
-// Operand descriptor for a tile of 128-byte rows with 128-byte swizzle whose 8-row
+// Operand descriptor for blocks of 128-byte rows with 128-byte swizzle whose 8-row
 // groups are 1024 bytes apart.  Read K-major (rows = M/N index, the 64 values of a
-// row = k) or MN-major (rows = k index, the 64 values of a row = N index): which
+// row = k) or MN-major (rows = k index, the 64 values of a row = M/N index): which
 // one is said by the instruction descriptor, the bytes are laid out the same.
-__device__ __forceinline__ uint64_t umma_desc(uint32_t addr) {
+// `mn_block_bytes`: for an MN-major operand wider than 64, the distance between
+// its 64-wide blocks.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t addr, uint32_t mn_block_bytes = 16) {
     uint64_t d = 0;
     d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
-    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)((mn_block_bytes >> 4) & 0x3FFFu) << 16;
     d |= (uint64_t)(1024 >> 4) << 32;
     d |= (uint64_t)1 << 46;
     d |= (uint64_t)2 << 61;
@@ -152,8 +164,12 @@ __device__ __forceinline__ float exp2_in_order(float x) {
 }
 
 // map_q: the step's [tokens, row width] activations, boxes of 64 channels x 128 rows.
-// map_kv: one cache entry as rows of 64 channels, row = ((page*2 + k|v)*n_kv + head)*64 + token.
+// map_kv: one cache entry as rows of HD channels, row = ((page*2 + k|v)*n_kv + head)*64 + token;
+//         boxes of 64 channels x 64 rows.
 // grid: (query heads, sequences, query tiles), the longest tiles first.
+// A stage of the ring: the step's keys, then its values, each as HD/64 blocks of
+// [BK tokens][64 channels] (a block holds the step's pages one after the other).
+template <int HD>
 __global__ void __launch_bounds__(kThreads, 2)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
                             bf16* __restrict__ out, int ldo,
@@ -161,6 +177,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             const int* __restrict__ cu_seqlens, const int* __restrict__ slots,
                             const int* __restrict__ start_pos,
                             int n_heads, int n_kv, float scale, int window) {
+    using S = Shape<HD>;
+    constexpr int BK = S::BK;
     extern __shared__ __align__(1024) unsigned char smem[];
     const int h = blockIdx.x, b = blockIdx.y;
     const int tile = gridDim.z - 1 - blockIdx.z;
@@ -172,12 +190,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         if (threadIdx.x == 0) atomicExch(&g_status, 2);
         return;
     }
-    const uint32_t bars = base + kOffBar;
+    const uint32_t bars = base + S::kOffBar;
     const uint32_t q_full = bars, s_full = bars + 8, s_free = bars + 16, p_full = bars + 24, pv_done = bars + 32;
     auto kv_full = [&](int s) { return bars + 40u + 8u * s; };
-    auto kv_empty = [&](int s) { return bars + 40u + 8u * kStages + 8u * s; };
-    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + kOffBar + 128);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kOffBar + 136);
+    auto kv_empty = [&](int s) { return bars + 40u + 8u * S::kStages + 8u * s; };
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + S::kOffBar + 128);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + S::kOffBar + 136);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int start = start_pos[b];
@@ -187,7 +205,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const int k_max = start + tile * BQ + rows_here - 1;         // last key any row of the tile sees
     const int k_min = window > 0 ? max(0, start + tile * BQ - window + 1) : 0;
     const int j_lo = k_min / kPageTokens, j_hi = k_max / kPageTokens;
-    const int n_steps = (j_hi - j_lo + 2) / 2;                   // two pages per step
+    const int n_steps = (j_hi - j_lo + S::kPages) / S::kPages;
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
@@ -195,7 +213,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         mbar_init(s_free, 4);                                    // one arrival per softmax warp
         mbar_init(p_full, 4);
         mbar_init(pv_done, 1);
-        for (int s = 0; s < kStages; ++s) { mbar_init(kv_full(s), 1); mbar_init(kv_empty(s), 1); }
+        for (int s = 0; s < S::kStages; ++s) { mbar_init(kv_full(s), 1); mbar_init(kv_empty(s), 1); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::);
     }
@@ -207,42 +225,51 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::);
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::);
-    const uint32_t tmem_s = *tmem_holder, tmem_o = tmem_s + 128, tmem_p = tmem_s + 192;
+    const uint32_t tmem_s = *tmem_holder, tmem_o = tmem_s + S::kColO, tmem_p = tmem_s + S::kColP;
     chain_wait();                                                // queries, keys and values come from the kernel before
     chain_release();
 
     if (warp == 4) {
         // ------------------------------------------------------------ TMA producer
         if (lane == 0) {
-            mbar_expect_tx(q_full, kQBytes);
-            tma_load_2d(base, &map_q, h * HD, q_begin + tile * BQ, q_full);
+            mbar_expect_tx(q_full, S::kQBytes);
+            for (int hh = 0; hh < S::kHalves; ++hh)
+                tma_load_2d(base + hh * (BQ * 128), &map_q, h * HD + 64 * hh, q_begin + tile * BQ, q_full);
             for (int i = 0; i < n_steps; ++i) {
-                const int s = i % kStages;
-                if (!mbar_wait(kv_empty(s), (((uint32_t)i / kStages) & 1u) ^ 1u, abort_flag)) break;
-                const int ja = j_lo + 2 * i;
-                // a missing second page is the first one again: finite values under keys that no row sees
-                const int page_a = table[ja], page_b = ja + 1 <= j_hi ? table[ja + 1] : page_a;
-                const uint32_t dst = base + kOffKV + s * kStageBytes;
-                mbar_expect_tx(kv_full(s), kStageBytes);
-                tma_load_2d(dst, &map_kv, 0, ((page_a * 2 + 0) * n_kv + kvh) * kPageTokens, kv_full(s));
-                tma_load_2d(dst + kPageBytes, &map_kv, 0, ((page_b * 2 + 0) * n_kv + kvh) * kPageTokens, kv_full(s));
-                tma_load_2d(dst + 2 * kPageBytes, &map_kv, 0, ((page_a * 2 + 1) * n_kv + kvh) * kPageTokens, kv_full(s));
-                tma_load_2d(dst + 3 * kPageBytes, &map_kv, 0, ((page_b * 2 + 1) * n_kv + kvh) * kPageTokens, kv_full(s));
+                const int s = i % S::kStages;
+                if (!mbar_wait(kv_empty(s), (((uint32_t)i / S::kStages) & 1u) ^ 1u, abort_flag)) break;
+                const uint32_t dst = base + S::kOffKV + s * S::kStageBytes;
+                mbar_expect_tx(kv_full(s), S::kStageBytes);
+                for (int pg = 0; pg < S::kPages; ++pg) {
+                    // a page beyond the last one is the step's first page again: finite values under keys that no row sees
+                    const int j = j_lo + S::kPages * i + pg;
+                    const int page = table[j <= j_hi ? j : j_lo + S::kPages * i];
+                    for (int kv = 0; kv < 2; ++kv) {
+                        const int row = ((page * 2 + kv) * n_kv + kvh) * kPageTokens;
+                        for (int hh = 0; hh < S::kHalves; ++hh)
+                            tma_load_2d(dst + kv * S::kTileBytes + (hh * S::kPages + pg) * kBlockBytes, &map_kv,
+                                        64 * hh, row, kv_full(s));
+                    }
+                }
             }
         }
     } else if (warp == 5) {
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
-            const uint32_t idesc_s = umma_idesc(BQ, BK, 0);               // S[128 x 128 keys], key pages K-major
-            const uint32_t idesc_pv = umma_idesc(BQ, HD, 1);              // O[128 x 64 channels], value pages MN-major
+            const uint32_t idesc_s = umma_idesc(BQ, BK, 0);               // S[128 x BK keys], key pages K-major
+            const uint32_t idesc_pv = umma_idesc(BQ, HD, 1);              // O[128 x HD channels], value pages MN-major
             bool ok = mbar_wait(q_full, 0, abort_flag);
             auto issue_s = [&](int i) {
-                const int s = i % kStages;
-                if (!mbar_wait(kv_full(s), ((uint32_t)i / kStages) & 1u, abort_flag)) return false;
+                const int s = i % S::kStages;
+                if (!mbar_wait(kv_full(s), ((uint32_t)i / S::kStages) & 1u, abort_flag)) return false;
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::);
-                const uint64_t dq = umma_desc(base), dk = umma_desc(base + kOffKV + s * kStageBytes);
+                const uint32_t kbase = base + S::kOffKV + s * S::kStageBytes;
 #pragma unroll
-                for (int kk = 0; kk < HD / 16; ++kk) umma_ss(tmem_s, dq + 2 * kk, dk + 2 * kk, idesc_s, kk > 0 ? 1u : 0u);
+                for (int kk = 0; kk < HD / 16; ++kk) {                     // 16 channels per step, 64 per swizzled block
+                    const uint64_t dq = umma_desc(base + (kk / 4) * (BQ * 128)) + 2 * (kk % 4);
+                    const uint64_t dk = umma_desc(kbase + (kk / 4) * (BK * 128)) + 2 * (kk % 4);
+                    umma_ss(tmem_s, dq, dk, idesc_s, kk > 0 ? 1u : 0u);
+                }
                 umma_commit(s_full);
                 return true;
             };
@@ -255,8 +282,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 ok = mbar_wait(p_full, (uint32_t)i & 1u, abort_flag);     // P_i is in TMEM, O rescaled if it had to be
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::);
-                const int s = i % kStages;
-                const uint64_t dv = umma_desc(base + kOffKV + s * kStageBytes + 2 * kPageBytes);
+                const int s = i % S::kStages;
+                const uint64_t dv = umma_desc(base + S::kOffKV + s * S::kStageBytes + S::kTileBytes, BK * 128);
 #pragma unroll
                 for (int kk = 0; kk < BK / 16; ++kk)                       // 16 keys per step: 8 columns of P, two 8-key groups of V
                     umma_ts(tmem_o, tmem_p + 8 * kk, dv + (uint64_t)(2 * 1024 >> 4) * kk, idesc_pv, (i > 0 || kk > 0) ? 1u : 0u);
@@ -275,7 +302,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         uint32_t sv[BK];
         bool ok = true;
         for (int i = 0; i < n_steps; ++i) {
-            const int key0 = (j_lo + 2 * i) * kPageTokens;       // position of the step's first key
+            const int key0 = (j_lo + S::kPages * i) * kPageTokens;   // position of the step's first key
             ok = __all_sync(full, mbar_wait(s_full, (uint32_t)i & 1u, abort_flag));
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::);
@@ -332,27 +359,22 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             }
             const float m_use = m_run == -INFINITY ? 0.f : m_run;
             float l0 = 0.f, l1 = 0.f;
-            // the row of P: 128 bfloat16 as 64 packed columns, written 32 columns at a time.
-            // Eight exponentials are issued back to back (the special-function unit takes
-            // one warp instruction every 8 cycles and answers after some tens of cycles)
-            // before the first of them is used.
+            // the row of P: BK bfloat16 as BK/2 packed columns (packed in place: the
+            // pair of scores 2c, 2c+1 becomes word c).  Eight exponentials are issued
+            // back to back before the first of them is used.
 #pragma unroll
-            for (int half = 0; half < 2; ++half) {
+            for (int c = 0; c < BK / 2; c += 4) {
+                float p[8];
 #pragma unroll
-                for (int c = 0; c < 32; c += 4) {
-                    float p[8];
+                for (int e = 0; e < 8; ++e) p[e] = fmaf(__uint_as_float(sv[2 * c + e]), sl2, -m_use);
 #pragma unroll
-                    for (int e = 0; e < 8; ++e)
-                        p[e] = fmaf(__uint_as_float(sv[64 * half + 2 * c + e]), sl2, -m_use);
+                for (int e = 0; e < 8; ++e) p[e] = exp2_in_order(p[e]);
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) p[e] = exp2_in_order(p[e]);
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        l0 += p[2 * e];
-                        l1 += p[2 * e + 1];
-                        __nv_bfloat162 hh = __floats2bfloat162_rn(p[2 * e], p[2 * e + 1]);
-                        sv[64 * half + c + e] = *reinterpret_cast<uint32_t*>(&hh);   // the scores at and below this index are done with
-                    }
+                for (int e = 0; e < 4; ++e) {
+                    l0 += p[2 * e];
+                    l1 += p[2 * e + 1];
+                    __nv_bfloat162 hh = __floats2bfloat162_rn(p[2 * e], p[2 * e + 1]);
+                    sv[c + e] = *reinterpret_cast<uint32_t*>(&hh);   // the scores at and below this index are done with
                 }
             }
             // P_i goes where P_{i-1} was: its product must have read it (it has, long ago,
@@ -361,8 +383,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 ok = __all_sync(full, mbar_wait(pv_done, (uint32_t)(i - 1) & 1u, abort_flag));
                 if (!ok) break;
             }
-            tmem_st32(tmem_p + lane_off, sv);
-            tmem_st32(tmem_p + lane_off + 32, sv + 64);
+#pragma unroll
+            for (int c = 0; c < BK / 64; ++c) tmem_st32(tmem_p + lane_off + 32 * c, sv + 32 * c);
             l_run += l0 + l1;
             asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::);
@@ -372,22 +394,24 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         if (ok) ok = __all_sync(full, mbar_wait(pv_done, (uint32_t)(n_steps - 1) & 1u, abort_flag));
         if (ok) {
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::);
-            tmem_ld32(tmem_o + lane_off, sv);
-            tmem_ld32(tmem_o + lane_off + 32, sv + 32);
-            asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-            if (r < rows_here) {
-                const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
-                bf16* dst = out + (size_t)(q_begin + tile * BQ + r) * ldo + h * HD;
+            const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+            bf16* dst = out + (size_t)(q_begin + tile * BQ + r) * ldo + h * HD;
+#pragma unroll 1
+            for (int c = 0; c < HD / 32; ++c) {
+                tmem_ld32(tmem_o + lane_off + 32 * c, sv);
+                asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+                if (r < rows_here) {
 #pragma unroll
-                for (int piece = 0; piece < 8; ++piece) {
-                    uint32_t o4[4];
+                    for (int piece = 0; piece < 4; ++piece) {
+                        uint32_t o4[4];
 #pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        __nv_bfloat162 hh = __floats2bfloat162_rn(__uint_as_float(sv[8 * piece + 2 * q]) * inv,
-                                                                  __uint_as_float(sv[8 * piece + 2 * q + 1]) * inv);
-                        o4[q] = *reinterpret_cast<uint32_t*>(&hh);
+                        for (int q = 0; q < 4; ++q) {
+                            __nv_bfloat162 hh = __floats2bfloat162_rn(__uint_as_float(sv[8 * piece + 2 * q]) * inv,
+                                                                      __uint_as_float(sv[8 * piece + 2 * q + 1]) * inv);
+                            o4[q] = *reinterpret_cast<uint32_t*>(&hh);
+                        }
+                        *reinterpret_cast<uint4*>(dst + 32 * c + 8 * piece) = make_uint4(o4[0], o4[1], o4[2], o4[3]);
                     }
-                    *reinterpret_cast<uint4*>(dst + 8 * piece) = make_uint4(o4[0], o4[1], o4[2], o4[3]);
                 }
             }
         }
@@ -427,6 +451,23 @@ int make_map(CUtensorMap* map, const void* ptr, long long rows, int cols, long l
                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? 0 : kErrBadArgument;
 }
+
+template <int HD>
+int launch(const CUtensorMap& map_q, const CUtensorMap& map_kv, bf16* out, int ldo, const int* block_table,
+           int table_stride, const int* cu_seqlens, const int* slots, const int* start_pos, int B, int max_q_len,
+           int n_heads, int n_kv, float scale, int window, cudaStream_t stream) {
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             Shape<HD>::kSmemBytes);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    dim3 grid(n_heads, B, (max_q_len + BQ - 1) / BQ);
+    return launch_chained(attention_prefill_tc_kernel<HD>, grid, dim3(kThreads), (size_t)Shape<HD>::kSmemBytes, stream,
+                          map_q, map_kv, out, ldo, block_table, table_stride, cu_seqlens, slots, start_pos,
+                          n_heads, n_kv, scale, window);
+}
 }  // namespace
 
 GTG_API int gtg_attention_tcgen05_status() {
@@ -435,11 +476,11 @@ GTG_API int gtg_attention_tcgen05_status() {
     return v;
 }
 
-// What this kernel serves: heads of 64 channels whose keys and values lie in one
-// cache entry as [page][k|v][head][token][channel] (values right after the keys).
-GTG_API int gtg_attention_tcgen05_supports(int hd) { return hd == HD; }
+// What this kernel serves: heads of 64 or 128 channels whose keys and values lie in
+// one cache entry as [page][k|v][head][token][channel] (values right after the keys).
+GTG_API int gtg_attention_tcgen05_supports(int hd) { return hd == 64 || hd == 128; }
 
-// q: [n_tokens, ldq] with head h at columns h*64; kc, vc: the entry's key and value
+// q: [n_tokens, ldq] with head h at columns h*hd; kc, vc: the entry's key and value
 // bases; page_stride: elements between pages.  n_pages: pages of the entry's pool.
 GTG_API int gtg_attention_prefill_tcgen05(const void* q, int ldq, int n_tokens, void* out, int ldo,
                                           const void* kc, const void* vc, long long page_stride, int n_pages,
@@ -448,27 +489,22 @@ GTG_API int gtg_attention_prefill_tcgen05(const void* q, int ldq, int n_tokens, 
                                           int B, int max_q_len, int n_heads, int n_kv, int hd,
                                           float scale, int window, cudaStream_t stream) {
     if (B <= 0 || max_q_len <= 0) return 0;
-    if (hd != HD) return kErrUnsupported;
+    if (hd != 64 && hd != 128) return kErrUnsupported;
     if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv != 0) return kErrBadArgument;
     if (ldq % 8 || ldo % 8 || ((uintptr_t)q % 16) || ((uintptr_t)out % 16) || ((uintptr_t)kc % 16)) return kErrUnsupported;
     // keys then values of a page, contiguous: the layout the row arithmetic above assumes
     const long long kv_rows = 2LL * n_kv * kPageTokens;
-    if (page_stride != kv_rows * HD || (const bf16*)vc != (const bf16*)kc + (long long)n_kv * kPageTokens * HD)
+    if (page_stride != kv_rows * hd || (const bf16*)vc != (const bf16*)kc + (long long)n_kv * kPageTokens * hd)
         return kErrUnsupported;
     if (B > 65535 || (max_q_len + BQ - 1) / BQ > 65535 || (long long)n_pages * kv_rows > 0x7fffffffLL) return kErrUnsupported;
     CUtensorMap map_q, map_kv;
-    int st = make_map(&map_q, q, n_tokens, n_heads * HD, ldq, BQ);
+    int st = make_map(&map_q, q, n_tokens, n_heads * hd, ldq, BQ);
     if (st != 0) return st;
-    st = make_map(&map_kv, kc, (long long)n_pages * kv_rows, HD, HD, kPageTokens);
+    st = make_map(&map_kv, kc, (long long)n_pages * kv_rows, hd, hd, kPageTokens);
     if (st != 0) return st;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
-    dim3 grid(n_heads, B, (max_q_len + BQ - 1) / BQ);
-    return launch_chained(attention_prefill_tc_kernel, grid, dim3(kThreads), (size_t)kSmemBytes, stream, map_q, map_kv,
-                          (bf16*)out, ldo, block_table, table_stride, cu_seqlens, slots, start_pos, n_heads, n_kv,
-                          scale, window);
+    if (hd == 64)
+        return launch<64>(map_q, map_kv, (bf16*)out, ldo, block_table, table_stride, cu_seqlens, slots, start_pos,
+                          B, max_q_len, n_heads, n_kv, scale, window, stream);
+    return launch<128>(map_q, map_kv, (bf16*)out, ldo, block_table, table_stride, cu_seqlens, slots, start_pos,
+                       B, max_q_len, n_heads, n_kv, scale, window, stream);
 }

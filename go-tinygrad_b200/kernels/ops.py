@@ -364,11 +364,12 @@ def attention_prefill_bf16(q, out, kv, cu_seqlens, slots, start_pos, n_seqs: int
 
 
 def attention_tcgen05_supports(kv) -> bool:
-    """The tensor-core prompt attention serves heads of 64 channels whose keys and
-    values lie page by page as [k|v][head][token][channel]."""
-    return (kv.k.dtype == torch.bfloat16 and kv.head_dim == 64
-            and kv.page_stride == 2 * kv.n_kv_heads * 64 * 64
-            and kv.v.data_ptr() - kv.k.data_ptr() == kv.n_kv_heads * 64 * 64 * 2)
+    """The tensor-core prompt attention serves heads of 64 or 128 channels whose
+    keys and values lie page by page as [k|v][head][token][channel]."""
+    hd = kv.head_dim
+    return (kv.k.dtype == torch.bfloat16 and hd in (64, 128)
+            and kv.page_stride == 2 * kv.n_kv_heads * 64 * hd
+            and kv.v.data_ptr() - kv.k.data_ptr() == kv.n_kv_heads * 64 * hd * 2)
 
 
 def attention_prefill_tcgen05(q, out, kv, cu_seqlens, slots, start_pos, n_seqs: int, max_q_len: int,
@@ -377,7 +378,7 @@ def attention_prefill_tcgen05(q, out, kv, cu_seqlens, slots, start_pos, n_seqs: 
     _rows2d(q, "attention: q"); _rows2d(out, "attention: out")
     _need(q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16, "attention_prefill_tcgen05: bfloat16 only")
     _need(attention_tcgen05_supports(kv),
-          "attention_prefill_tcgen05: needs head_dim 64 and keys and values of a page side by side")
+          "attention_prefill_tcgen05: needs head_dim 64 or 128 and keys and values of a page side by side")
     _check(_fn("gtg_attention_prefill_tcgen05")(_ptr(q), q.stride(0), q.shape[0], _ptr(out), out.stride(0),
                                                 _ptr(kv.k), _ptr(kv.v), kv.page_stride, kv.k.shape[0],
                                                 _ptr(kv.block_table), kv.table_stride, _ptr(cu_seqlens),

@@ -351,13 +351,13 @@ def test_attention_simple(dtype, n_heads, n_kv, hd, window):
                                                      else dict(rtol=2e-2, atol=2e-2)))
 
 
-@pytest.mark.parametrize("n_heads,n_kv", [(1, 1), (6, 2), (5, 5), (8, 1)])
+@pytest.mark.parametrize("n_heads,n_kv,hd", [(1, 1, 64), (6, 2, 64), (5, 5, 64), (8, 1, 64), (6, 2, 128), (3, 3, 128)])
 @pytest.mark.parametrize("window", [0, 37, 64, 200])
 @pytest.mark.parametrize("lens_before,lens_new", [([0], [1]), ([0, 0, 0], [5, 129, 64]), ([0], [128]),
                                                   ([10, 64, 100], [70, 1, 200]), ([0], [300]),
                                                   ([577, 0], [450, 1000])])
-def test_attention_prefill_tcgen05(n_heads, n_kv, window, lens_before, lens_new):
-    cache, q, want, m, scale = attention_case(torch.bfloat16, n_heads, n_kv, 64, lens_before, lens_new, window)
+def test_attention_prefill_tcgen05(n_heads, n_kv, hd, window, lens_before, lens_new):
+    cache, q, want, m, scale = attention_case(torch.bfloat16, n_heads, n_kv, hd, lens_before, lens_new, window)
     kv = cache.handles[0].kv
     assert ops.attention_tcgen05_supports(kv)
     qbuf = torch.zeros(q.shape[0], q.shape[1] + 16, dtype=torch.bfloat16, device=DEV)   # strided q
