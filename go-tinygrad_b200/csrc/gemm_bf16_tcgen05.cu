@@ -126,11 +126,26 @@ __device__ __forceinline__ void store_values(OutT* dst, const uint32_t* v, int n
     }
 }
 
+// For epilogue 2 (the fused query/key/value projection of heads of 64 channels):
+// where a token's rotation table, cache page and place in the page are found.
+struct RopeKV {
+    const float2* cos_sin;       // [M][32] (cos, sin) of the token's position
+    const int* token_seq;        // [M] sequence of the step each token belongs to
+    const int* slots;            // [sequences] cache slot
+    const int* positions;        // [M]
+    const int* block_table;
+    int table_stride;
+    bf16* kc;                    // the cache entry's keys and values
+    bf16* vc;
+    long long page_stride;
+    int n_heads, n_kv;
+};
+
 template <typename OutT>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     const __grid_constant__ CUtensorMap map_c, int use_store_map,
-                    OutT* __restrict__ C, int ldc, int M, int N, int K, int epi) {
+                    OutT* __restrict__ C, int ldc, int M, int N, int K, int epi, RopeKV rope) {
     extern __shared__ unsigned char smem_raw[];
     const uint32_t base = (smem_addr(smem_raw) + 1023u) & ~1023u;        // tiles need 1024-byte alignment
     unsigned char* aligned = smem_raw + (base - smem_addr(smem_raw));
@@ -232,7 +247,84 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::);
             const int row = m0 + warp * 32 + lane;
             const uint32_t tmem_row = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(acc * BN);
-            if (staged) {
+            if (epi == 2) {
+                // Query/key/value heads of 64 channels: a box of 64 columns is one head, its two
+                // chunks hold the rotation's pairs (d, d + 32).  Query heads are rotated and stored
+                // like any output; key heads are rotated and written into the token's cache page,
+                // value heads are copied there (the projection's key and value columns are not stored).
+                const bool live = row < M;
+                size_t cache_at = 0;                       // of (key/value head 0, this token, channel 0)
+                if (live) {
+                    const int pos = rope.positions[row];
+                    const int page = rope.block_table[(size_t)rope.slots[rope.token_seq[row]] * rope.table_stride + pos / kPageTokens];
+                    cache_at = (size_t)page * rope.page_stride + (size_t)(pos % kPageTokens) * 64;
+                }
+                const float4* cs = reinterpret_cast<const float4*>(rope.cos_sin + (size_t)(live ? row : 0) * 32);
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN / 32; c0 += 2) {
+                    const int col = n0 + c0 * 32;
+                    if (col >= N) break;
+                    const int head = col >> 6;
+                    uint32_t v0[32], v1[32];
+                    tmem_ld32(tmem_row + (uint32_t)(c0 * 32), v0);
+                    tmem_ld32(tmem_row + (uint32_t)((c0 + 1) * 32), v1);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+                    if (head < rope.n_heads + rope.n_kv) {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 2) {
+                            const float4 t = cs[i >> 1];   // (cos, sin) of channels i and i + 1
+                            const float a0 = __uint_as_float(v0[i]), b0 = __uint_as_float(v1[i]);
+                            const float a1 = __uint_as_float(v0[i + 1]), b1 = __uint_as_float(v1[i + 1]);
+                            v0[i] = __float_as_uint(a0 * t.x - b0 * t.y);
+                            v1[i] = __float_as_uint(a0 * t.y + b0 * t.x);
+                            v0[i + 1] = __float_as_uint(a1 * t.z - b1 * t.w);
+                            v1[i + 1] = __float_as_uint(a1 * t.w + b1 * t.z);
+                        }
+                    }
+                    // 64 values -> eight 16-byte pieces
+                    uint4 pieces[8];
+#pragma unroll
+                    for (int piece = 0; piece < 4; ++piece) {
+                        uint32_t lo[4], hi[4];
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(v0[8 * piece + 2 * q]),
+                                                                      __uint_as_float(v0[8 * piece + 2 * q + 1]));
+                            __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(v1[8 * piece + 2 * q]),
+                                                                      __uint_as_float(v1[8 * piece + 2 * q + 1]));
+                            lo[q] = *reinterpret_cast<uint32_t*>(&h0);
+                            hi[q] = *reinterpret_cast<uint32_t*>(&h1);
+                        }
+                        pieces[piece] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                        pieces[piece + 4] = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+                    }
+                    if (head < rope.n_heads) {
+                        unsigned char* buf = stage_base + (groups & 1u) * kStoreBytes;
+                        if (groups >= 2) {                 // the box stored from this buffer two rounds ago has been read
+                            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;\n" ::: "memory");
+                            __syncwarp();
+                        }
+#pragma unroll
+                        for (int piece = 0; piece < 8; ++piece)
+                            *reinterpret_cast<uint4*>(buf + lane * 128 + ((piece ^ (lane & 7)) << 4)) = pieces[piece];
+                        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // generic writes -> TMA reads
+                        __syncwarp();
+                        if (lane == 0) {
+                            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];\n"
+                                         ::"l"(&map_c), "r"(smem_addr(buf)), "r"(col), "r"(m0 + warp * 32) : "memory");
+                            asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
+                        }
+                        ++groups;
+                    } else if (live) {
+                        const bool is_key = head < rope.n_heads + rope.n_kv;
+                        const int kvh = head - rope.n_heads - (is_key ? 0 : rope.n_kv);
+                        uint4* dst = reinterpret_cast<uint4*>((is_key ? rope.kc : rope.vc) + cache_at +
+                                                              (size_t)kvh * kPageTokens * 64);
+#pragma unroll
+                        for (int piece = 0; piece < 8; ++piece) dst[piece] = pieces[piece];
+                    }
+                }
+            } else if (staged) {
                 const int per_box = epi ? 4 : 2;           // accumulator chunks of 32 columns per 64 output columns
 #pragma unroll 1
                 for (int c0 = 0; c0 < BN / 32; c0 += per_box, ++groups) {
@@ -367,14 +459,14 @@ GTG_API int gtg_gemm_bf16_tcgen05_status() {
     return v;
 }
 
-// epilogue 0: C[M,N] = A W^T.  epilogue 1: W's rows come in blocks of 8 gate
-// features followed by their 8 up features, and C[M,N/2] = silu(gate) * up.
-GTG_API int gtg_gemm_bf16_tcgen05(const void* A, int lda, const void* W, int ldw, void* C, int ldc,
-                                  int out_f32, int M, int N, int K, int epilogue, cudaStream_t stream) {
+namespace {
+// epilogue 0: C[M,N] = A W^T.  1: SwiGLU over interleaved rows.  2: rotation and cache store (rope).
+int run(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int out_f32, int M, int N, int K,
+        int epilogue, const RopeKV& rope, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
-    if (epilogue != 0 && epilogue != 1) return kErrBadArgument;
+    if (epilogue < 0 || epilogue > 2) return kErrBadArgument;
     if (epilogue == 1 && N % 16 != 0) return kErrUnsupported;
-    if (K <= 0 || lda < K || ldw < K || ldc < (epilogue ? N / 2 : N)) return kErrBadArgument;
+    if (K <= 0 || lda < K || ldw < K || ldc < (epilogue == 1 ? N / 2 : N)) return kErrBadArgument;
     if (K % 8 || lda % 8 || ldw % 8 || ((uintptr_t)A % 16) || ((uintptr_t)W % 16)) return kErrUnsupported;
     const long long tiles = (long long)((N + BN - 1) / BN) * ((M + BM - 1) / BM);
     if (tiles > 0x7fffffffLL) return kErrUnsupported;
@@ -384,12 +476,13 @@ GTG_API int gtg_gemm_bf16_tcgen05(const void* A, int lda, const void* W, int ldw
     st = make_map(&map_w, W, N, K, ldw, BN);
     if (st != 0) return st;
     // the store map: C as [M, output width] bfloat16 in boxes of 64 x 32 (when its rows allow it)
-    const int n_out = epilogue ? N / 2 : N;
+    const int n_out = epilogue == 1 ? N / 2 : N;
     CUtensorMap map_c = map_a;
     int use_store_map = 0;
     if (!out_f32 && ldc % 8 == 0 && ((uintptr_t)C % 16) == 0) {
         if (make_map(&map_c, C, M, n_out, ldc, 32) == 0) use_store_map = 1;
     }
+    if (epilogue == 2 && !use_store_map) return kErrUnsupported;
     static bool configured = false;
     static int sms = 148;
     if (!configured) {
@@ -406,7 +499,34 @@ GTG_API int gtg_gemm_bf16_tcgen05(const void* A, int lda, const void* W, int ldw
     const int grid = (int)(tiles < sms ? tiles : sms);
     if (out_f32)
         return launch_chained(gemm_tcgen05_kernel<float>, dim3(grid), dim3(kThreads), (size_t)kSmemBytes, stream,
-                              map_a, map_w, map_c, use_store_map, (float*)C, ldc, M, N, K, epilogue);
+                              map_a, map_w, map_c, use_store_map, (float*)C, ldc, M, N, K, epilogue, rope);
     return launch_chained(gemm_tcgen05_kernel<bf16>, dim3(grid), dim3(kThreads), (size_t)kSmemBytes, stream,
-                          map_a, map_w, map_c, use_store_map, (bf16*)C, ldc, M, N, K, epilogue);
+                          map_a, map_w, map_c, use_store_map, (bf16*)C, ldc, M, N, K, epilogue, rope);
+}
+}  // namespace
+
+// epilogue 0: C[M,N] = A W^T.  epilogue 1: W's rows come in blocks of 8 gate
+// features followed by their 8 up features, and C[M,N/2] = silu(gate) * up.
+GTG_API int gtg_gemm_bf16_tcgen05(const void* A, int lda, const void* W, int ldw, void* C, int ldc,
+                                  int out_f32, int M, int N, int K, int epilogue, cudaStream_t stream) {
+    if (epilogue != 0 && epilogue != 1) return kErrBadArgument;
+    return run(A, lda, W, ldw, C, ldc, out_f32, M, N, K, epilogue, RopeKV{}, stream);
+}
+
+// The query/key/value projection of heads of 64 channels with what follows it
+// fused into the epilogue: W = [Wq; Wk; Wv] with (n_heads + 2 n_kv) * 64 rows;
+// the query columns of C receive the rotated queries; rotated keys and the
+// values go straight into the cache entry (kc, vc, page_stride, block_table) at
+// each token's (slot, position); C's key and value columns are left untouched.
+// cos_sin: float [M][32][2].
+GTG_API int gtg_gemm_bf16_tcgen05_qkv_rope(const void* A, int lda, const void* W, int ldw, void* C, int ldc,
+                                           int M, int K, const void* cos_sin, const int* token_seq,
+                                           const int* slots, const int* positions, const int* block_table,
+                                           int table_stride, void* kc, void* vc, long long page_stride,
+                                           int n_heads, int n_kv, cudaStream_t stream) {
+    if (n_heads <= 0 || n_kv <= 0 || cos_sin == nullptr || kc == nullptr || vc == nullptr) return kErrBadArgument;
+    if (((uintptr_t)cos_sin % 16) || ((uintptr_t)kc % 16) || ((uintptr_t)vc % 16) || page_stride % 8) return kErrUnsupported;
+    RopeKV rope{(const float2*)cos_sin, token_seq, slots, positions, block_table, table_stride,
+                (bf16*)kc, (bf16*)vc, page_stride, n_heads, n_kv};
+    return run(A, lda, W, ldw, C, ldc, 0, M, (n_heads + 2 * n_kv) * 64, K, 2, rope, stream);
 }

@@ -33,6 +33,8 @@ _SIGNATURES = {
     "gtg_gemm_bf16_skinny_status": ("gemm_bf16_skinny", []),
     "gtg_gemm_bf16_tcgen05": ("gemm_bf16_tcgen05", [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _P]),
     "gtg_gemm_bf16_tcgen05_status": ("gemm_bf16_tcgen05", []),
+    "gtg_gemm_bf16_tcgen05_qkv_rope": ("gemm_bf16_tcgen05", [_P, _I, _P, _I, _P, _I, _I, _I, _P, _P, _P, _P, _P, _I,
+                                                             _P, _P, _L, _I, _I, _P]),
     "gtg_gemm_bf16_swapab": ("gemm_bf16_swapab", [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _P, _P]),
     "gtg_gemm_bf16_swapab_scratch_floats": ("gemm_bf16_swapab", [_I, _I, _I]),
     "gtg_gemm_bf16_swapab_status": ("gemm_bf16_swapab", []),
@@ -316,6 +318,43 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, kind: str = "aut
         code = _fn(symbol)(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0),
                            out_f32, M, N, K, 1 if epilogue == "swiglu" else 0, _stream())
     _check(code, "linear(bfloat16)")
+
+
+def qkv_rope_fused_supports(x: torch.Tensor, w: torch.Tensor, qkv: torch.Tensor, cos_sin, n_heads: int,
+                            n_kv_heads: int, head_dim: int, kv) -> bool:
+    """Whether `linear_qkv_rope` takes these operands: a prompt-sized bfloat16
+    product (more rows than the weight-streaming kernels take), heads of 64
+    channels, a rotation table, and operands the tensor copies can address."""
+    return (cos_sin is not None and kv is not None and head_dim == 64 and x.shape[0] > SKINNY_MAX_ROWS
+            and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and qkv.dtype == torch.bfloat16
+            and kv.k.dtype == torch.bfloat16 and kv.head_dim == 64 and kv.n_kv_heads == n_kv_heads
+            and w.shape[0] == (n_heads + 2 * n_kv_heads) * 64 and qkv.shape[1] == w.shape[0]
+            and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and qkv.stride(0) % 8 == 0
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and qkv.data_ptr() % 16 == 0
+            and kv.page_stride % 8 == 0)
+
+
+def linear_qkv_rope(x: torch.Tensor, w: torch.Tensor, qkv: torch.Tensor, cos_sin: torch.Tensor, n_heads: int,
+                    n_kv_heads: int, kv, token_seq: torch.Tensor, slots: torch.Tensor,
+                    positions: torch.Tensor) -> None:
+    """The query/key/value projection of a prompt with rotation and cache store in
+    its epilogue (heads of 64 channels): qkv[:, :n_heads*64] = rotated queries;
+    rotated keys and the values go into `kv` at each token's (slot, position); the
+    key and value columns of qkv are not written.  What `linear` followed by
+    `rope_kv_store` computes, with the rotation applied to the float accumulators."""
+    _rows2d(x, "linear_qkv_rope: x"); _rows2d(w, "linear_qkv_rope: w"); _rows2d(qkv, "linear_qkv_rope: qkv")
+    _need(qkv_rope_fused_supports(x, w, qkv, cos_sin, n_heads, n_kv_heads, 64, kv),
+          "linear_qkv_rope: operands not supported (see qkv_rope_fused_supports)")
+    M, K = x.shape
+    _need(w.shape[1] == K and qkv.shape[0] == M, "linear_qkv_rope: shapes do not agree")
+    _need(cos_sin.dtype == torch.float32 and cos_sin.is_contiguous() and tuple(cos_sin.shape) == (M, 32, 2),
+          "linear_qkv_rope: cos_sin must be float32 [M, 32, 2]")
+    for name, t in (("token_seq", token_seq), ("slots", slots), ("positions", positions)):
+        _need(t.dtype == torch.int32 and t.is_contiguous(), f"linear_qkv_rope: {name} must be contiguous int32")
+    _check(_fn("gtg_gemm_bf16_tcgen05_qkv_rope")(
+        _ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(qkv), qkv.stride(0), M, K, _ptr(cos_sin),
+        _ptr(token_seq), _ptr(slots), _ptr(positions), _ptr(kv.block_table), kv.table_stride,
+        _ptr(kv.k), _ptr(kv.v), kv.page_stride, n_heads, n_kv_heads, _stream()), "linear_qkv_rope")
 
 
 def bounded_wait_failures() -> int:

@@ -100,10 +100,17 @@ class GQAttention(Mixer):
             raise ValueError("attention was given a cache entry that does not match its heads")
         n = x.shape[0]
         qkv = rt.empty(n, self.w_qkv.shape[0])
-        ops.linear(x, self.w_qkv, qkv)
+        rotation = self.position.rotation(ctx)
         store = self.n_kv if (cache.writes and self.own_kv) else 0
-        ops.rope_kv_store(qkv, self.position.rotation(ctx), self.n_heads, store, self.head_dim,
-                          kv, ctx.token_seq, ctx.slots, ctx.positions)
+        if store and ops.qkv_rope_fused_supports(x, self.w_qkv, qkv, rotation, self.n_heads, self.n_kv,
+                                                 self.head_dim, kv):
+            # a prompt: rotation and cache store happen in the projection's epilogue
+            ops.linear_qkv_rope(x, self.w_qkv, qkv, rotation, self.n_heads, self.n_kv, kv,
+                                ctx.token_seq, ctx.slots, ctx.positions)
+        else:
+            ops.linear(x, self.w_qkv, qkv)
+            ops.rope_kv_store(qkv, rotation, self.n_heads, store, self.head_dim,
+                              kv, ctx.token_seq, ctx.slots, ctx.positions)
         q = qkv[:, : self.q_dim]
         mixed = rt.empty(n, self.q_dim)
         window = self.window or 0

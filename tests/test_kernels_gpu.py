@@ -129,6 +129,58 @@ def read_sequence(cache, entry, slot, T):
     return k, v
 
 
+@pytest.mark.parametrize("n_heads,n_kv,K", [(8, 8, 256), (6, 2, 520), (3, 1, 64), (32, 8, 2048)])
+def test_qkv_projection_with_rotation_and_cache_store_in_its_epilogue(n_heads, n_kv, K):
+    """linear_qkv_rope against the plain product followed by the plain rotation:
+    rotated queries in the output, rotated keys and values in the cache at each
+    token's (slot, position), other cache entries and pages untouched."""
+    hd, dtype = 64, torch.bfloat16
+    cache = make_cache(n_kv, hd, dtype)
+    slots = [cache.open_sequence() for _ in range(3)]
+    starts, lens = [0, 61, 130], [70, 129, 3]     # runs that cross page borders; 202 rows: two row tiles
+    for s, st, n in zip(slots, starts, lens):
+        cache.reserve(s, st + n)
+        cache._length[s] = st
+    cache.flush_tables()
+    N, width = sum(lens), (n_heads + 2 * n_kv) * hd
+    x = rnd(N, K, dtype=dtype, seed=3, scale=0.5)
+    w = rnd(width, K, dtype=dtype, seed=4, scale=0.2)
+    positions = torch.tensor([st + j for st, n in zip(starts, lens) for j in range(n)], dtype=torch.int32, device=DEV)
+    token_seq = torch.tensor([b for b, n in enumerate(lens) for _ in range(n)], dtype=torch.int32, device=DEV)
+    slot_t = torch.tensor(slots, dtype=torch.int32, device=DEV)
+    inv = torch.tensor([1.0 / math.pow(10000.0, 2 * i / hd) for i in range(32)], dtype=torch.float64, device=DEV)
+    cs = torch.empty(N, 32, 2, dtype=torch.float32, device=DEV)
+    ops.rope_table(positions, inv, cs)
+    kv = cache.handles[1].kv
+    qkv = torch.full((N, width), 7.0, dtype=dtype, device=DEV)
+    assert ops.qkv_rope_fused_supports(x, w, qkv, cs, n_heads, n_kv, hd, kv)
+    ops.linear_qkv_rope(x, w, qkv, cs, n_heads, n_kv, kv, token_seq, slot_t, positions)
+    assert ops.bounded_wait_failures() == 0
+
+    full = x.double() @ w.double().T
+
+    def rot(t, nh):
+        t = t.reshape(N, nh, hd)
+        a, b = t[..., :32], t[..., 32:]
+        c, s = cs[:, None, :, 0].double(), cs[:, None, :, 1].double()
+        return torch.cat([a * c - b * s, a * s + b * c], dim=-1)
+    scale = float(full.abs().max())
+    want_q = rot(full[:, : n_heads * hd], n_heads).reshape(N, -1).float()
+    want_k = rot(full[:, n_heads * hd: (n_heads + n_kv) * hd], n_kv).float()
+    want_v = full[:, (n_heads + n_kv) * hd:].reshape(N, n_kv, hd).float()
+    close = dict(rtol=1.6e-2, atol=1e-2 * max(1.0, scale / 4))
+    torch.testing.assert_close(qkv[:, : n_heads * hd].float(), want_q, **close)
+    assert float((qkv[:, n_heads * hd:].float() - 7.0).abs().sum()) == 0.0    # key and value columns are not written
+    o = 0
+    for s, st, n in zip(slots, starts, lens):
+        k, v = read_sequence(cache, 1, s, st + n)
+        torch.testing.assert_close(k[st:].float(), want_k[o:o + n], **close)
+        torch.testing.assert_close(v[st:].float(), want_v[o:o + n], **close)
+        assert float(k[:st].abs().sum()) == 0.0            # nothing written before the run
+        o += n
+    assert float(cache.handles[0].kv.k.abs().sum()) == 0.0  # the other entry is untouched
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("n_heads,n_kv,hd", [(4, 2, 16), (3, 1, 48), (8, 8, 64), (5, 5, 112), (2, 2, 24), (32, 8, 128)])
 def test_rope_kv_store(dtype, n_heads, n_kv, hd):
