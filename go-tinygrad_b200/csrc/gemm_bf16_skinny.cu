@@ -449,6 +449,22 @@ int launch_stream(const bf16* X, int ldx, const bf16* W, int ldw, OutT* C, int l
     attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    // A cluster needs all its CTAs in one GPC, so fewer clusters can be resident than
+    // 2 * SMs / ranks says; a grid beyond that runs its last clusters as a second wave.
+    static int resident[kMaxCluster + 1] = {};
+    if (ranks > 1 && resident[ranks] == 0) {
+        int n = 0;
+        resident[ranks] = cudaOccupancyMaxActiveClusters(&n, gemm_stream_kernel<NT, OutT>, &cfg) == cudaSuccess && n > 0
+                              ? n : -1;
+        cudaGetLastError();
+    }
+    if (ranks > 1 && resident[ranks] > 0 && (int)cfg.gridDim.x > resident[ranks]) {
+        // the fewest clusters that still finish in as many rounds of row tiles: what the
+        // count above leaves free absorbs clusters that find no four free places at once
+        const int rounds = (row_tiles + resident[ranks] - 1) / resident[ranks];
+        cfg.gridDim.x = (row_tiles + rounds - 1) / rounds;
+    }
     cfg.numAttrs = g_chained_launch ? 2 : 1;
     cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_stream_kernel<NT, OutT>, X, ldx, map_w, C, ldc, M, N, K, k_slice, epi);
     if (e != cudaSuccess) return (int)e;
