@@ -42,6 +42,25 @@ SMOLLM2_1P7B = {
     "rope_theta": 130000.0, "rope_scaling": None, "rms_norm_eps": 1e-5,
     "tie_word_embeddings": True, "max_position_embeddings": 8192,
 }
+LLAMA3_SCALING = {"rope_type": "llama3", "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                  "original_max_position_embeddings": 8192}
+# The other shapes the reference's engine names, for measurements beside the default.
+LLAMA_3P2_1B = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "num_hidden_layers": 16, "hidden_size": 2048, "num_attention_heads": 32,
+    "num_key_value_heads": 8, "head_dim": 64, "intermediate_size": 8192, "vocab_size": 128256,
+    "rope_theta": 500000.0, "rope_scaling": dict(LLAMA3_SCALING, factor=32.0), "rms_norm_eps": 1e-5,
+    "tie_word_embeddings": True, "max_position_embeddings": 131072,
+}
+LLAMA_3P1_8B = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "num_hidden_layers": 32, "hidden_size": 4096, "num_attention_heads": 32,
+    "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 14336, "vocab_size": 128256,
+    "rope_theta": 500000.0, "rope_scaling": dict(LLAMA3_SCALING, factor=8.0), "rms_norm_eps": 1e-5,
+    "tie_word_embeddings": False, "max_position_embeddings": 131072,
+}
+SHAPES = {"smollm2-1.7b": ("SmolLM2-1.7B", SMOLLM2_1P7B), "llama-3.2-1b": ("Llama-3.2-1B", LLAMA_3P2_1B),
+          "llama-3.1-8b": ("Llama-3.1-8B", LLAMA_3P1_8B)}
 FULL_LAYERS = SMOLLM2_1P7B["num_hidden_layers"]
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
 
@@ -109,6 +128,8 @@ def decode_bytes(cfg, n_layers, batch, context):
     q = cfg["num_attention_heads"] * cfg["head_dim"]
     kv = cfg["num_key_value_heads"] * cfg["head_dim"]
     per_layer = (q + 2 * kv) * H + H * q + 3 * H * I + 2 * H
+    # a tied head reads the embedding table; a separate one is read instead of it (a
+    # decode step reads only a few rows of the table itself)
     weights = 2 * (n_layers * per_layer + V * H + H)
     cache = batch * context * n_layers * 2 * kv * 2
     return weights + cache, weights, cache
@@ -152,7 +173,11 @@ def run_own(args):
 
     dev = torch.device("cuda:0")
     torch.cuda.set_device(dev)
-    cfg = dict(SMOLLM2_1P7B, num_hidden_layers=args.layers)
+    shape_name, shape = SHAPES[args.shape]
+    full_layers = shape["num_hidden_layers"]
+    if args.layers is None:
+        args.layers = full_layers
+    cfg = dict(shape, num_hidden_layers=args.layers)
     pk = peaks()
     model = lib.Model.random(cfg, seed=0, dtype="bfloat16", device=dev, std=0.02)
     context, vocab = args.context, cfg["vocab_size"]
@@ -244,16 +269,16 @@ def run_own(args):
     total_bytes, w_bytes, kv_bytes = decode_bytes(cfg, args.layers, args.batch, context - (args.steps + 1) // 2)
     achieved = total_bytes / (ms * 1e-3) / 1e9
     line = {
-        "metric": "decode tok/s at batch 8, context 8192 (SmolLM2-1.7B shape)",
+        "metric": f"decode tok/s at batch {args.batch}, context {context} ({shape_name} shape)",
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {
-            "model": "SmolLM2-1.7B shape, random weights", "layers": args.layers,
-            "layers_of_model": FULL_LAYERS, "hidden": cfg["hidden_size"],
+            "model": f"{shape_name} shape, random weights", "layers": args.layers,
+            "layers_of_model": full_layers, "hidden": cfg["hidden_size"],
             "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
             "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"],
-            "vocab": cfg["vocab_size"], "rope_theta": cfg["rope_theta"], "tied_head": True,
+            "vocab": cfg["vocab_size"], "rope_theta": cfg["rope_theta"], "tied_head": bool(cfg["tie_word_embeddings"]),
             "global_batch": args.batch, "seq_len": context, "context": context,
             "prefill_tokens": T, "parallelism": "single GPU", "l2": "inputs larger than L2",
             "peaks": pk["source"], "graph": "decode step replayed as a CUDA graph",
@@ -281,7 +306,9 @@ def main():
     ap.add_argument("--impl", default="own", choices=["own", "reference"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=SMOLLM2_1P7B["max_position_embeddings"])
-    ap.add_argument("--layers", type=int, default=FULL_LAYERS,
+    ap.add_argument("--shape", default="smollm2-1.7b", choices=sorted(SHAPES),
+                    help="the model shape; the default is the one the headline numbers are quoted on")
+    ap.add_argument("--layers", type=int, default=None,
                     help="fewer layers than the model has, where memory or time needs it")
     ap.add_argument("--no-points", dest="points", action="store_false",
                     help="skip the batch-1 and batch-64 decode points")

@@ -267,7 +267,11 @@ __global__ void __launch_bounds__(kWarps * 32, 2)
 gemm_stream_kernel(const bf16* __restrict__ X, int ldx, const __grid_constant__ CUtensorMap map_w,
                    OutT* __restrict__ C, int ldc, int M, int N, int K, int k_slice, int epi) {
     extern __shared__ __align__(1024) unsigned char ring_raw[];
+    constexpr int kSlot = 16 * NT * 8;                          // sums of one row tile
+    constexpr int kSlots = kWarps * 16 * (NT * 8 + 1) / kSlot;  // 9 (NT = 1) or 8 that `red` holds
+    constexpr int kBatchMax = NT == 1 ? 8 : 7;                  // what fits beside the ring with two CTAs per SM
     __shared__ float red[kWarps][16][NT * 8 + 1];               // also receives the cluster's partial sums
+    __shared__ float pending[kBatchMax * kSlot];                // this rank's sums of a batch of row tiles
     __shared__ __align__(8) unsigned long long bar_storage[kRing];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -315,6 +319,8 @@ gemm_stream_kernel(const bf16* __restrict__ X, int ldx, const __grid_constant__ 
     }
 
     cg::cluster_group cluster = cg::this_cluster();
+    // row tiles per exchange: ceil(batch / ranks) * ranks slots must fit into `red`
+    const int batch = min(kBatchMax, (min(kSlots, 8) / n_ranks) * n_ranks);
     bool failed = false;
     float acc[NT][4];
     for (int item = 0; item < n_items; ++item) {
@@ -350,7 +356,7 @@ gemm_stream_kernel(const bf16* __restrict__ X, int ldx, const __grid_constant__ 
         __syncthreads();                                            // the piece has been read: its stage is free,
         if (threadIdx.x == 0 && item + kRing < n_items) issue(item + kRing);   // and so is `red` (read before this barrier)
         if (piece != n_pieces - 1) continue;
-        const int tile = blockIdx.x + (item / n_pieces) * gridDim.x;
+        const int tile_no = item / n_pieces;                        // among this CTA's row tiles
 #pragma unroll
         for (int j = 0; j < NT; ++j) {
             red[warp][g][j * 8 + t * 2] = acc[j][0];
@@ -361,25 +367,40 @@ gemm_stream_kernel(const bf16* __restrict__ X, int ldx, const __grid_constant__ 
         __syncthreads();
         // 16 features x NT*8 tokens: at most one sum per thread (NT <= 2)
         const int idx = threadIdx.x, m = idx >> 4, r = idx & 15;
-        const bool mine_valid = idx < 16 * NT * 8;
+        const bool mine_valid = idx < kSlot;
         float mine = 0.f;
         if (mine_valid) {
 #pragma unroll
             for (int w = 0; w < kWarps; ++w) mine += red[w][r][m];
         }
-        if (n_ranks > 1) {
-            cluster.sync();                                       // every rank is done reading its own `red`
-            float* gather = cluster.map_shared_rank(&red[0][0][0], 0);
-            if (mine_valid) gather[rank * 16 * NT * 8 + idx] = mine;
-            cluster.sync();
-            if (rank == 0 && mine_valid) {
-                const float* sums = &red[0][0][0];
-                mine = 0.f;
-                for (int c = 0; c < n_ranks; ++c) mine += sums[c * 16 * NT * 8 + idx];
+        if (n_ranks == 1) {
+            if (mine_valid)                                       // uniform per warp: whole warps are valid or not
+                store_feature<OutT>(C, ldc, m, (blockIdx.x + tile_no * gridDim.x) * 16, r, M, N, mine, epi);
+            continue;
+        }
+        // The ranks' sums of a row tile meet through shared memory of the cluster, a batch
+        // of row tiles at a time (two cluster barriers per batch, not per tile): tile i of
+        // the batch is summed and written by rank i % ranks, which receives the others'
+        // sums for it in its own `red`, in slot (i / ranks) * ranks + sender.
+        const int in_batch = tile_no % batch;
+        if (mine_valid) pending[in_batch * kSlot + idx] = mine;
+        if (in_batch != batch - 1 && tile_no != my_tiles - 1) continue;
+        const int n_batch = in_batch + 1, first = tile_no - in_batch;
+        cluster.sync();                                           // every rank is done with its own `red`
+        for (int i = 0; i < n_batch; ++i) {
+            float* dst = cluster.map_shared_rank(&red[0][0][0], i % n_ranks);
+            if (mine_valid) dst[((i / n_ranks) * n_ranks + rank) * kSlot + idx] = pending[i * kSlot + idx];
+        }
+        cluster.sync();
+        for (int i = rank; i < n_batch; i += n_ranks) {
+            const float* sums = &red[0][0][0] + (i / n_ranks) * n_ranks * kSlot;
+            float total = 0.f;
+            if (mine_valid) {
+                for (int c = 0; c < n_ranks; ++c) total += sums[c * kSlot + idx];
+                store_feature<OutT>(C, ldc, m, (blockIdx.x + (first + i) * gridDim.x) * 16, r, M, N, total, epi);
             }
         }
-        if (rank == 0 && mine_valid)                              // uniform per warp: whole warps are valid or not
-            store_feature<OutT>(C, ldc, m, tile * 16, r, M, N, mine, epi);
+        // the next tile writes `red` only after the barrier that follows its multiplication
     }
     if (failed && threadIdx.x == 0) atomicExch(&g_status, 1);
 }
@@ -418,10 +439,10 @@ int launch_stream(const bf16* X, int ldx, const bf16* W, int ldw, OutT* C, int l
                   int M, int N, int K, int epi, cudaStream_t stream) {
     if (K % 64) return kErrUnsupported;
     const int row_tiles = (N + 15) / 16;
-    int ranks = 1;
-    while (ranks < kMaxCluster && (K + ranks - 1) / ranks > kPassK) ranks *= 2;
+    int ranks = (K + kPassK - 1) / kPassK;      // whole passes where K allows: no piece is copied half empty
+    if (ranks > kMaxCluster) return kErrUnsupported;
     // few rows: split k further (down to one piece per rank) until every SM has two blocks to run
-    while (ranks < kMaxCluster && row_tiles * ranks < 2 * 148 && (K + 2 * ranks - 1) / (2 * ranks) >= kPieceK) ranks *= 2;
+    while (2 * ranks <= kMaxCluster && row_tiles * ranks < 2 * 148 && (K + 2 * ranks - 1) / (2 * ranks) >= kPieceK) ranks *= 2;
     const int k_slice = (((K + ranks - 1) / ranks) + 63) / 64 * 64;
     if (k_slice > kPassK) return kErrUnsupported;
     CUtensorMap map_w;

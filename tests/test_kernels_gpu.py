@@ -294,10 +294,12 @@ def test_linear_strided_operands():
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 2048, 8192), (8, 2048, 2048), (3, 40, 14336), (16, 100, 20000),
-                                   (2, 16, 32768 + 40)])
+                                   (2, 16, 32768 + 40), (4, 23700, 4096), (12, 9000, 6144), (2, 20000, 14336),
+                                   (9, 4096, 14336), (5, 7000, 10240)])
 def test_linear_skinny_long_rows_split_over_a_cluster(M, N, K):
-    """Inner sizes beyond one pass: 2, 4 or 8 CTAs share a row, and beyond that a
-    CTA makes several passes."""
+    """Inner sizes beyond one pass: 2 to 8 CTAs share a row (their sums meet a batch
+    of row tiles at a time: whole batches, a last short one, fewer tiles than ranks),
+    and beyond that a CTA makes several passes."""
     x, w = rnd(M, K, dtype=torch.bfloat16, seed=1), rnd(N, K, dtype=torch.bfloat16, seed=2)
     out = torch.empty(M, N, dtype=torch.float32, device=DEV)
     ops.linear(x, w, out, kind="skinny")
