@@ -473,16 +473,20 @@ int launch_stream(const bf16* X, int ldx, const bf16* W, int ldw, OutT* C, int l
     cfg.numAttrs = 1;
     // A cluster needs all its CTAs in one GPC, so fewer clusters can be resident than
     // 2 * SMs / ranks says; a grid beyond that runs its last clusters as a second wave.
+    // The count the runtime gives holds for an empty GPU.  These clusters arrive while
+    // the blocks of the product before are still leaving, take the places that happen
+    // to be free, and then pack less well: clusters of three and more get a twelfth
+    // fewer (measured: of 71 clusters of four and of 37 of seven some came late).
     static int resident[kMaxCluster + 1] = {};
     if (ranks > 1 && resident[ranks] == 0) {
         int n = 0;
         resident[ranks] = cudaOccupancyMaxActiveClusters(&n, gemm_stream_kernel<NT, OutT>, &cfg) == cudaSuccess && n > 0
                               ? n : -1;
         cudaGetLastError();
+        if (ranks > 2 && resident[ranks] > 12) resident[ranks] -= (resident[ranks] + 11) / 12;
     }
     if (ranks > 1 && resident[ranks] > 0 && (int)cfg.gridDim.x > resident[ranks]) {
-        // the fewest clusters that still finish in as many rounds of row tiles: what the
-        // count above leaves free absorbs clusters that find no four free places at once
+        // the fewest clusters that still finish in as many rounds of row tiles
         const int rounds = (row_tiles + resident[ranks] - 1) / resident[ranks];
         cfg.gridDim.x = (row_tiles + rounds - 1) / rounds;
     }
