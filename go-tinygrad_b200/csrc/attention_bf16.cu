@@ -219,7 +219,11 @@ attention_prefill_kernel(const bf16* __restrict__ q, int ldq, bf16* __restrict__
 }
 
 // ============================================================== decode
-constexpr int kDecodeStages = 4;
+// Pages in the ring of a decode block.  What the kernel reaches is set by the bytes in
+// flight per SM: four stages of 16 KB pages let three blocks share an SM (heads up to 64
+// channels); pages of 128 channels take 32 KB, and three stages keep two blocks on an SM
+// where four would leave one.
+template <int DP> __host__ __device__ constexpr int decode_stages() { return DP == 128 ? 3 : 4; }
 
 // Partials: for each (sequence, query head, split): DP floats of unnormalised
 // output, then the running max (log2 domain) and the running sum.
@@ -232,6 +236,7 @@ attention_decode_kernel(const bf16* __restrict__ q, int ldq, bf16* __restrict__ 
                         int n_heads, int n_kv, int hd, float scale, int window,
                         int n_splits, float* __restrict__ part_o, float* __restrict__ part_ml) {
     chain_release();
+    constexpr int kDecodeStages = decode_stages<DP>();
     constexpr int CPR = DP / 8;
     constexpr int TILE_BYTES = 64 * DP * 2;
     constexpr int STAGE_BYTES = 2 * TILE_BYTES;
@@ -485,7 +490,7 @@ int launch_decode(const bf16* q, int ldq, bf16* out, int ldo, const bf16* kc, co
                   float scale, int window, int n_splits, float* part_o, float* part_ml,
                   cudaStream_t stream) {
     static bool configured = false;
-    const int ring = kDecodeStages * 2 * 64 * DP * 2;
+    const int ring = decode_stages<DP>() * 2 * 64 * DP * 2;
     const int merge = (4 * 16 * DP + 128) * 4;
     const int smem = 16 * DP * 2 + (ring > merge ? ring : merge);
     if (!configured) {

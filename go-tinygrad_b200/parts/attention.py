@@ -78,7 +78,8 @@ class GQAttention(Mixer):
         and on the longest sequence only, never on the data."""
         base = ctx.n_seqs * self.n_kv * ((self.n_heads // self.n_kv + 15) // 16)
         dp = 16 if self.head_dim <= 16 else 32 if self.head_dim <= 32 else 64 if self.head_dim <= 64 else 128
-        smem = 16 * dp * 2 + 4 * 2 * 64 * dp * 2 + 1024
+        stages = 3 if dp == 128 else 4          # as the kernel has them
+        smem = 16 * dp * 2 + stages * 2 * 64 * dp * 2 + 1024
         slots = _SMS * max(1, min(8, (227 * 1024) // smem))
         pages = max(1, (max(ctx.max_kv_len, 1) + 63) // 64)
         best, best_score = 1, -1.0
