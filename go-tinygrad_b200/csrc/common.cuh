@@ -113,3 +113,25 @@ static inline int launch_chained(void (*kernel)(Params...), dim3 grid, dim3 bloc
     const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<Params>(args)...);
     return e != cudaSuccess ? (int)e : launch_status();
 }
+
+// The same for a grid of thread-block clusters of `cluster_x` blocks along x.
+template <typename... Params, typename... Args>
+static inline int launch_chained_cluster(void (*kernel)(Params...), dim3 grid, dim3 block, int cluster_x,
+                                         size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = cluster_x;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_chained_launch ? 2 : 1;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<Params>(args)...);
+    return e != cudaSuccess ? (int)e : launch_status();
+}

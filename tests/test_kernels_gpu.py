@@ -461,9 +461,9 @@ def test_attention_refuses_head_sizes_it_cannot_serve():
 
 
 # -------------------------------------------------------------------- sampling
-@pytest.mark.parametrize("R,V", [(1, 5), (7, 391), (3, 49152), (2, 128257)])
+@pytest.mark.parametrize("R,V", [(1, 5), (7, 391), (3, 49152), (2, 128257), (4, 128256), (5, 8192), (3, 50001)])
 def test_argmax_first_maximum(R, V):
-    logits = rnd(R, V, seed=4)
+    logits = rnd(R, V + 3, seed=4)[:, :V] if V == 50001 else rnd(R, V, seed=4)   # 50001: rows 50004 apart
     logits[0, V - 1] = 50.0
     if R > 1:
         logits[1, 3] = 60.0
@@ -476,10 +476,14 @@ def test_argmax_first_maximum(R, V):
         assert out[1].item() == 3
 
 
-def test_sample_temperature_matches_inverse_cdf():
+@pytest.mark.parametrize("R,V", [(64, 391), (6, 4096), (9, 49152), (5, 128256), (3, 128257), (4, 131073)])
+def test_sample_temperature_matches_inverse_cdf(R, V):
+    """Small rows take one block, rows up to 131072 entries a cluster of blocks that
+    keep the row in shared memory, longer ones one block again."""
     import plain_llama
-    R, V, T, seed = 64, 391, 0.8, 7
+    T, seed = 0.8, 7
     logits = rnd(R, V, scale=2.0, seed=9)
+    logits[0, V - 7] = 30.0                                  # one row whose mass sits in one late entry
     seq = torch.arange(R, dtype=torch.int32, device=DEV) % 5
     steps = torch.arange(R, dtype=torch.int32, device=DEV) // 5
     out = torch.zeros(R, dtype=torch.int32, device=DEV)
@@ -493,8 +497,10 @@ def test_sample_temperature_matches_inverse_cdf():
         assert below - 1e-5 <= u <= cdf[t] + 1e-5, (r, t, u, below, cdf[t])
     # the same (seed, sequence, step) gives the same token whatever else is in the batch
     out2 = torch.zeros(1, dtype=torch.int32, device=DEV)
-    ops.sample_temperature(logits[17:18], T, seed, seq[17:18].contiguous(), steps[17:18].contiguous(), out2)
-    assert out2.item() == out[17].item()
+    k = R // 2
+    ops.sample_temperature(logits[k:k + 1], T, seed, seq[k:k + 1].contiguous(), steps[k:k + 1].contiguous(), out2)
+    assert out2.item() == out[k].item()
+    assert out[0].item() == V - 7
 
 
 def test_sample_temperature_follows_the_distribution():
