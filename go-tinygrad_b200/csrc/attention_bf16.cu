@@ -225,6 +225,28 @@ attention_prefill_kernel(const bf16* __restrict__ q, int ldq, bf16* __restrict__
 // where four would leave one.
 template <int DP> __host__ __device__ constexpr int decode_stages() { return DP == 128 ? 3 : 4; }
 
+// What a decode step's rotation-and-store kernel would do, done here instead (all
+// null: q arrives rotated and the new keys and values are in the cache already).
+//   cos_sin: (cos, sin) [B][hd/2] of each sequence's new position: the queries are
+//            rotated in shared memory after they arrive, the new key before it is used.
+//   k_new, v_new: the new token's keys and values as the projection wrote them, rows
+//            of `ldq` elements (n_kv heads of hd channels each).  The block that
+//            holds the sequence's newest page puts them (the key rotated) into its
+//            staged copy of that page, and one block per key/value head also into
+//            the cache (kc_w, vc_w), for the steps to come.
+struct DecodeRope {
+    const float2* cos_sin;
+    const bf16* k_new;
+    const bf16* v_new;
+    bf16* kc_w;
+    bf16* vc_w;
+};
+// (a, b) at rotary frequency i -> (a cos - b sin, a sin + b cos), as rope_kv_store computes it
+__device__ __forceinline__ void rotate_pair(float a, float b, float2 cs, bf16& ra, bf16& rb) {
+    ra = __float2bfloat16_rn(a * cs.x - b * cs.y);
+    rb = __float2bfloat16_rn(a * cs.y + b * cs.x);
+}
+
 // Partials: for each (sequence, query head, split): DP floats of unnormalised
 // output, then the running max (log2 domain) and the running sum.
 template <int DP>
@@ -234,7 +256,8 @@ attention_decode_kernel(const bf16* __restrict__ q, int ldq, bf16* __restrict__ 
                         const int* __restrict__ block_table, int table_stride,
                         const int* __restrict__ slots, const int* __restrict__ positions,
                         int n_heads, int n_kv, int hd, float scale, int window,
-                        int n_splits, float* __restrict__ part_o, float* __restrict__ part_ml) {
+                        int n_splits, float* __restrict__ part_o, float* __restrict__ part_ml,
+                        const DecodeRope rope) {
     chain_release();
     constexpr int kDecodeStages = decode_stages<DP>();
     constexpr int CPR = DP / 8;
@@ -277,10 +300,13 @@ attention_decode_kernel(const bf16* __restrict__ q, int ldq, bf16* __restrict__ 
     // Pages before the newest one were completed by earlier steps: their copies may
     // start while the kernels before this one (the projection, the rotation that
     // writes the newest key and value) are still running.  Positions, slots and the
-    // block table were written before the projection began.
+    // block table were written before the projection began.  When this kernel adds
+    // the new token itself, the newest page holds nothing newer than the step before
+    // either (its row for the new token is replaced below) and goes with the others.
+    const bool adds_token = rope.k_new != nullptr;
 #pragma unroll
     for (int s = 0; s < kDecodeStages - 1; ++s)
-        if (p_begin + s < p_end && p_begin + s < p_last) load_page(s, p_begin + s);
+        if (p_begin + s < p_end && (p_begin + s < p_last || adds_token)) load_page(s, p_begin + s);
     chain_wait();
     // ---- queries of the group (rows beyond `rows` are zero)
     for (int id = tid; id < 16 * CPR; id += 128) {
@@ -291,7 +317,7 @@ attention_decode_kernel(const bf16* __restrict__ q, int ldq, bf16* __restrict__ 
     }
 #pragma unroll
     for (int s = 0; s < kDecodeStages - 1; ++s) {
-        if (p_begin + s < p_end && p_begin + s == p_last) load_page(s, p_last);
+        if (p_begin + s < p_end && p_begin + s == p_last && !adds_token) load_page(s, p_last);
         cp_async_commit();
     }
 
@@ -311,13 +337,53 @@ attention_decode_kernel(const bf16* __restrict__ q, int ldq, bf16* __restrict__ 
             if (nxt < p_end) load_page((it + kDecodeStages - 1) % kDecodeStages, nxt);
             cp_async_commit();
         }
+        const int half = hd >> 1;
         if (it == 0) {
+            if (rope.cos_sin != nullptr) {                    // the queries arrived unrotated
+                for (int id = tid; id < rows * half; id += 128) {
+                    const int r = id / half, i = id - r * half;
+                    bf16* pa = reinterpret_cast<bf16*>(smem + swz_offset<DP>(r, i >> 3)) + (i & 7);
+                    bf16* pb = reinterpret_cast<bf16*>(smem + swz_offset<DP>(r, (i + half) >> 3)) + ((i + half) & 7);
+                    rotate_pair(__bfloat162float(*pa), __bfloat162float(*pb), rope.cos_sin[(size_t)b * half + i], *pa, *pb);
+                }
+                __syncthreads();
+            }
 #pragma unroll
             for (int kk = 0; kk < DP / 16; ++kk) {
                 const int r = (lane & 7) + ((lane >> 3) & 1) * 8;
                 const int c = kk * 2 + (lane >> 4);
                 ldmatrix_x4(qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], sQ + swz_offset<DP>(r, c));
             }
+        }
+        if (adds_token && p == p_last) {
+            // the new token's key (rotated) and value: into the staged page, and once per
+            // key/value head into the cache
+            const int rr = pos % kPageTokens;
+            unsigned char* kt = smem + 16 * DP * 2 + (it % kDecodeStages) * STAGE_BYTES;
+            unsigned char* vt = kt + TILE_BYTES;
+            const bool writer = rope.kc_w != nullptr && blockIdx.y % tiles_per_kv == 0;
+            const size_t goff = (size_t)table[p_last] * page_stride + ((size_t)kvh * kPageTokens + rr) * hd;
+            const bf16* ksrc = rope.k_new + (size_t)b * ldq + kvh * hd;
+            const bf16* vsrc = rope.v_new + (size_t)b * ldq + kvh * hd;
+            for (int i = tid; i < half; i += 128) {
+                bf16 ka = ksrc[i], kb = ksrc[i + half];
+                if (rope.cos_sin != nullptr)
+                    rotate_pair(__bfloat162float(ka), __bfloat162float(kb), rope.cos_sin[(size_t)b * half + i], ka, kb);
+                const bf16 va = vsrc[i], vb = vsrc[i + half];
+                const uint32_t oa = swz_offset<DP>(rr, i >> 3) + (i & 7) * 2;
+                const uint32_t ob = swz_offset<DP>(rr, (i + half) >> 3) + ((i + half) & 7) * 2;
+                *reinterpret_cast<bf16*>(kt + oa) = ka;
+                *reinterpret_cast<bf16*>(kt + ob) = kb;
+                *reinterpret_cast<bf16*>(vt + oa) = va;
+                *reinterpret_cast<bf16*>(vt + ob) = vb;
+                if (writer) {
+                    rope.kc_w[goff + i] = ka;
+                    rope.kc_w[goff + i + half] = kb;
+                    rope.vc_w[goff + i] = va;
+                    rope.vc_w[goff + i + half] = vb;
+                }
+            }
+            __syncthreads();
         }
         const uint32_t kbase = sKV + (it % kDecodeStages) * STAGE_BYTES, vbase = kbase + TILE_BYTES;
         // this warp's 16 keys of the page: S[16 heads x 16 keys]
@@ -488,7 +554,7 @@ int launch_decode(const bf16* q, int ldq, bf16* out, int ldo, const bf16* kc, co
                   long long page_stride, const int* block_table, int table_stride,
                   const int* slots, const int* positions, int B, int n_heads, int n_kv, int hd,
                   float scale, int window, int n_splits, float* part_o, float* part_ml,
-                  cudaStream_t stream) {
+                  cudaStream_t stream, const DecodeRope rope = DecodeRope{}) {
     static bool configured = false;
     const int ring = decode_stages<DP>() * 2 * 64 * DP * 2;
     const int merge = (4 * 16 * DP + 128) * 4;
@@ -503,7 +569,7 @@ int launch_decode(const bf16* q, int ldq, bf16* out, int ldo, const bf16* kc, co
     dim3 grid(n_splits, n_kv * ((group + 15) / 16), B);
     int st = launch_chained(attention_decode_kernel<DP>, grid, dim3(128), smem, stream, q, ldq, out, ldo, kc, vc,
                             page_stride, block_table, table_stride, slots, positions, n_heads, n_kv, hd, scale,
-                            window, n_splits, part_o, part_ml);
+                            window, n_splits, part_o, part_ml, rope);
     if (st != 0 || n_splits == 1) return st;
     return launch_chained(attention_combine_kernel<DP>, dim3(B * n_heads), dim3(DP), 0, stream,
                           (const float*)part_o, (const float*)part_ml, out, ldo, n_heads, hd, n_splits);
@@ -536,6 +602,44 @@ GTG_API int gtg_attention_prefill_bf16(const void* q, int ldq, void* out, int ld
         case 32: return launch_prefill<32>(GTG_ARGS);
         case 64: return launch_prefill<64>(GTG_ARGS);
         case 128: return launch_prefill<128>(GTG_ARGS);
+        default: return kErrUnsupported;
+    }
+#undef GTG_ARGS
+}
+
+// Decode attention that also does what rope_kv_store does for a decode step (see
+// DecodeRope): q, k_new and v_new are the unrotated columns of the projection's
+// output (rows of ldq elements); cos_sin float [B][hd/2][2] or null for no rotation;
+// k_new null if this layer adds nothing to the cache (then v_new is ignored);
+// `store` 0 keeps the new token out of the cache (it is still attended to).
+GTG_API int gtg_attention_decode_rope_bf16(const void* q, int ldq, void* out, int ldo,
+                                           void* kc, void* vc, long long page_stride,
+                                           const int* block_table, int table_stride,
+                                           const int* slots, const int* positions,
+                                           int B, int n_heads, int n_kv, int hd, float scale, int window,
+                                           int n_splits, float* scratch, const float* cos_sin,
+                                           const void* k_new, const void* v_new, int store, cudaStream_t stream) {
+    if (B <= 0) return 0;
+    if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv != 0 || ldq % 8 != 0 || n_splits < 1) return kErrBadArgument;
+    if (k_new != nullptr && v_new == nullptr) return kErrBadArgument;
+    const int dp = padded_head_dim(hd);
+    if (dp == 0 || B > 65535 || n_splits > 65535) return kErrUnsupported;
+    if (n_splits > 1 && scratch == nullptr) return kErrBadArgument;
+    float* part_o = scratch;
+    float* part_ml = scratch ? scratch + (size_t)B * n_heads * n_splits * dp : nullptr;
+    DecodeRope rope = {};
+    rope.cos_sin = (const float2*)cos_sin;
+    rope.k_new = (const bf16*)k_new;
+    rope.v_new = (const bf16*)v_new;
+    if (k_new != nullptr && store) { rope.kc_w = (bf16*)kc; rope.vc_w = (bf16*)vc; }
+#define GTG_ARGS (const bf16*)q, ldq, (bf16*)out, ldo, (const bf16*)kc, (const bf16*)vc, page_stride, \
+        block_table, table_stride, slots, positions, B, n_heads, n_kv, hd, scale, window, n_splits, part_o, part_ml, \
+        stream, rope
+    switch (dp) {
+        case 16: return launch_decode<16>(GTG_ARGS);
+        case 32: return launch_decode<32>(GTG_ARGS);
+        case 64: return launch_decode<64>(GTG_ARGS);
+        case 128: return launch_decode<128>(GTG_ARGS);
         default: return kErrUnsupported;
     }
 #undef GTG_ARGS

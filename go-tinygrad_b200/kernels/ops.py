@@ -44,6 +44,8 @@ _SIGNATURES = {
     "gtg_attention_decode_scratch_floats": ("attention_bf16", [_I, _I, _I, _I]),
     "gtg_attention_prefill_bf16": ("attention_bf16", [_P, _I, _P, _I, _P, _P, _L, _P, _I, _P, _P, _P,
                                                       _I, _I, _I, _I, _I, _F, _I, _P]),
+    "gtg_attention_decode_rope_bf16": ("attention_bf16", [_P, _I, _P, _I, _P, _P, _L, _P, _I, _P, _P,
+                                                          _I, _I, _I, _I, _F, _I, _I, _P, _P, _P, _P, _I, _P]),
     "gtg_attention_decode_bf16": ("attention_bf16", [_P, _I, _P, _I, _P, _P, _L, _P, _I, _P, _P,
                                                      _I, _I, _I, _I, _F, _I, _I, _P, _P]),
     "gtg_attention_tcgen05_supports": ("attention_tcgen05", [_I]),
@@ -431,7 +433,14 @@ def attention_decode_scratch_floats(n_seqs: int, n_heads: int, head_dim: int, n_
 
 
 def attention_decode_bf16(q, out, kv, slots, positions, n_heads: int, scale: float, window: int,
-                          n_splits: int, scratch: Optional[torch.Tensor]) -> None:
+                          n_splits: int, scratch: Optional[torch.Tensor], unrotated=None) -> None:
+    """Attention of one new token per sequence over the cache (keys split over
+    `n_splits` thread blocks per head group).  Normally q is rotated and the new
+    keys and values are in the cache (`rope_kv_store`).  With
+    unrotated=(cos_sin, k_new, v_new, store) the kernel does that work itself: q
+    and k_new come as the projection wrote them, cos_sin float32 [B, hd/2, 2] or
+    None rotates them, and the new key and value are attended to and, if `store`,
+    written to the cache; k_new None for a layer that reads another's cache."""
     _rows2d(q, "attention: q"); _rows2d(out, "attention: out")
     B = q.shape[0]
     _need(q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and kv.k.dtype == torch.bfloat16,
@@ -442,6 +451,24 @@ def attention_decode_bf16(q, out, kv, slots, positions, n_heads: int, scale: flo
         need = attention_decode_scratch_floats(B, n_heads, kv.head_dim, n_splits)
         _need(scratch is not None and scratch.dtype == torch.float32 and scratch.is_contiguous()
               and scratch.numel() >= need, f"attention_decode_bf16: scratch needs {need} floats")
+    if unrotated is not None:
+        cos_sin, k_new, v_new, store = unrotated
+        hd = kv.head_dim
+        if cos_sin is not None:
+            _need(cos_sin.dtype == torch.float32 and cos_sin.is_contiguous() and tuple(cos_sin.shape) == (B, hd // 2, 2),
+                  "attention_decode_bf16: cos_sin must be float32 [B, hd/2, 2]")
+        if k_new is not None:
+            for name, t in (("k_new", k_new), ("v_new", v_new)):
+                _need(t is not None and t.dtype == torch.bfloat16 and t.dim() == 2 and t.stride(1) == 1
+                      and t.stride(0) == q.stride(0) and tuple(t.shape) == (B, kv.n_kv_heads * hd),
+                      f"attention_decode_bf16: {name} must be bfloat16 [B, n_kv * hd] with q's row stride")
+        _check(_fn("gtg_attention_decode_rope_bf16")(
+            _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(kv.k), _ptr(kv.v), kv.page_stride,
+            _ptr(kv.block_table), kv.table_stride, _ptr(slots), _ptr(positions), B, n_heads, kv.n_kv_heads,
+            kv.head_dim, float(scale), int(window), int(n_splits), _ptr(scratch), _ptr(cos_sin),
+            _ptr(k_new), _ptr(v_new) if k_new is not None else None, 1 if store else 0, _stream()),
+            "attention_decode_bf16")
+        return
     _check(_fn("gtg_attention_decode_bf16")(_ptr(q), q.stride(0), _ptr(out), out.stride(0),
                                             _ptr(kv.k), _ptr(kv.v), kv.page_stride, _ptr(kv.block_table),
                                             kv.table_stride, _ptr(slots), _ptr(positions), B, n_heads,

@@ -103,27 +103,35 @@ class GQAttention(Mixer):
         qkv = rt.empty(n, self.w_qkv.shape[0])
         rotation = self.position.rotation(ctx)
         store = self.n_kv if (cache.writes and self.own_kv) else 0
+        # a decode step in bfloat16: the attention kernel rotates the queries and adds the new
+        # token's key and value itself, and no kernel stands between it and the projection
+        in_attention = (ctx.is_decode and rt.dtype == torch.bfloat16 and ops.attention_bf16_supports(self.head_dim))
         if store and ops.qkv_rope_fused_supports(x, self.w_qkv, qkv, rotation, self.n_heads, self.n_kv,
                                                  self.head_dim, kv):
             # a prompt: rotation and cache store happen in the projection's epilogue
             ops.linear_qkv_rope(x, self.w_qkv, qkv, rotation, self.n_heads, self.n_kv, kv,
                                 ctx.token_seq, ctx.slots, ctx.positions)
+            in_attention = False
         else:
             ops.linear(x, self.w_qkv, qkv)
-            ops.rope_kv_store(qkv, rotation, self.n_heads, store, self.head_dim,
-                              kv, ctx.token_seq, ctx.slots, ctx.positions)
+            if not in_attention:
+                ops.rope_kv_store(qkv, rotation, self.n_heads, store, self.head_dim,
+                                  kv, ctx.token_seq, ctx.slots, ctx.positions)
         q = qkv[:, : self.q_dim]
         mixed = rt.empty(n, self.q_dim)
         window = self.window or 0
         if rt.dtype == torch.bfloat16 and ops.attention_bf16_supports(self.head_dim):
             if ctx.is_decode:
+                new_k = qkv[:, self.q_dim: self.q_dim + self.kv_dim] if store else None
+                new_v = qkv[:, self.q_dim + self.kv_dim:] if store else None
                 splits = self._decode_splits(ctx)
                 scratch = None
                 if splits > 1:
                     scratch = rt.empty(ops.attention_decode_scratch_floats(
                         n, self.n_heads, self.head_dim, splits), dtype=torch.float32)
                 ops.attention_decode_bf16(q, mixed, kv, ctx.slots, ctx.positions, self.n_heads,
-                                          self.scale, window, splits, scratch)
+                                          self.scale, window, splits, scratch,
+                                          unrotated=(rotation, new_k, new_v, True) if in_attention else None)
             elif ops.attention_tcgen05_supports(kv) and qkv.stride(0) % 8 == 0:
                 ops.attention_prefill_tcgen05(q, mixed, kv, ctx.cu_seqlens, ctx.slots, ctx.start_pos,
                                               ctx.n_seqs, ctx.max_q_len, self.n_heads, self.scale, window)

@@ -454,6 +454,55 @@ def test_attention_decode_bf16(n_heads, n_kv, hd, window, splits):
     torch.testing.assert_close(out.float(), want, rtol=2e-2, atol=2e-2)
 
 
+@pytest.mark.parametrize("n_heads,n_kv,hd", ATT_SHAPES + [(40, 2, 64)])
+@pytest.mark.parametrize("window", [0, 37])
+@pytest.mark.parametrize("splits", [1, 3, 16])
+@pytest.mark.parametrize("rotate", [True, False])
+def test_attention_decode_that_rotates_and_stores_the_new_token_itself(n_heads, n_kv, hd, window, splits, rotate):
+    """Unrotated queries, keys and values of the new tokens as a projection leaves
+    them: the kernel gives what rope_kv_store followed by the plain decode kernel
+    gives, and leaves the same keys and values in the cache (new tokens at a page's
+    first row, its last row, and in between)."""
+    lens_before = [0, 63, 64, 700, 129]
+    B = len(lens_before)
+    q_dim, kv_dim = n_heads * hd, n_kv * hd
+    caches, outs = [], []
+    for fused in (False, True):
+        cache = make_cache(n_kv, hd, torch.bfloat16, n_pages=64)
+        slots = [cache.open_sequence() for _ in range(B)][::-1]
+        for b, t0 in enumerate(lens_before):
+            if t0:
+                fill_sequence(cache, 0, slots[b], rnd(t0, n_kv, hd, dtype=torch.bfloat16, seed=10 * b + 1),
+                              rnd(t0, n_kv, hd, dtype=torch.bfloat16, seed=10 * b + 2))
+            cache.reserve(slots[b], t0 + 1)
+        cache.flush_tables()
+        kv = cache.handles[0].kv
+        qkv = rnd(B, q_dim + 2 * kv_dim, dtype=torch.bfloat16, seed=77)
+        slot_t = torch.tensor(slots, dtype=torch.int32, device=DEV)
+        positions = torch.tensor(lens_before, dtype=torch.int32, device=DEV)
+        token_seq = torch.arange(B, dtype=torch.int32, device=DEV)
+        cos_sin = None
+        if rotate:
+            ang = rnd(B, hd // 2, seed=5, scale=3.0)
+            cos_sin = torch.stack([torch.cos(ang), torch.sin(ang)], dim=-1).contiguous()
+        out = torch.full((B, q_dim), float("nan"), dtype=torch.bfloat16, device=DEV)
+        n = ops.attention_decode_scratch_floats(B, n_heads, hd, splits)
+        scratch = torch.full((max(n, 1),), float("nan"), dtype=torch.float32, device=DEV)
+        if fused:
+            ops.attention_decode_bf16(qkv[:, :q_dim], out, kv, slot_t, positions, n_heads, 0.2, window, splits, scratch,
+                                      unrotated=(cos_sin, qkv[:, q_dim:q_dim + kv_dim], qkv[:, q_dim + kv_dim:], True))
+        else:
+            ops.rope_kv_store(qkv, cos_sin, n_heads, n_kv, hd, kv, token_seq, slot_t, positions)
+            ops.attention_decode_bf16(qkv[:, :q_dim], out, kv, slot_t, positions, n_heads, 0.2, window, splits, scratch)
+        outs.append(out.float())
+        caches.append([read_sequence(cache, 0, slots[b], t0 + 1) for b, t0 in enumerate(lens_before)])
+    assert torch.isfinite(outs[1]).all()
+    torch.testing.assert_close(outs[1], outs[0], rtol=2e-2, atol=2e-2)
+    for (k0, v0), (k1, v1) in zip(*caches):
+        torch.testing.assert_close(k1.float(), k0.float(), rtol=1e-2, atol=1e-2)    # one rounding of the rotation
+        assert torch.equal(v1, v0)
+
+
 def test_attention_refuses_head_sizes_it_cannot_serve():
     assert not ops.attention_bf16_supports(40)
     assert not ops.attention_bf16_supports(144)
