@@ -116,14 +116,33 @@ class DecodeBatch:
         elif self._runs == 0:
             self._forward()
         else:
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                self._forward()
-            self.graph = graph
-            graph.replay()
+            self.graph = self._record()
+            self.graph.replay()
         self._runs += 1
         for s in self.slots:
             self.cache.advance(s, 1)
+
+    def _record(self) -> "torch.cuda.CUDAGraph":
+        """Capture one step on a side stream.  Done by hand rather than with
+        `torch.cuda.graph`, which first collects garbage and hands every cached block
+        back to the driver: a generation loop records a step whenever its batch
+        shrinks, and would pay for both each time (and allocate its cache anew)."""
+        graph = torch.cuda.CUDAGraph()
+        main = torch.cuda.current_stream()
+        if DecodeBatch._side is None:
+            DecodeBatch._side = torch.cuda.Stream()
+        side = DecodeBatch._side
+        side.wait_stream(main)
+        with torch.cuda.stream(side):
+            graph.capture_begin()
+            try:
+                self._forward()
+            finally:
+                graph.capture_end()
+        main.wait_stream(side)
+        return graph
+
+    _side: Optional["torch.cuda.Stream"] = None
 
     # ------------------------------------------------------------------ driving
     def step_host(self, tokens: Sequence[int], steps: Sequence[int]) -> List[int]:
