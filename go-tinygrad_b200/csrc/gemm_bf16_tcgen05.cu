@@ -324,6 +324,39 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         for (int piece = 0; piece < 8; ++piece) dst[piece] = pieces[piece];
                     }
                 }
+            } else if (epi == 3) {
+                // C is a float residual stream and map_c describes it in boxes of 32 columns x 32
+                // rows: every chunk of the accumulator, rounded to bfloat16 as a stored update
+                // would be, is staged as 32 rows of 128 bytes and ADDED to the residual by the
+                // copy engine (one tensor reduction per box; each element is added once).
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN / 32; ++c0, ++groups) {
+                    if (n0 + c0 * 32 >= N) break;
+                    unsigned char* buf = stage_base + (groups & 1u) * kStoreBytes;
+                    if (groups >= 2) {                     // the box sent from this buffer two rounds ago has been read
+                        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;\n" ::: "memory");
+                        __syncwarp();
+                    }
+                    uint32_t v[32];
+                    tmem_ld32(tmem_row + (uint32_t)(c0 * 32), v);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+                    for (int piece = 0; piece < 8; ++piece) {
+                        float f[4];
+#pragma unroll
+                        for (int q = 0; q < 4; ++q)
+                            f[q] = __bfloat162float(__float2bfloat16_rn(__uint_as_float(v[4 * piece + q])));
+                        *reinterpret_cast<float4*>(buf + lane * 128 + ((piece ^ (lane & 7)) << 4)) =
+                            make_float4(f[0], f[1], f[2], f[3]);
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // generic writes -> TMA reads
+                    __syncwarp();
+                    if (lane == 0) {
+                        asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];\n"
+                                     ::"l"(&map_c), "r"(smem_addr(buf)), "r"(n0 + c0 * 32), "r"(m0 + warp * 32) : "memory");
+                        asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
+                    }
+                }
             } else if (staged) {
                 const int per_box = epi ? 4 : 2;           // accumulator chunks of 32 columns per 64 output columns
 #pragma unroll 1
@@ -410,7 +443,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             __syncwarp();
             if (lane == 0) mbar_arrive(acc_empty_bar(acc));
         }
-        if (staged && lane == 0) asm volatile("cp.async.bulk.wait_group 0;\n" ::: "memory");   // stores have landed
+        if ((staged || epi == 3) && lane == 0) asm volatile("cp.async.bulk.wait_group 0;\n" ::: "memory");   // stores have landed
     }
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::);
     __syncthreads();
@@ -464,8 +497,9 @@ namespace {
 int run(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int out_f32, int M, int N, int K,
         int epilogue, const RopeKV& rope, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
-    if (epilogue < 0 || epilogue > 2) return kErrBadArgument;
+    if (epilogue < 0 || epilogue > 3) return kErrBadArgument;
     if (epilogue == 1 && N % 16 != 0) return kErrUnsupported;
+    if (epilogue == 3 && (!out_f32 || ldc % 4 || ((uintptr_t)C % 16))) return kErrUnsupported;
     if (K <= 0 || lda < K || ldw < K || ldc < (epilogue == 1 ? N / 2 : N)) return kErrBadArgument;
     if (K % 8 || lda % 8 || ldw % 8 || ((uintptr_t)A % 16) || ((uintptr_t)W % 16)) return kErrUnsupported;
     const long long tiles = (long long)((N + BN - 1) / BN) * ((M + BM - 1) / BM);
@@ -483,6 +517,18 @@ int run(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int ou
         if (make_map(&map_c, C, M, n_out, ldc, 32) == 0) use_store_map = 1;
     }
     if (epilogue == 2 && !use_store_map) return kErrUnsupported;
+    if (epilogue == 3) {
+        // the residual stream as [M, N] float in boxes of 32 x 32 for the tensor reduction
+        EncodeTiled enc = encode_fn();
+        if (!enc) return kErrUnsupported;
+        const cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)M};
+        const cuuint64_t strides[1] = {(cuuint64_t)ldc * 4};
+        const cuuint32_t box[2] = {32u, 32u};
+        const cuuint32_t elem[2] = {1, 1};
+        if (enc(&map_c, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, C, dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return kErrUnsupported;
+    }
     static bool configured = false;
     static int sms = 148;
     if (!configured) {
@@ -511,6 +557,16 @@ GTG_API int gtg_gemm_bf16_tcgen05(const void* A, int lda, const void* W, int ldw
                                   int out_f32, int M, int N, int K, int epilogue, cudaStream_t stream) {
     if (epilogue != 0 && epilogue != 1) return kErrBadArgument;
     return run(A, lda, W, ldw, C, ldc, out_f32, M, N, K, epilogue, RopeKV{}, stream);
+}
+
+// residual[M,N] (float, row pitch ldr) += bfloat16(A W^T): the update, rounded as a
+// stored one would be, is added to the residual stream by tensor reductions in the
+// epilogue.  Each element is added exactly once, so the result does not depend on
+// timing.
+GTG_API int gtg_gemm_bf16_tcgen05_add(const void* A, int lda, const void* W, int ldw, float* residual, int ldr,
+                                      int M, int N, int K, cudaStream_t stream) {
+    if (residual == nullptr) return kErrBadArgument;
+    return run(A, lda, W, ldw, residual, ldr, 1, M, N, K, 3, RopeKV{}, stream);
 }
 
 // The query/key/value projection of heads of 64 channels with what follows it

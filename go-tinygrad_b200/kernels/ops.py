@@ -32,6 +32,7 @@ _SIGNATURES = {
     "gtg_gemm_bf16_skinny": ("gemm_bf16_skinny", [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _P]),
     "gtg_gemm_bf16_skinny_status": ("gemm_bf16_skinny", []),
     "gtg_gemm_bf16_tcgen05": ("gemm_bf16_tcgen05", [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _P]),
+    "gtg_gemm_bf16_tcgen05_add": ("gemm_bf16_tcgen05", [_P, _I, _P, _I, _P, _I, _I, _I, _I, _P]),
     "gtg_gemm_bf16_tcgen05_status": ("gemm_bf16_tcgen05", []),
     "gtg_gemm_bf16_tcgen05_qkv_rope": ("gemm_bf16_tcgen05", [_P, _I, _P, _I, _P, _I, _I, _I, _P, _P, _P, _P, _P, _I,
                                                              _P, _P, _L, _I, _I, _P]),
@@ -320,6 +321,32 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, kind: str = "aut
         code = _fn(symbol)(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0),
                            out_f32, M, N, K, 1 if epilogue == "swiglu" else 0, _stream())
     _check(code, "linear(bfloat16)")
+
+
+def linear_add_residual(x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor) -> bool:
+    """residual[M,N] += bfloat16(x[M,K] . w[N,K]^T): the product of a prompt step
+    adds its result to a float32 residual stream in its epilogue (tensor reductions,
+    each element once), rounded as it would be if it were stored first -- what
+    `linear` into a bfloat16 update followed by the norm kernel's addition gives,
+    without the update's trip through memory.  False, with nothing done, for
+    operands the tensor-memory kernel does not take this way (few rows, float32
+    operands, rows the tensor copies cannot address); the caller then uses `linear`."""
+    if not (x.dim() == 2 and w.dim() == 2 and residual.dim() == 2):
+        return False
+    M, K = x.shape
+    N = w.shape[0]
+    if not (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and residual.dtype == torch.float32
+            and M > SKINNY_MAX_ROWS and w.shape[1] == K and tuple(residual.shape) == (M, N)
+            and x.stride(1) == 1 and w.stride(1) == 1 and residual.stride(1) == 1
+            and K % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and residual.stride(0) % 4 == 0
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and residual.data_ptr() % 16 == 0):
+        return False
+    code = _fn("gtg_gemm_bf16_tcgen05_add")(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(residual),
+                                            residual.stride(0), M, N, K, _stream())
+    if code == -2:
+        return False
+    _check(code, "linear_add_residual")
+    return True
 
 
 def qkv_rope_fused_supports(x: torch.Tensor, w: torch.Tensor, qkv: torch.Tensor, cos_sin, n_heads: int,

@@ -23,7 +23,7 @@ import torch
 from ..cache import CacheHandle, KVRequest, Request
 from ..kernels import ops
 from ..weights.binder import WeightSpec
-from .base import Mixer, Runtime, StepContext, build_part, register_part
+from .base import Mixer, Runtime, StepContext, build_part, emit_update, register_part
 
 _SMS = 148                  # streaming multiprocessors of a B200
 
@@ -141,6 +141,4 @@ class GQAttention(Mixer):
         else:
             ops.attention_simple(q, mixed, kv, ctx.token_seq, ctx.slots, ctx.positions,
                                  self.n_heads, self.scale, window)
-        out = rt.empty(n, self.hidden)
-        ops.linear(mixed, self.w_o, out)
-        return out
+        return emit_update(mixed, self.w_o, ctx)

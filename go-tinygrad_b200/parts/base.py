@@ -16,6 +16,7 @@ from typing import Any, Callable, Dict, List, Mapping, Optional, Tuple, Type
 import torch
 
 from ..cache import CacheHandle, Request
+from ..kernels import ops
 from ..weights.binder import WeightSpec
 from .plan import PartSpec
 
@@ -100,6 +101,7 @@ class StepContext:
     max_kv_len: int             # longest sequence after this step
     is_decode: bool             # every sequence brings exactly one token
     shared: Dict[Any, Any] = field(default_factory=dict)   # per-step values parts share (rotary tables)
+    update_into: Optional["ResidualStream"] = None   # set by a block around a part's forward: see emit_update
 
 
 class Part:
@@ -132,6 +134,21 @@ class ResidualStream:
     def __init__(self, residual: torch.Tensor, pending: Optional[torch.Tensor] = None):
         self.residual = residual
         self.pending = pending
+
+
+def emit_update(x: torch.Tensor, w: torch.Tensor, ctx: "StepContext") -> Optional[torch.Tensor]:
+    """The last product of a mixer or feed-forward: its update x . w^T, [n_tokens, H].
+    When the block has offered its residual stream (`ctx.update_into`) and the
+    product can add to it in its epilogue (a prompt step in bfloat16), the update
+    is added there and None is returned in its place: it never goes through
+    memory, and the norm that follows has nothing left to add."""
+    stream = ctx.update_into
+    if (stream is not None and stream.pending is None and ctx.rt.dtype == torch.bfloat16
+            and ops.linear_add_residual(x, w, stream.residual)):
+        return None
+    out = ctx.rt.empty(x.shape[0], w.shape[0])
+    ops.linear(x, w, out)
+    return out
 
 
 # ---- category interfaces --------------------------------------------------------

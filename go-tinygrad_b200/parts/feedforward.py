@@ -16,7 +16,7 @@ import torch
 
 from ..kernels import ops
 from ..weights.binder import WeightSpec
-from .base import FeedForward, Runtime, StepContext, register_part
+from .base import FeedForward, Runtime, StepContext, emit_update, register_part
 
 
 @register_part("feed_forward", "swiglu")
@@ -56,6 +56,4 @@ class SwiGLU(FeedForward):
             gate_up = rt.empty(n, 2 * self.inter)
             ops.linear(x, self.w_gate_up, gate_up)
             ops.swiglu(gate_up, act)
-        out = rt.empty(n, self.hidden)
-        ops.linear(act, self.w_down, out)
-        return out
+        return emit_update(act, self.w_down, ctx)

@@ -331,6 +331,39 @@ def test_linear_with_fused_swiglu(kind, M, I, K):
     assert ops.bounded_wait_failures() == 0
 
 
+@pytest.mark.parametrize("M,N,K", [(65, 64, 64), (2048, 2048, 2048), (300, 144, 96), (130, 1000, 2056), (257, 2048, 8192),
+                                   (128, 48, 64), (1000, 391, 264)])
+def test_linear_adds_to_a_residual_stream(M, N, K):
+    """residual += bfloat16(x . w^T) by tensor reductions in the product's epilogue:
+    bit for bit what the product into a bfloat16 update, then the addition, give;
+    row and column counts that are no multiples of the boxes; twice in a row."""
+    x, w = rnd(M, K, dtype=torch.bfloat16, seed=1), rnd(N, K, dtype=torch.bfloat16, seed=2, scale=0.5)
+    wide = rnd(M, N + 8, seed=3, scale=2.0)
+    residual = wide[:, 4:N + 4] if N % 4 == 0 else rnd(M, N, seed=3, scale=2.0)   # a column slice where alignment allows
+    before = residual.clone()
+    plain = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    ops.linear(x, w, plain, kind="tcgen05")
+    if not ops.linear_add_residual(x, w, residual):
+        assert N % 4 != 0                                      # rows the tensor copies cannot address
+        return
+    assert torch.equal(residual, before + plain.float())
+    assert ops.linear_add_residual(x, w, residual)
+    assert torch.equal(residual, (before + plain.float()) + plain.float())
+    if N % 4 == 0:
+        assert torch.equal(wide[:, :4], rnd(M, N + 8, seed=3, scale=2.0)[:, :4])      # nothing beside the slice is touched
+        assert torch.equal(wide[:, N + 4:], rnd(M, N + 8, seed=3, scale=2.0)[:, N + 4:])
+    assert ops.bounded_wait_failures() == 0
+
+
+def test_linear_does_not_add_to_a_residual_stream_what_it_cannot_serve():
+    for M, N, K, dt in ((64, 64, 64, torch.bfloat16), (200, 64, 64, torch.float32), (200, 64, 12, torch.bfloat16)):
+        x, w = rnd(M, K, dtype=dt, seed=1), rnd(N, K, dtype=dt, seed=2)
+        residual = rnd(M, N, seed=3)
+        before = residual.clone()
+        assert not ops.linear_add_residual(x, w, residual)
+        assert torch.equal(residual, before)
+
+
 def test_linear_refuses_unaligned_inner_size():
     x, w = rnd(4, 12, dtype=torch.bfloat16), rnd(5, 12, dtype=torch.bfloat16)
     with pytest.raises(ops.KernelError, match="multiples of 8"):
