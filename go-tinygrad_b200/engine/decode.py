@@ -57,6 +57,7 @@ class DecodeBatch:
         pin = dev.type == "cuda"
         self.h_in = torch.zeros(3 * B, dtype=torch.int32, pin_memory=pin)
         self.h_out = torch.zeros(B, dtype=torch.int32, pin_memory=pin)
+        self._h_in, self._h_out = self.h_in.numpy(), self.h_out.numpy()   # the same memory, cheap to fill and read
         self.logits: Optional[torch.Tensor] = None
         self.use_graph = use_graph and dev.type == "cuda"
         self.chained = chained and dev.type == "cuda"     # kernels of the step overlap their launch gaps
@@ -80,10 +81,10 @@ class DecodeBatch:
     def set_state(self, tokens: Sequence[int], steps: Sequence[int]) -> None:
         """Tokens to feed next and how many tokens each sequence has generated;
         positions are the sequences' lengths in the cache."""
-        B = self.B
-        self.h_in[:B] = torch.tensor(list(tokens), dtype=torch.int32)
-        self.h_in[B:2 * B] = torch.tensor([self.cache.length(s) for s in self.slots], dtype=torch.int32)
-        self.h_in[2 * B:] = torch.tensor(list(steps), dtype=torch.int32)
+        B, h, length = self.B, self._h_in, self.cache.length
+        h[:B] = tokens
+        h[B:2 * B] = [length(s) for s in self.slots]
+        h[2 * B:] = steps
         self.meta[:3 * B].copy_(self.h_in, non_blocking=True)
 
     def _context(self) -> StepContext:
@@ -149,8 +150,9 @@ class DecodeBatch:
         self.set_state(tokens, steps)
         self._launch()
         self.h_out.copy_(self.sampled, non_blocking=True)
-        torch.cuda.current_stream().synchronize() if self.model.rt.device.type == "cuda" else None
-        return self.h_out.tolist()
+        if self.model.rt.device.type == "cuda":
+            torch.cuda.current_stream().synchronize()
+        return self._h_out.tolist()
 
     def step_device(self) -> None:
         """Feed back the tokens just sampled; no host synchronisation."""
