@@ -77,3 +77,27 @@ def test_real_layer_shapes(shaped, dtype):
             check(got[i], w[h + t], dtype, widest, f"{name} {dtype} decoded token {t} of prompt {i}")
     from go_tinygrad_b200.kernels import ops
     assert ops.bounded_wait_failures() == 0
+
+
+def test_decode_steps_of_more_sequences_than_the_streaming_products_take(shaped):
+    """70 sequences: their decode steps have more rows than the weight-streaming
+    products take, so the prompt-sized products (and, at 64 channels, the projection
+    that rotates and stores in its epilogue) run in a decode step."""
+    name, folder, _, _ = shaped
+    cfg, w = plain_llama.read_model(folder)
+    rng = np.random.default_rng(5)
+    n_seqs, decoded = 70, 2
+    lengths = rng.integers(3, 9, n_seqs).tolist()
+    requests = [rng.integers(0, cfg["vocab_size"], n + decoded).tolist() for n in lengths]
+    model = lib.Model.load(folder, dtype="bfloat16", device="cuda")
+    cache = model.new_cache(max_tokens=64 * n_seqs, max_slots=n_seqs)
+    slots = [cache.open_sequence() for _ in requests]
+    step(model, cache, [StepEntry(s, r[:n], []) for s, r, n in zip(slots, requests, lengths)])
+    got = []
+    for t in range(decoded):
+        logits = step(model, cache, [StepEntry(s, [r[n + t]], [0]) for s, r, n in zip(slots, requests, lengths)])
+        got.append(logits.float().cpu().numpy())
+    for i in (0, 1, 33, 68, 69):
+        want = plain_llama.forward(cfg, w, requests[i])
+        have = np.stack([got[t][i] for t in range(decoded)])
+        check(have, want[lengths[i]:lengths[i] + decoded], "bfloat16", cfg["intermediate_size"], f"{name} sequence {i} of {n_seqs}")
