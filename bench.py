@@ -144,6 +144,48 @@ def prefill_flops(cfg, n_layers, T):
     return n_layers * (gemm + attn) + 2 * V * H
 
 
+def kernel_breakdown(run, repeats, what, n_layers):
+    """Where a step's time goes: for every kernel the time it ADDS to the step (its end
+    minus the end of the kernel before it; kernels of a step overlap their starts under
+    programmatic dependent launch, so durations would count some time twice), summed per
+    kernel name; a kernel launched several times per layer (the products) is split by
+    its position among those launches (#0, #1, ... in launch order)."""
+    import collections
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(repeats):
+            run()
+        torch.cuda.synchronize()
+    events = sorted((e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA),
+                    key=lambda e: e.time_range.start)
+    def short(name):
+        name = name.replace("(anonymous namespace)::", "").replace("void ", "")
+        return name.split("(")[0][:60]
+    per_step = collections.Counter(short(e.name) for e in events)
+    per_layer = {k: (v // repeats) // n_layers if (v // repeats) % n_layers == 0 else 1 for k, v in per_step.items()}
+    seen = collections.Counter()
+    added = collections.defaultdict(lambda: [0, 0.0])
+    last_end = None
+    for e in events:
+        begin, end = e.time_range.start, e.time_range.end
+        name = short(e.name)
+        if per_layer[name] > 1:
+            k = seen[name]
+            seen[name] = k + 1
+            name = f"{name} #{k % per_layer[name]}"
+        if last_end is not None:
+            gain = max(0.0, end - last_end) if begin - last_end < 50 else end - begin   # a gap: another step begins
+            row = added[name]
+            row[0] += 1
+            row[1] += gain
+        last_end = end if last_end is None else max(last_end, end)
+    total = sum(t for _, t in added.values())
+    print(f"# {what}: time added per kernel, microseconds per step (sum {total / repeats:.1f})")
+    for name, (count, t) in sorted(added.items(), key=lambda kv: -kv[1][1]):
+        print(f"# {t / repeats:9.1f} us  {100 * t / total:5.1f} %  {count / repeats:6.1f} launches  {name}")
+
+
 def prefill_only(args, model, cache, vocab, gen):
     """For profilers: `warmup` + `steps` prefills of one 2,048-token prompt."""
     import torch
@@ -160,6 +202,12 @@ def prefill_only(args, model, cache, vocab, gen):
         if i >= args.warmup:
             times.append(a.elapsed_time(b))
         cache.close_sequence(slot)
+    if args.breakdown:
+        def once():
+            slot = cache.open_sequence()
+            step(model, cache, [StepEntry(slot, prompt, [2047])])
+            cache.close_sequence(slot)
+        kernel_breakdown(once, 3, "prefill of 2,048 tokens", args.layers)
     print(json.dumps({"only": "prefill", "ms": round(statistics.median(times), 3)}))
     return 0
 
@@ -192,7 +240,7 @@ def run_own(args):
     def decode_run(batch, steps, warmup, host):
         """Tokens a second of `steps` decode steps that end at `context` tokens."""
         slots = [cache.open_sequence() for _ in range(batch)]
-        total = warmup + steps
+        total = warmup + steps + (6 if args.breakdown else 0)
         for s in slots:
             cache.reserve(s, context)
             cache.advance(s, context - total)
@@ -229,6 +277,8 @@ def run_own(args):
         torch.cuda.synchronize()
         clocks = sampler.stop()
         ms = start.elapsed_time(stop) / steps
+        if args.breakdown and not host:
+            kernel_breakdown(db.step_device, 6, f"decode step, batch {batch}, context {context}", args.layers)
         for s in slots:
             cache.close_sequence(s)
         return batch / (ms * 1e-3), ms, clocks, per_step + 1      # +1: the kernel that feeds tokens back
@@ -314,6 +364,8 @@ def main():
                     help="skip the batch-1 and batch-64 decode points")
     ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
                     help="run one part only and print a short line (for profilers)")
+    ap.add_argument("--breakdown", action="store_true",
+                    help="with --only: also print, as comment lines, the time each kernel adds to a step")
     ap.add_argument("--eager", action="store_true",
                     help="launch the decode step kernel by kernel instead of replaying a graph")
     ap.add_argument("--no-chain", action="store_true",
