@@ -2,30 +2,28 @@
 // with few rows M (one token per live sequence, M <= 64).  The work is reading W
 // once from HBM; everything is shaped around that.
 //
-//   * One CTA owns 16 output features (rows of W): they are the M dimension of
+//   * A tile of 16 output features (rows of W) is the M dimension of
 //     mma.sync.m16n8k16, the tokens are its N dimension (8 per tile).
-//   * The CTA's 8 warps split K: warp w takes the 32-wide k blocks w, w+8, ...,
-//     so at any moment the CTA reads one contiguous 512-byte stretch of each
-//     row.  Each thread loads 16 bytes (8 consecutive k) of rows g and g+8; the
-//     MMA's k slots are assigned to those 8 values in the order they lie in
-//     memory (a dot product does not care about the order of k as long as both
-//     operands agree), so no shuffle or shared-memory staging is needed.
-//   * A CTA reads at most 2048 values of k per row and pass.  Its 16 x 4 KB of W
-//     arrive by sixteen bulk asynchronous copies (cp.async.bulk, the TMA engine)
-//     that one thread issues up front and that complete on one mbarrier: 64 KB
-//     in flight per CTA whatever the compiler does with registers, and one
-//     exposure to memory latency.  Rows are padded by 64 bytes in shared memory
-//     so that the 16-byte fragment reads of a quarter-warp fall in distinct
-//     banks.  Longer rows are split over a thread-block cluster (2, 4 or 8 CTAs
-//     along k) whose partial sums meet in the first CTA's shared memory, so that
-//     a product with few output features and a long inner size still fills the
-//     GPU.
-//   * The wait on the mbarrier is bounded: if the copies never land, the kernel
+//   * A CTA's 8 warps split K: warp w takes the 32-wide k blocks w, w+8, ...  Each
+//     thread loads 16 bytes (8 consecutive k) of rows g and g+8; the MMA's k slots are
+//     assigned to those 8 values in the order they lie in memory (a dot product does
+//     not care about the order of k as long as both operands agree), so no shuffle or
+//     shared-memory transposition is needed.
+//   * Two forms.  The persistent one (gemm_stream_kernel, up to 16 tokens, K a
+//     multiple of 64; described above its code) keeps two CTAs on every SM, each with
+//     a ring of three 32 KB pieces of W that arrive by one tensor copy (TMA) each.
+//     The other (gemm_skinny_kernel: any K that is a multiple of 8, up to 64 tokens)
+//     gives every 16-row tile a CTA of its own, whose 16 rows of up to 2048 values
+//     arrive by sixteen bulk copies on one mbarrier.
+//   * Rows longer than 2048 values are split over a thread-block cluster (2 to 8 CTAs
+//     along k) whose partial sums meet through the cluster's shared memory, so that a
+//     product with few output features and a long inner size still fills the GPU.
+//   * Every wait on an mbarrier is bounded: if the copies never land, the kernel
 //     records it in a status word (gtg_gemm_bf16_skinny_status) and returns.
 //   * X stays in L1/L2 (read by every CTA) and is loaded with plain loads.
 //   * Partial sums are added in a fixed order (warps, then cluster ranks): the
 //     result does not depend on timing.
-// Any N; K a multiple of 8; output bfloat16 or float.
+// Any N; output bfloat16 or float.
 #include "mma_helpers.cuh"
 #include <cooperative_groups.h>
 #include <cuda.h>
@@ -246,12 +244,14 @@ int launch_typed(const bf16* X, int ldx, const bf16* W, int ldw, OutT* C, int ld
 // the copy engine as [k/64][row][64 values] (the middle stride is the row pitch),
 // so a piece lands as sixteen blocks of 16 rows x 128 bytes with the 128-byte
 // swizzle, and the 16-byte fragment reads of rows g and g+1 fall in different
-// banks without padding.  The ring and the sums take less than half of an SM's
-// shared memory on purpose: under programmatic dependent launch the CTAs of the
-// next product of the step become resident beside these and fill their own ring
-// while this product drains, so the memory system stays busy across the boundary
-// between kernels.  The activations of the slice are the same for every row
-// tile, so each thread loads its fragments of X once, into registers.
+// banks without padding.  The ring and the sums take half of an SM's shared
+// memory, so two CTAs share an SM (six pieces, 192 KB, in flight per SM: what the
+// kernel reaches is set by that figure over the latency of a copy), and under
+// programmatic dependent launch a CTA of the next product of the step moves in as
+// soon as one of these leaves and fills its own ring while this product drains,
+// so the memory system stays busy across the boundary between kernels.  The
+// activations of the slice are the same for every row tile, so each thread loads
+// its fragments of X once, into registers.
 constexpr int kPieceK = 1024;                            // values of k per staged piece
 constexpr int kPieceBlocks = kPieceK / (kWarps * 32);    // k blocks of 32 per warp and piece
 constexpr int kPieceBytes = 16 * kPieceK * 2;
