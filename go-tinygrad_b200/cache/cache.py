@@ -113,6 +113,11 @@ class Cache:
         if max_position is not None:
             per_seq = min(per_seq, (max_position + PAGE_TOKENS - 1) // PAGE_TOKENS)
         self.pages_per_seq = max(1, per_seq)
+        # the longest sequence, in tokens: what the pages of one sequence hold, and no
+        # more than the model's own longest position where one is given
+        self.max_sequence = self.pages_per_seq * PAGE_TOKENS
+        if max_position is not None:
+            self.max_sequence = min(self.max_sequence, int(max_position))
         self.slots = SlotTable(self.n_slots)
         self._length = [0] * self.n_slots
 
@@ -187,9 +192,9 @@ class Cache:
         if not self.slots.is_held(slot):
             raise CacheMisuse(f"slot {slot} is not open")
         need = (new_length + PAGE_TOKENS - 1) // PAGE_TOKENS
-        if need > self.pages_per_seq:
+        if new_length > self.max_sequence:
             raise CacheFull(f"a sequence of {new_length} tokens exceeds the longest the cache "
-                            f"holds ({self.pages_per_seq * PAGE_TOKENS})")
+                            f"holds ({self.max_sequence})")
         for grp in self.groups:
             have = grp.pages_of[slot]
             if need > len(have):
@@ -213,9 +218,9 @@ class Cache:
                 if not self.slots.is_held(slot):
                     raise CacheMisuse(f"slot {slot} is not open")
                 pages = (new_length + PAGE_TOKENS - 1) // PAGE_TOKENS
-                if pages > self.pages_per_seq:
+                if new_length > self.max_sequence:
                     raise CacheFull(f"a sequence of {new_length} tokens exceeds the longest the "
-                                    f"cache holds ({self.pages_per_seq * PAGE_TOKENS})")
+                                    f"cache holds ({self.max_sequence})")
                 need += max(0, pages - len(grp.pages_of[slot]))
             if need > grp.pool.n_free:
                 raise CacheFull(f"the cache is full: this step needs {need} more pages of 64 tokens, "
@@ -232,7 +237,15 @@ class Cache:
         self._length[slot] = new_length
 
     def truncate(self, slot: int, new_length: int) -> None:
-        """Forget the tokens after `new_length` (their pages stay with the sequence)."""
+        """Forget the tokens after `new_length` (their pages stay with the sequence).
+        Keys and values are addressed by position, so a shorter length is all it
+        takes (the reference's rollback does the same: runtime/kv/staging.go:35-68).
+        A record of fixed size has already absorbed the tokens to be forgotten and
+        cannot give them back: a cache that holds such state refuses, since a shorter
+        length beside an unchanged record would be silently wrong."""
+        if self._state_tensors and new_length != self._length[slot]:
+            raise CacheMisuse("this cache holds per-sequence state of fixed size, which cannot be "
+                              "rolled back by shortening a length; close the sequence and run it again")
         if not 0 <= new_length <= self._length[slot]:
             raise CacheMisuse(f"cannot truncate slot {slot} from {self._length[slot]} to {new_length}")
         self._length[slot] = new_length

@@ -20,10 +20,14 @@ from .llama import ConfigError
 @dataclass(frozen=True)
 class Architecture:
     """`names` are matched against config.json's ``architectures`` entries and
-    ``model_type``.  `read_config(raw_json) -> config`; `plan(config) -> ModelPlan`."""
+    ``model_type``.  `read_config(raw_json) -> config`; `plan(config) -> ModelPlan`.
+    `ignore`: shell-style patterns of tensor names a checkpoint of this
+    architecture may carry that no part reads (stored buffers and the like); a
+    tensor that neither a part declares nor a pattern matches is still an error."""
     names: Tuple[str, ...]
     read_config: Callable[[Mapping[str, Any]], Any]
     plan: Callable[[Any], Any]
+    ignore: Tuple[str, ...] = ()
 
 
 _ARCHITECTURES: Dict[str, Architecture] = {}

@@ -224,6 +224,13 @@ attention_prefill_kernel(const bf16* __restrict__ q, int ldq, bf16* __restrict__
 // channels); pages of 128 channels take 32 KB, and three stages keep two blocks on an SM
 // where four would leave one.
 template <int DP> __host__ __device__ constexpr int decode_stages() { return DP == 128 ? 3 : 4; }
+// Shared memory of a decode block: the queries, then the page ring (reused for the merge).
+template <int DP>
+constexpr int decode_smem_bytes() {
+    constexpr int ring = decode_stages<DP>() * 2 * 64 * DP * 2;
+    constexpr int merge = (4 * 16 * DP + 128) * 4;
+    return 16 * DP * 2 + (ring > merge ? ring : merge);
+}
 
 // What a decode step's rotation-and-store kernel would do, done here instead (all
 // null: q arrives rotated and the new keys and values are in the cache already).
@@ -556,9 +563,7 @@ int launch_decode(const bf16* q, int ldq, bf16* out, int ldo, const bf16* kc, co
                   float scale, int window, int n_splits, float* part_o, float* part_ml,
                   cudaStream_t stream, const DecodeRope rope = DecodeRope{}) {
     static bool configured = false;
-    const int ring = decode_stages<DP>() * 2 * 64 * DP * 2;
-    const int merge = (4 * 16 * DP + 128) * 4;
-    const int smem = 16 * DP * 2 + (ring > merge ? ring : merge);
+    const int smem = decode_smem_bytes<DP>();
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<DP>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -578,6 +583,69 @@ int launch_decode(const bf16* q, int ldq, bf16* out, int ldo, const bf16* kc, co
 
 // Head sizes the tiled bfloat16 kernels serve (others go to the one-warp-per-row kernel).
 GTG_API int gtg_attention_bf16_supports(int hd) { return padded_head_dim(hd) != 0; }
+
+// ---- into how many blocks to split the keys of one (sequence, key/value head)
+// How many decode blocks the current device holds at once: what the occupancy
+// calculator says for this kernel's registers and shared memory, times the
+// device's multiprocessors.  Asked once per (device, head size).
+template <int DP>
+static int decode_block_slots() {
+    static int cached[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+    if (cached[dev] == 0) {
+        constexpr int smem = decode_smem_bytes<DP>();
+        int per_sm = 0, sms = 0;
+        if (cudaFuncSetAttribute(attention_decode_kernel<DP>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess ||
+            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attention_decode_kernel<DP>, 128, smem) != cudaSuccess ||
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return 0;
+        }
+        cached[dev] = sms * (per_sm > 0 ? per_sm : 1);
+    }
+    return cached[dev];
+}
+
+// Blocks run in waves of what the device holds at once: a count just above a
+// whole number of waves leaves the last wave nearly empty, and a split of very
+// few pages pays its fixed cost (query load, merge, partial write) for little
+// work.  The choice depends on the batch, on the longest sequence and on the
+// window only, never on the data.  A layer with a window reads the pages its
+// window spans, however long the sequence is.  Returns the split count (>= 1),
+// or a negative error code.
+GTG_API int gtg_attention_decode_plan(int B, int n_heads, int n_kv, int hd, int max_kv_len, int window) {
+    if (B <= 0 || n_heads <= 0 || n_kv <= 0 || n_heads % n_kv != 0) return kErrBadArgument;
+    int slots = 0;
+    switch (padded_head_dim(hd)) {
+        case 16: slots = decode_block_slots<16>(); break;
+        case 32: slots = decode_block_slots<32>(); break;
+        case 64: slots = decode_block_slots<64>(); break;
+        case 128: slots = decode_block_slots<128>(); break;
+        default: return kErrUnsupported;
+    }
+    if (slots <= 0) return 1;
+    const long long base = (long long)B * n_kv * ((n_heads / n_kv + 15) / 16);
+    int keys = max_kv_len > 1 ? max_kv_len : 1;
+    int pages = (keys + kPageTokens - 1) / kPageTokens;
+    if (window > 0 && window < keys) {
+        // `window` consecutive keys touch at most this many pages
+        const int span = (window + kPageTokens - 2) / kPageTokens + 1;
+        if (span < pages) pages = span;
+    }
+    int best = 1;
+    double best_score = -1.0;
+    const int most = pages < 64 ? pages : 64;
+    for (int s = 1; s <= most; ++s) {
+        const long long blocks = base * s;
+        const long long waves = (blocks + slots - 1) / slots;
+        const int per_split = (pages + s - 1) / s;
+        double score = (double)blocks / (double)(waves * slots) * per_split / (per_split + 1.0);
+        if (s > 1) score *= 0.93;             // the partial results and the kernel that merges them
+        if (score > best_score + 1e-9) { best = s; best_score = score; }
+    }
+    return best;
+}
 
 // Floats of scratch a decode call needs: (part_o, part_ml) for `n_splits` > 1.
 GTG_API long long gtg_attention_decode_scratch_floats(int B, int n_heads, int hd, int n_splits) {

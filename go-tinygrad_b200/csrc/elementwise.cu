@@ -213,14 +213,17 @@ GTG_API int gtg_rope_table(const int* positions, const double* inv_freq, float* 
 
 // ------------------------------------------- rotation + write into the cache
 // For token n with fused projections qkv[n] = [q heads | k heads | v heads]:
-// rotate q in place and k on its way into the cache, half-split pairs
-// (i, i+hd/2): a' = a*c - b*s, b' = a*s + b*c (model/llama.go:1556-1589); copy v
-// into the cache.  Keys are stored after rotation (model/llama.go:1253-1254).
-// With n_kv_store == 0 only the queries are rotated (a layer that reads another
-// layer's cache).  cos_sin == nullptr means no rotation.
+// rotate q in place and k on its way into the cache, a' = a*c - b*s,
+// b' = a*s + b*c; copy v into the cache.  Keys are stored after rotation
+// (model/llama.go:1253-1254).  Which channels (a, b) form pair i is the
+// encoding's layout: half-split, (i, i + rot/2) (model/llama.go:1556-1589), or
+// interleaved, (2i, 2i+1); `rot` <= hd channels of a head rotate, the rest pass
+// unchanged.  cos_sin holds rot/2 (cos, sin) per token.  With n_kv_store == 0
+// only the queries are rotated (a layer that reads another layer's cache).
+// cos_sin == nullptr means no rotation.
 template <typename T>
 __global__ void rope_kv_store_kernel(T* __restrict__ qkv, int ld, const float2* __restrict__ cos_sin,
-                                     int n_heads, int n_kv_store, int hd,
+                                     int n_heads, int n_kv_store, int hd, int rot, int interleaved,
                                      T* __restrict__ kc, T* __restrict__ vc, long long page_stride,
                                      const int* __restrict__ block_table, int table_stride,
                                      const int* __restrict__ token_seq, const int* __restrict__ slots,
@@ -228,7 +231,7 @@ __global__ void rope_kv_store_kernel(T* __restrict__ qkv, int ld, const float2* 
     chain_release();
     chain_wait();
     const int n = blockIdx.x;
-    const int half = hd >> 1;
+    const int half = hd >> 1, rhalf = rot >> 1;
     const int pos = positions[n];
     T* row = qkv + (size_t)n * ld;
     size_t cache_off = 0;
@@ -237,27 +240,31 @@ __global__ void rope_kv_store_kernel(T* __restrict__ qkv, int ld, const float2* 
         const int page = block_table[(size_t)slot * table_stride + pos / kPageTokens];
         cache_off = (size_t)page * page_stride + (size_t)(pos % kPageTokens) * hd;
     }
+    // one item = two channels of one head: pair i of the rotated part, or two
+    // consecutive channels of what passes unchanged
     const int items = (n_heads + 2 * n_kv_store) * half;
     for (int it = threadIdx.x; it < items; it += blockDim.x) {
         const int head = it / half, i = it - head * half;
         T* src = row + head * hd;
-        const float a = to_f32<T>(src[i]), b = to_f32<T>(src[i + half]);
+        int ia, ib;
+        if (i < rhalf) { ia = interleaved ? 2 * i : i; ib = interleaved ? 2 * i + 1 : i + rhalf; }
+        else { ia = rot + 2 * (i - rhalf); ib = ia + 1; }
+        const float a = to_f32<T>(src[ia]), b = to_f32<T>(src[ib]);
         if (head < n_heads + n_kv_store) {
             float c = 1.f, s = 0.f;
-            if (cos_sin) { const float2 cs = cos_sin[(size_t)n * half + i]; c = cs.x; s = cs.y; }
+            if (cos_sin && i < rhalf) { const float2 cs = cos_sin[(size_t)n * rhalf + i]; c = cs.x; s = cs.y; }
             const float ra = a * c - b * s, rb = a * s + b * c;
             if (head < n_heads) {
-                src[i] = from_f32<T>(ra);
-                src[i + half] = from_f32<T>(rb);
+                if (i < rhalf) { src[ia] = from_f32<T>(ra); src[ib] = from_f32<T>(rb); }
             } else {
                 T* dst = kc + cache_off + (size_t)(head - n_heads) * kPageTokens * hd;
-                dst[i] = from_f32<T>(ra);
-                dst[i + half] = from_f32<T>(rb);
+                dst[ia] = i < rhalf ? from_f32<T>(ra) : src[ia];
+                dst[ib] = i < rhalf ? from_f32<T>(rb) : src[ib];
             }
         } else {
             T* dst = vc + cache_off + (size_t)(head - n_heads - n_kv_store) * kPageTokens * hd;
-            dst[i] = src[i];
-            dst[i + half] = src[i + half];
+            dst[ia] = src[ia];
+            dst[ib] = src[ib];
         }
     }
 }
@@ -316,15 +323,15 @@ __global__ void rope_kv_store_bf16_vec_kernel(bf16* __restrict__ qkv, int ld, co
 }
 
 GTG_API int gtg_rope_kv_store(int dtype, void* qkv, int ld, const float* cos_sin,
-                              int n_heads, int n_kv_store, int hd,
+                              int n_heads, int n_kv_store, int hd, int rot, int interleaved,
                               void* kc, void* vc, long long page_stride,
                               const int* block_table, int table_stride,
                               const int* token_seq, const int* slots, const int* positions,
                               int N, cudaStream_t stream) {
     int st = 0;
     if (N <= 0) return 0;
-    if (hd <= 0 || (hd & 1)) return kErrBadArgument;
-    if (dtype == 1 && hd % 16 == 0 && ld % 8 == 0 && page_stride % 8 == 0 && ((uintptr_t)qkv % 16) == 0 &&
+    if (hd <= 0 || (hd & 1) || rot <= 0 || (rot & 1) || rot > hd) return kErrBadArgument;
+    if (dtype == 1 && rot == hd && !interleaved && hd % 16 == 0 && ld % 8 == 0 && page_stride % 8 == 0 && ((uintptr_t)qkv % 16) == 0 &&
         ((uintptr_t)kc % 16) == 0 && ((uintptr_t)vc % 16) == 0 && ((uintptr_t)cos_sin % 16) == 0) {
         const int vec_items = (n_heads + 2 * n_kv_store) * (hd / 16);
         int t = 32;
@@ -337,10 +344,10 @@ GTG_API int gtg_rope_kv_store(int dtype, void* qkv, int ld, const float* cos_sin
     int threads = 64;
     while (threads < 512 && threads < items) threads *= 2;
     if (dtype == 0)
-        st = launch_chained(rope_kv_store_kernel<float>, dim3(N), dim3(threads), 0, stream, (float*)qkv, ld, (const float2*)cos_sin, n_heads, n_kv_store, hd,
+        st = launch_chained(rope_kv_store_kernel<float>, dim3(N), dim3(threads), 0, stream, (float*)qkv, ld, (const float2*)cos_sin, n_heads, n_kv_store, hd, rot, interleaved,
             (float*)kc, (float*)vc, page_stride, block_table, table_stride, token_seq, slots, positions);
     else if (dtype == 1)
-        st = launch_chained(rope_kv_store_kernel<bf16>, dim3(N), dim3(threads), 0, stream, (bf16*)qkv, ld, (const float2*)cos_sin, n_heads, n_kv_store, hd,
+        st = launch_chained(rope_kv_store_kernel<bf16>, dim3(N), dim3(threads), 0, stream, (bf16*)qkv, ld, (const float2*)cos_sin, n_heads, n_kv_store, hd, rot, interleaved,
             (bf16*)kc, (bf16*)vc, page_stride, block_table, table_stride, token_seq, slots, positions);
     else return kErrBadArgument;
     return st;

@@ -59,7 +59,9 @@ class DecodeBatch:
         self.h_out = torch.zeros(B, dtype=torch.int32, pin_memory=pin)
         self._h_in, self._h_out = self.h_in.numpy(), self.h_out.numpy()   # the same memory, cheap to fill and read
         self.logits: Optional[torch.Tensor] = None
-        self.use_graph = use_graph and dev.type == "cuda"
+        # a part that talks to the host in its forward, or a listening diagnostic hook,
+        # cannot be recorded: such a model's steps are launched kernel by kernel
+        self.use_graph = use_graph and dev.type == "cuda" and model.capturable
         self.chained = chained and dev.type == "cuda"     # kernels of the step overlap their launch gaps
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self._runs = 0
@@ -91,7 +93,8 @@ class DecodeBatch:
         return StepContext(rt=self.model.rt, n_tokens=self.B, n_seqs=self.B, tokens=self.tokens,
                            positions=self.positions, token_seq=self.token_seq, cu_seqlens=self.cu,
                            slots=self.slot_ids, start_pos=self.positions, max_q_len=1,
-                           max_kv_len=self._planned_len, is_decode=True)
+                           max_kv_len=self._planned_len, is_decode=True,
+                           step=self.model.steps_run, op_hook=self.model.op_hook)
 
     def _forward(self) -> None:
         ctx = self._context()
@@ -105,6 +108,12 @@ class DecodeBatch:
         self.cache.reserve_many([(s, self.cache.length(s) + 1) for s in self.slots])
         self.cache.flush_tables()
         longest = max(self.cache.length(s) for s in self.slots) + 1
+        if self.model.op_hook is not None:                # a hook listens now: this step runs in the open
+            self.graph = None
+            self._planned_len = max(longest, int(longest * self.AHEAD))
+            self._forward()
+            self._finish_step()
+            return
         if self.graph is None or not self.use_graph:
             self._planned_len = max(longest, int(longest * self.AHEAD))
         elif longest > self._planned_len * 1.17 or longest * 2 < self._planned_len:
@@ -119,7 +128,11 @@ class DecodeBatch:
         else:
             self.graph = self._record()
             self.graph.replay()
+        self._finish_step()
+
+    def _finish_step(self) -> None:
         self._runs += 1
+        self.model.steps_run += 1
         for s in self.slots:
             self.cache.advance(s, 1)
 

@@ -49,7 +49,8 @@ def generate(model: Model, prompts: Sequence[Sequence[int]],
     is made that holds `max_tokens` tokens (default: what the largest batch
     needs, up to `max_batch` requests at a time, default 64).  Decode steps of a
     batch whose membership does not change are replayed as a CUDA graph unless
-    `use_graph` is False."""
+    `use_graph` is False or the model cannot be captured (a part of it talks to
+    the host in its forward, or a diagnostic hook is set: `Model.capturable`)."""
     n = len(prompts)
     limits = [int(max_new_tokens)] * n if isinstance(max_new_tokens, int) else [int(m) for m in max_new_tokens]
     if len(limits) != n:

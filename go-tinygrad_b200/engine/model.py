@@ -15,7 +15,7 @@ import torch
 
 from ..cache import Cache
 from ..config.registry import Architecture, find_architecture, read_config_json
-from ..parts.base import Block, Runtime, build_part
+from ..parts.base import Block, Runtime, build_part, walk
 from ..parts.plan import ModelPlan, plan_weight_specs
 from ..weights.binder import WeightSpec, bind, check_specs
 from ..weights.random_init import random_tensors
@@ -41,24 +41,29 @@ class Model:
         self.rt = rt
         self.config = config
         self.embedding = build_part("embedding", plan.embedding)
-        self.blocks: List[Block] = []
-        for layer in plan.layers:
-            block = build_part("block", layer.block)
-            block.assemble(build_part("norm", layer.mixer_norm), build_part("mixer", layer.mixer),
-                           build_part("norm", layer.feed_forward_norm),
-                           build_part("feed_forward", layer.feed_forward))
-            self.blocks.append(block)
+        # a block builds and owns what its layer is made of (norms, mixer, feed-forward, ...)
+        self.blocks: List[Block] = [build_part("block", layer.block) for layer in plan.layers]
         self.final_norm = build_part("norm", plan.final_norm)
         self.head = build_part("head", plan.head)
         self.loaded = False
+        self.steps_run = 0
+        # Optional diagnostic: op_hook(step, layer, op, tensor) receives named
+        # intermediate values of every layer (see StepContext.trace), as the reference's
+        # debugOpHook does (model/debug_hooks.go:5-7).  None in normal execution; while
+        # it is set, decode steps are not recorded as CUDA graphs.
+        self.op_hook = None
 
     # ------------------------------------------------------------------ parts
     def parts(self):
-        yield self.embedding
-        for b in self.blocks:
-            yield from (b.mixer_norm, b.mixer, b.ff_norm, b.ff)
-        yield self.final_norm
-        yield self.head
+        """Every part of the model: each root, then what it owns."""
+        for root in (self.embedding, *self.blocks, self.final_norm, self.head):
+            yield from walk(root)
+
+    @property
+    def capturable(self) -> bool:
+        """Whether a step of this model can be recorded as a CUDA graph: every part
+        says so and no diagnostic hook listens."""
+        return self.op_hook is None and all(part.capturable for part in self.parts())
 
     def weight_specs(self) -> List[WeightSpec]:
         specs: List[WeightSpec] = []
@@ -83,8 +88,12 @@ class Model:
         config = arch.read_config(raw)
         model = cls(arch.plan(config), Runtime(torch.device(device), compute_dtype(dtype)), config)
         with TensorSource(folder) as source:
-            tensors = bind(source, model.weight_specs(), where=folder)
-        return model.load_tensors(tensors)
+            # views of the mapped files: every tensor goes from the file's pages to the
+            # device in one copy (parts that fuse or convert make their own host copy)
+            tensors = bind(source, model.weight_specs(), where=folder, ignore=arch.ignore, copy=False)
+            model.load_tensors(tensors)
+            del tensors
+        return model
 
     @classmethod
     def random(cls, config_json: Any, seed: int = 0, dtype: Union[str, torch.dtype] = "bfloat16",
@@ -107,9 +116,8 @@ class Model:
         sequence's count rounded up to a multiple of 64."""
         requests, shared = [], []
         for i, entry in enumerate(self.plan.schedule):
-            mixer = self.blocks[entry.layer].mixer
             if entry.cache is None:
-                requests.append(list(mixer.cache_requests()))
+                requests.append(list(self.blocks[entry.layer].cache_requests()))
                 shared.append(None)
             else:
                 requests.append([])
@@ -130,10 +138,4 @@ class Model:
                 if isinstance(v, torch.Tensor) and v.data_ptr() not in seen:
                     seen.add(v.data_ptr())
                     total += v.numel() * v.element_size()
-            pos = getattr(part, "position", None)
-            if pos is not None:
-                for v in vars(pos).values():
-                    if isinstance(v, torch.Tensor) and v.data_ptr() not in seen:
-                        seen.add(v.data_ptr())
-                        total += v.numel() * v.element_size()
         return total

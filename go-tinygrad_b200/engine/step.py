@@ -135,6 +135,7 @@ def build_context(model: Model, cache: Cache, entries: Sequence[StepEntry]):
         max_q_len=max(len(e.tokens) for e in entries),
         max_kv_len=max(s + len(e.tokens) for s, e in zip(start, entries)),
         is_decode=all(len(e.tokens) == 1 for e in entries),
+        step=model.steps_run, op_hook=model.op_hook,
     )
     rows = take(n_want) if n_want else None
     return ctx, rows
@@ -144,7 +145,9 @@ def run_layers(model: Model, cache: Cache, ctx: StepContext) -> ResidualStream:
     """Embedding, then every schedule entry in order."""
     stream = model.embedding.forward(ctx)
     for i, entry in enumerate(model.plan.schedule):
+        ctx.layer = entry.layer
         model.blocks[entry.layer].forward(stream, ctx, cache.handles[i])
+    ctx.layer = -1
     return stream
 
 
@@ -170,4 +173,5 @@ def step(model: Model, cache: Cache, entries: Sequence[StepEntry]) -> torch.Tens
         logits = logits_at(model, stream, ctx, rows)
     for e in entries:
         cache.advance(e.slot, len(e.tokens))
+    model.steps_run += 1
     return logits

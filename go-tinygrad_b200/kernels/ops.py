@@ -25,7 +25,7 @@ _SIGNATURES = {
     "gtg_add_rmsnorm": ("elementwise", [_I, _P, _P, _P, _F, _P, _P, _I, _I, _P]),
     "gtg_swiglu": ("elementwise", [_I, _P, _P, _I, _I, _P]),
     "gtg_rope_table": ("elementwise", [_P, _P, _P, _I, _I, _P]),
-    "gtg_rope_kv_store": ("elementwise", [_I, _P, _I, _P, _I, _I, _I, _P, _P, _L, _P, _I, _P, _P, _P, _I, _P]),
+    "gtg_rope_kv_store": ("elementwise", [_I, _P, _I, _P, _I, _I, _I, _I, _I, _P, _P, _L, _P, _I, _P, _P, _P, _I, _P]),
     "gtg_advance": ("elementwise", [_P, _P, _P, _P, _I, _P]),
     "gtg_gemm_f32": ("gemm_f32", [_P, _I, _P, _I, _P, _I, _I, _I, _I, _P]),
     "gtg_gemm_bf16_mma": ("gemm_bf16_mma", [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _P]),
@@ -43,6 +43,7 @@ _SIGNATURES = {
                                                   _I, _I, _I, _I, _F, _I, _P]),
     "gtg_attention_bf16_supports": ("attention_bf16", [_I]),
     "gtg_attention_decode_scratch_floats": ("attention_bf16", [_I, _I, _I, _I]),
+    "gtg_attention_decode_plan": ("attention_bf16", [_I, _I, _I, _I, _I, _I]),
     "gtg_attention_prefill_bf16": ("attention_bf16", [_P, _I, _P, _I, _P, _P, _L, _P, _I, _P, _P, _P,
                                                       _I, _I, _I, _I, _I, _F, _I, _P]),
     "gtg_attention_decode_rope_bf16": ("attention_bf16", [_P, _I, _P, _I, _P, _P, _L, _P, _I, _P, _P,
@@ -219,19 +220,30 @@ def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, out: torch.Tenso
     _check(_fn("gtg_rope_table")(_ptr(positions), _ptr(inv_freq), _ptr(out), N, half, _stream()), "rope_table")
 
 
+ROTARY_PAIRINGS = {"half": 0, "interleaved": 1}
+
+
 def rope_kv_store(qkv: torch.Tensor, cos_sin: Optional[torch.Tensor], n_heads: int, n_kv_store: int,
                   head_dim: int, kv, token_seq: torch.Tensor, slots: torch.Tensor,
-                  positions: torch.Tensor) -> None:
+                  positions: torch.Tensor, pairing: str = "half", rotary_dim: Optional[int] = None) -> None:
     """Rotate the query heads of qkv in place; rotate the key heads and copy the
     value heads into the cache `kv` at each token's (slot, position).  With
-    n_kv_store == 0 only queries are rotated and `kv` may be None."""
+    n_kv_store == 0 only queries are rotated and `kv` may be None.  `pairing`:
+    "half" rotates channel i with i + rotary_dim/2, "interleaved" 2i with 2i+1;
+    the first `rotary_dim` channels of a head rotate (default: all), the rest
+    pass unchanged.  Any other layout is refused."""
     _rows2d(qkv, "rope_kv_store: qkv")
     N = qkv.shape[0]
     _need(head_dim % 2 == 0, "rope_kv_store: head_dim must be even")
+    _need(pairing in ROTARY_PAIRINGS, f"rope_kv_store: pairing {pairing!r} is not supported; "
+                                      f"supported: {sorted(ROTARY_PAIRINGS)}")
+    rot = head_dim if rotary_dim is None else int(rotary_dim)
+    _need(rot % 2 == 0 and 0 < rot <= head_dim,
+          f"rope_kv_store: rotary_dim {rot} must be even and between 2 and head_dim {head_dim}")
     _need(qkv.shape[1] >= (n_heads + 2 * n_kv_store) * head_dim, "rope_kv_store: qkv is too narrow")
     if cos_sin is not None:
         _need(cos_sin.dtype == torch.float32 and cos_sin.is_contiguous()
-              and tuple(cos_sin.shape) == (N, head_dim // 2, 2), "rope_kv_store: cos_sin must be float32 [N, hd/2, 2]")
+              and tuple(cos_sin.shape) == (N, rot // 2, 2), "rope_kv_store: cos_sin must be float32 [N, rotary_dim/2, 2]")
     for name, t in (("token_seq", token_seq), ("slots", slots), ("positions", positions)):
         _need(t.dtype == torch.int32 and t.is_contiguous(), f"rope_kv_store: {name} must be contiguous int32")
     if n_kv_store > 0:
@@ -241,7 +253,7 @@ def rope_kv_store(qkv: torch.Tensor, cos_sin: Optional[torch.Tensor], n_heads: i
     else:
         args = (None, None, 0, None, 0)
     _check(_fn("gtg_rope_kv_store")(_dt(qkv), _ptr(qkv), qkv.stride(0), _ptr(cos_sin), n_heads, n_kv_store,
-                                    head_dim, *args, _ptr(token_seq), _ptr(slots), _ptr(positions),
+                                    head_dim, rot, ROTARY_PAIRINGS[pairing], *args, _ptr(token_seq), _ptr(slots), _ptr(positions),
                                     N, _stream()), "rope_kv_store")
 
 
@@ -453,6 +465,19 @@ def attention_prefill_tcgen05(q, out, kv, cu_seqlens, slots, start_pos, n_seqs: 
                                                 _ptr(slots), _ptr(start_pos), n_seqs, max_q_len, n_heads,
                                                 kv.n_kv_heads, kv.head_dim, float(scale), int(window), _stream()),
            "attention_prefill_tcgen05")
+
+
+def attention_decode_plan(n_seqs: int, n_heads: int, n_kv_heads: int, head_dim: int, max_kv_len: int,
+                          window: int = 0) -> int:
+    """Into how many thread blocks `attention_decode_bf16` should split the keys of
+    one (sequence, key/value head): the library weighs whole waves of blocks on
+    this device (its multiprocessor count and the kernel's own occupancy) against
+    the fixed cost of a split.  It depends on the batch, the longest sequence and
+    the window, never on the data."""
+    n = int(_fn("gtg_attention_decode_plan")(n_seqs, n_heads, n_kv_heads, head_dim, int(max_kv_len), int(window)))
+    if n < 1:
+        raise KernelError(f"attention_decode_plan: {_CODES.get(n, n)}")
+    return n
 
 
 def attention_decode_scratch_floats(n_seqs: int, n_heads: int, head_dim: int, n_splits: int) -> int:

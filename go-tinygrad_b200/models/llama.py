@@ -11,7 +11,7 @@ from __future__ import annotations
 
 from ..config.llama import LlamaConfig
 from ..config.registry import Architecture, register_architecture
-from ..parts.plan import LayerSpec, ModelPlan, PartSpec, default_schedule
+from ..parts.plan import ModelPlan, PartSpec, default_schedule, pre_norm_layer
 
 
 def llama_plan(cfg: LlamaConfig) -> ModelPlan:
@@ -23,8 +23,7 @@ def llama_plan(cfg: LlamaConfig) -> ModelPlan:
     layers = []
     for i in range(cfg.num_hidden_layers):
         p = f"model.layers.{i}."
-        layers.append(LayerSpec(
-            block=PartSpec("pre_norm"),
+        layers.append(pre_norm_layer(
             mixer_norm=PartSpec("rmsnorm", {"size": cfg.hidden_size, "eps": cfg.rms_norm_eps,
                                             "weight": p + "input_layernorm.weight"}),
             mixer=PartSpec("gqa_attention", {
@@ -68,4 +67,7 @@ LLAMA = register_architecture(Architecture(
     names=("LlamaForCausalLM", "llama"),
     read_config=LlamaConfig.from_json,
     plan=llama_plan,
+    # older exporters store each layer's rotary frequencies as a buffer; they are
+    # recomputed from the configuration here and the stored copy is not read
+    ignore=("*.rotary_emb.inv_freq",),
 ))

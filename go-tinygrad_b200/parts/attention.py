@@ -25,8 +25,6 @@ from ..kernels import ops
 from ..weights.binder import WeightSpec
 from .base import Mixer, Runtime, StepContext, build_part, emit_update, register_part
 
-_SMS = 148                  # streaming multiprocessors of a B200
-
 
 @register_part("mixer", "gqa_attention")
 class GQAttention(Mixer):
@@ -56,7 +54,10 @@ class GQAttention(Mixer):
             specs += [WeightSpec(self.names["k"], (self.kv_dim, self.hidden)),
                       WeightSpec(self.names["v"], (self.kv_dim, self.hidden))]
         specs.append(WeightSpec(self.names["o"], (self.hidden, self.q_dim)))
-        return specs + self.position.weight_specs()
+        return specs
+
+    def children(self):
+        return [self.position]
 
     def cache_requests(self) -> List[Request]:
         return [KVRequest(self.n_kv, self.head_dim, self.window)] if self.own_kv else []
@@ -67,32 +68,6 @@ class GQAttention(Mixer):
             parts += [tensors[self.names["k"]], tensors[self.names["v"]]]
         self.w_qkv = rt.matrix(torch.cat([p.to(rt.dtype) for p in parts], dim=0))
         self.w_o = rt.matrix(tensors[self.names["o"]])
-        self.position.load(tensors, rt)
-
-    def _decode_splits(self, ctx: StepContext) -> int:
-        """Into how many thread blocks the keys of one (sequence, key/value head)
-        are split.  Blocks run in waves of `slots` (what the GPU holds at once):
-        a count just above a whole number of waves leaves the last wave nearly
-        empty, and a split of very few pages pays its fixed cost (query load,
-        merge, partial write) for little work.  The choice depends on the batch
-        and on the longest sequence only, never on the data."""
-        base = ctx.n_seqs * self.n_kv * ((self.n_heads // self.n_kv + 15) // 16)
-        dp = 16 if self.head_dim <= 16 else 32 if self.head_dim <= 32 else 64 if self.head_dim <= 64 else 128
-        stages = 3 if dp == 128 else 4          # as the kernel has them
-        smem = 16 * dp * 2 + stages * 2 * 64 * dp * 2 + 1024
-        slots = _SMS * max(1, min(8, (227 * 1024) // smem))
-        pages = max(1, (max(ctx.max_kv_len, 1) + 63) // 64)
-        best, best_score = 1, -1.0
-        for s in range(1, min(64, pages) + 1):
-            blocks = base * s
-            waves = -(-blocks // slots)
-            per_split = -(-pages // s)
-            score = blocks / (waves * slots) * per_split / (per_split + 1.0)
-            if s > 1:
-                score *= 0.93               # the partial results and the kernel that merges them
-            if score > best_score + 1e-9:
-                best, best_score = s, score
-        return best
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheHandle) -> torch.Tensor:
         rt = ctx.rt
@@ -102,29 +77,43 @@ class GQAttention(Mixer):
         n = x.shape[0]
         qkv = rt.empty(n, self.w_qkv.shape[0])
         rotation = self.position.rotation(ctx)
+        pairing, rotary_dim = self.position.pairing, self.position.rotary_dim or self.head_dim
+        # the kernels that rotate inside a product or inside the attention know one
+        # layout: half-split pairs over the whole head; any other goes the general way
+        plain_layout = rotation is None or (pairing == "half" and rotary_dim == self.head_dim)
         store = self.n_kv if (cache.writes and self.own_kv) else 0
         # a decode step in bfloat16: the attention kernel rotates the queries and adds the new
         # token's key and value itself, and no kernel stands between it and the projection
-        in_attention = (ctx.is_decode and rt.dtype == torch.bfloat16 and ops.attention_bf16_supports(self.head_dim))
-        if store and ops.qkv_rope_fused_supports(x, self.w_qkv, qkv, rotation, self.n_heads, self.n_kv,
-                                                 self.head_dim, kv):
+        in_attention = (ctx.is_decode and rt.dtype == torch.bfloat16 and plain_layout
+                        and ops.attention_bf16_supports(self.head_dim))
+        if store and plain_layout and ops.qkv_rope_fused_supports(x, self.w_qkv, qkv, rotation, self.n_heads,
+                                                                  self.n_kv, self.head_dim, kv):
             # a prompt: rotation and cache store happen in the projection's epilogue
             ops.linear_qkv_rope(x, self.w_qkv, qkv, rotation, self.n_heads, self.n_kv, kv,
                                 ctx.token_seq, ctx.slots, ctx.positions)
             in_attention = False
         else:
             ops.linear(x, self.w_qkv, qkv)
+            if ctx.op_hook is not None:
+                ctx.trace("q", qkv[:, : self.q_dim].clone())
+                if self.own_kv:
+                    ctx.trace("k", qkv[:, self.q_dim: self.q_dim + self.kv_dim])
+                    ctx.trace("v", qkv[:, self.q_dim + self.kv_dim:])
             if not in_attention:
                 ops.rope_kv_store(qkv, rotation, self.n_heads, store, self.head_dim,
-                                  kv, ctx.token_seq, ctx.slots, ctx.positions)
+                                  kv, ctx.token_seq, ctx.slots, ctx.positions,
+                                  pairing=pairing, rotary_dim=rotary_dim)
         q = qkv[:, : self.q_dim]
+        if not in_attention:
+            ctx.trace("q_attn", q)
         mixed = rt.empty(n, self.q_dim)
         window = self.window or 0
         if rt.dtype == torch.bfloat16 and ops.attention_bf16_supports(self.head_dim):
             if ctx.is_decode:
                 new_k = qkv[:, self.q_dim: self.q_dim + self.kv_dim] if store else None
                 new_v = qkv[:, self.q_dim + self.kv_dim:] if store else None
-                splits = self._decode_splits(ctx)
+                splits = ops.attention_decode_plan(n, self.n_heads, self.n_kv, self.head_dim,
+                                                   ctx.max_kv_len, window)
                 scratch = None
                 if splits > 1:
                     scratch = rt.empty(ops.attention_decode_scratch_floats(
@@ -141,4 +130,5 @@ class GQAttention(Mixer):
         else:
             ops.attention_simple(q, mixed, kv, ctx.token_seq, ctx.slots, ctx.positions,
                                  self.n_heads, self.scale, window)
+        ctx.trace("attn", mixed)
         return emit_update(mixed, self.w_o, ctx)

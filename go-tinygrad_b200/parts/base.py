@@ -70,13 +70,16 @@ class Runtime:
         if share_as is not None and share_as in self._shared:
             return self._shared[share_as]
         out = t.to(device=self.device, dtype=self.dtype).contiguous()
+        if out.data_ptr() == t.data_ptr():
+            out = out.clone()               # never keep the loader's own memory (it may be a mapped file)
         if share_as is not None:
             self._shared[share_as] = out
         return out
 
     def vector(self, t: torch.Tensor) -> torch.Tensor:
         """A scale vector on the device, always float32."""
-        return t.to(device=self.device, dtype=torch.float32).contiguous()
+        out = t.to(device=self.device, dtype=torch.float32).contiguous()
+        return out.clone() if out.data_ptr() == t.data_ptr() else out
 
     def empty(self, *shape: int, dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         return torch.empty(shape, dtype=dtype or self.dtype, device=self.device)
@@ -102,17 +105,43 @@ class StepContext:
     is_decode: bool             # every sequence brings exactly one token
     shared: Dict[Any, Any] = field(default_factory=dict)   # per-step values parts share (rotary tables)
     update_into: Optional["ResidualStream"] = None   # set by a block around a part's forward: see emit_update
+    step: int = 0               # which step of the model this is (counted by the model; for `op_hook`)
+    layer: int = -1             # the layer that is running (set by the engine before each block)
+    op_hook: Optional[Callable[[int, int, str, torch.Tensor], None]] = None
+
+    def trace(self, op: str, tensor) -> None:
+        """Hand a named intermediate value of the running layer to the hook, if one
+        is set: `op_hook(step, layer, op, tensor)`.  `tensor` may be a function
+        that builds the value, called only when a hook listens.  The names follow
+        the reference's per-op hook (model/debug_hooks.go:5-7 and its call sites in
+        model/llama.go:1089-1427): hidden_in, normed, q, k, v, q_attn, attn, o,
+        mlp_input, gate_pre, up, gate_act, down, hidden_post_ffn.  A part reports
+        what it materialises: a fused kernel that never writes a value to memory
+        has nothing to report under that name."""
+        if self.op_hook is not None:
+            self.op_hook(self.step, self.layer, op, tensor() if callable(tensor) else tensor)
 
 
 class Part:
     category: str = ""
     kind: str = ""
+    # False for a part whose forward talks to the host (reads a device value, picks
+    # rows by data): a step that contains it cannot be recorded as a CUDA graph,
+    # and the generation loop then launches its decode steps kernel by kernel.
+    capturable: bool = True
 
     def __init__(self, spec: PartSpec):
         self.spec = spec
         self.p: Mapping[str, Any] = spec.params
 
+    def children(self) -> List["Part"]:
+        """Parts this part built from nested specs and owns (a mixer's position
+        encoding, a block's norms, mixer and feed-forward).  The model walks them:
+        their tensors are declared, bound and loaded with everyone else's."""
+        return []
+
     def weight_specs(self) -> List[WeightSpec]:
+        """The tensors of this part itself (its children declare their own)."""
         return []
 
     def load(self, tensors: Mapping[str, torch.Tensor], rt: Runtime) -> None:
@@ -124,6 +153,13 @@ class Part:
         if default is not None:
             return default
         raise KeyError(f"{self.category} part {self.kind!r} needs parameter {name!r}")
+
+
+def walk(part: "Part"):
+    """`part`, then everything below it, parents before children."""
+    yield part
+    for child in part.children():
+        yield from walk(child)
 
 
 class ResidualStream:
@@ -166,12 +202,19 @@ class Norm(Part):
 
 
 class PositionEncoding(Part):
+    # How a rotary kind pairs the channels of a head and how many it rotates; the
+    # kernels that rotate read these.  "half": channel i with i + rotary_dim/2
+    # (model/llama.go:1581-1586); "interleaved": 2i with 2i+1.  rotary_dim None:
+    # the whole head; otherwise the first `rotary_dim` channels, the rest pass.
+    pairing: str = "half"
+    rotary_dim: Optional[int] = None
+
     def on_embedding(self, stream: ResidualStream, ctx: StepContext) -> None:
         """Hook for encodings that act on the embedded tokens (absolute positions)."""
 
     def rotation(self, ctx: StepContext) -> Optional[torch.Tensor]:
-        """For rotary encodings: float32 [n_tokens, head_dim/2, 2] of (cos, sin) for
-        this step's tokens, or None for no rotation of queries and keys."""
+        """For rotary encodings: float32 [n_tokens, rotated channels / 2, 2] of (cos, sin)
+        for this step's tokens, or None for no rotation of queries and keys."""
         return None
 
 
@@ -190,10 +233,29 @@ class FeedForward(Part):
 
 
 class Block(Part):
-    """An arrangement of a mixer and a feed-forward with their norms."""
+    """An arrangement: one layer.  A block kind declares what it is made of in
+    `sub_parts`, pairs of (name, category); each is built from the nested
+    PartSpec of that name among the block's parameters and becomes an attribute
+    of that name.  The block owns them: the model asks the block, never the
+    plan, for the parts of a layer, their tensors and their cache needs.  A
+    block may declare tensors of its own too (`weight_specs`, `load`)."""
+    sub_parts: Tuple[Tuple[str, str], ...] = ()
 
-    def assemble(self, mixer_norm: Norm, mixer: Mixer, ff_norm: Norm, ff: FeedForward) -> None:
-        self.mixer_norm, self.mixer, self.ff_norm, self.ff = mixer_norm, mixer, ff_norm, ff
+    def __init__(self, spec: PartSpec):
+        super().__init__(spec)
+        for name, category in self.sub_parts:
+            setattr(self, name, build_part(category, self.param(name)))
+
+    def children(self) -> List[Part]:
+        return [getattr(self, name) for name, _ in self.sub_parts]
+
+    def cache_requests(self) -> List[Request]:
+        """What one run of this layer keeps per sequence: what its parts ask for."""
+        requests: List[Request] = []
+        for part in walk(self):
+            if part is not self and hasattr(part, "cache_requests"):
+                requests += part.cache_requests()
+        return requests
 
     def forward(self, stream: ResidualStream, ctx: StepContext, cache: CacheHandle) -> None:
         raise NotImplementedError

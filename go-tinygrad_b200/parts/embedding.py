@@ -35,13 +35,13 @@ class TokenEmbedding(Embedding):
         self.table: Optional[torch.Tensor] = None
 
     def weight_specs(self) -> List[WeightSpec]:
-        specs = [WeightSpec(self.weight_name, (self.vocab, self.hidden), role="table")]
-        return specs + (self.position.weight_specs() if self.position else [])
+        return [WeightSpec(self.weight_name, (self.vocab, self.hidden), role="table")]
+
+    def children(self):
+        return [self.position] if self.position else []
 
     def load(self, tensors: Mapping[str, torch.Tensor], rt: Runtime) -> None:
         self.table = rt.matrix(tensors[self.weight_name], share_as=self.weight_name)
-        if self.position:
-            self.position.load(tensors, rt)
 
     def forward(self, ctx: StepContext) -> ResidualStream:
         residual = ctx.rt.empty(ctx.n_tokens, self.hidden, dtype=torch.float32)

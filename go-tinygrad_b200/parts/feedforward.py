@@ -55,5 +55,8 @@ class SwiGLU(FeedForward):
         else:
             gate_up = rt.empty(n, 2 * self.inter)
             ops.linear(x, self.w_gate_up, gate_up)
+            ctx.trace("gate_pre", gate_up[:, : self.inter])
+            ctx.trace("up", gate_up[:, self.inter:])
             ops.swiglu(gate_up, act)
+        ctx.trace("gate_act", act)
         return emit_update(act, self.w_down, ctx)

@@ -28,14 +28,28 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One layer: an arrangement (`block`) of a mixer and a feed-forward, each
-    behind its norm.  Every layer carries its own specs, so mixers and
-    feed-forwards may differ from layer to layer."""
+    """One layer: an arrangement (`block`).  What the arrangement is made of --
+    its mixer, feed-forward, norms, scalars of its own -- are nested PartSpecs
+    among the block's parameters, under the names that block kind declares;
+    the block builds and owns them.  Every layer carries its own spec, so
+    mixers and feed-forwards may differ from layer to layer."""
     block: PartSpec
-    mixer_norm: PartSpec
-    mixer: PartSpec
-    feed_forward_norm: PartSpec
-    feed_forward: PartSpec
+
+    def part(self, name: str) -> PartSpec:
+        """The nested spec the block holds under `name`."""
+        return self.block.params[name]
+
+    def replace(self, **parts: Any) -> "LayerSpec":
+        """The same layer with some of the block's parameters replaced."""
+        return LayerSpec(PartSpec(self.block.kind, dict(self.block.params, **parts)))
+
+
+def pre_norm_layer(mixer_norm: PartSpec, mixer: PartSpec, feed_forward_norm: PartSpec,
+                   feed_forward: PartSpec) -> LayerSpec:
+    """x += mixer(norm(x)); x += feed_forward(norm(x)): the ``pre_norm`` block."""
+    return LayerSpec(PartSpec("pre_norm", {"mixer_norm": mixer_norm, "mixer": mixer,
+                                           "feed_forward_norm": feed_forward_norm,
+                                           "feed_forward": feed_forward}))
 
 
 @dataclass(frozen=True)
@@ -85,14 +99,12 @@ def default_schedule(n_layers: int) -> Tuple[ScheduleEntry, ...]:
 
 def plan_weight_specs(plan: ModelPlan) -> List[Any]:
     """Every tensor the plan's parts declare, built without touching a device."""
-    from .base import build_part  # late import: base imports this module
+    from .base import build_part, walk  # late import: base imports this module
+    roots = [build_part("embedding", plan.embedding)]
+    roots += [build_part("block", layer.block) for layer in plan.layers]
+    roots += [build_part("norm", plan.final_norm), build_part("head", plan.head)]
     specs = []
-    specs += build_part("embedding", plan.embedding).weight_specs()
-    for layer in plan.layers:
-        for category, spec in (("norm", layer.mixer_norm), ("mixer", layer.mixer),
-                               ("norm", layer.feed_forward_norm),
-                               ("feed_forward", layer.feed_forward)):
-            specs += build_part(category, spec).weight_specs()
-    specs += build_part("norm", plan.final_norm).weight_specs()
-    specs += build_part("head", plan.head).weight_specs()
+    for root in roots:
+        for part in walk(root):
+            specs += part.weight_specs()
     return specs

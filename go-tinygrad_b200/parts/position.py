@@ -7,7 +7,12 @@ in float64 on the host; the angles of a step's tokens are computed on the
 device as float64 products and rounded to float32 (cos, sin) pairs, once per
 step, and shared by all layers that use equal parameters.  Parameters:
 ``head_dim``, ``theta``, ``scaling`` (None or the llama3 block: factor,
-low_freq_factor, high_freq_factor, original_max_position_embeddings).
+low_freq_factor, high_freq_factor, original_max_position_embeddings), and
+optionally ``pairing`` ("half", the default: channel i with i + d/2;
+"interleaved": 2i with 2i+1) and ``rotary_dim`` (d: how many of a head's first
+channels rotate; default all; f_i = theta^(-2i/d)).  The rotation inside the
+prompt projection and inside the decode attention serves the default layout;
+any other is rotated by the general kernel between projection and attention.
 
 The llama3 scaling is not in the reference: wavelengths shorter than
 original/high_freq_factor keep their frequency, longer than
@@ -57,20 +62,25 @@ class RotaryEncoding(PositionEncoding):
         self.theta = float(self.param("theta"))
         scaling = self.p.get("scaling")
         self.scaling = dict(scaling) if scaling else None
-        if self.head_dim % 2:
-            raise ValueError("rotary encoding needs an even head_dim")
-        self._key = ("rotary", self.head_dim, self.theta,
+        self.pairing = str(self.p.get("pairing") or "half")
+        if self.pairing not in ("half", "interleaved"):
+            raise ValueError(f"rotary pairing {self.pairing!r} is not known: 'half' or 'interleaved'")
+        self.rotary_dim = int(self.p.get("rotary_dim") or self.head_dim)
+        if self.rotary_dim % 2 or not 0 < self.rotary_dim <= self.head_dim:
+            raise ValueError(f"rotary encoding needs an even number of rotated channels up to the head's "
+                             f"{self.head_dim}, got {self.rotary_dim}")
+        self._key = ("rotary", self.rotary_dim, self.theta,
                      tuple(sorted(self.scaling.items())) if self.scaling else None)
         self.inv_freq: Optional[torch.Tensor] = None
 
     def load(self, tensors, rt: Runtime) -> None:
-        self.inv_freq = torch.tensor(rotary_frequencies(self.head_dim, self.theta, self.scaling),
+        self.inv_freq = torch.tensor(rotary_frequencies(self.rotary_dim, self.theta, self.scaling),
                                      dtype=torch.float64, device=rt.device)
 
     def rotation(self, ctx: StepContext) -> Optional[torch.Tensor]:
         table = ctx.shared.get(self._key)
         if table is None:
-            table = torch.empty((ctx.n_tokens, self.head_dim // 2, 2), dtype=torch.float32,
+            table = torch.empty((ctx.n_tokens, self.rotary_dim // 2, 2), dtype=torch.float32,
                                 device=ctx.rt.device)
             ops.rope_table(ctx.positions, self.inv_freq, table)
             ctx.shared[self._key] = table

@@ -11,6 +11,7 @@ and accepts any shape whose element count matches (model/llama.go:341-349).
 from __future__ import annotations
 
 from dataclasses import dataclass
+from fnmatch import fnmatchcase
 from typing import Dict, Iterable, List, Sequence, Tuple
 
 import torch
@@ -66,9 +67,13 @@ def check_specs(specs: Iterable[WeightSpec]) -> List[WeightSpec]:
     return out
 
 
-def bind(source: TensorSource, specs: Iterable[WeightSpec], where: str = None
-         ) -> Dict[str, torch.Tensor]:
-    """Host tensors by name, in their stored dtype, for exactly the declared specs."""
+def bind(source: TensorSource, specs: Iterable[WeightSpec], where: str = None,
+         ignore: Sequence[str] = (), copy: bool = True) -> Dict[str, torch.Tensor]:
+    """Host tensors by name, in their stored dtype, for exactly the declared specs.
+    A tensor of the checkpoint that no spec declares is an error unless its name
+    matches one of the shell-style patterns in `ignore`.  With copy=False the
+    tensors are read-only views of the mapped files, to be used (sent to the
+    device) and dropped before `source` is closed."""
     specs = check_specs(specs)
     where = where or source.folder
     missing, wrong_shape, wrong_dtype = [], [], []
@@ -84,8 +89,9 @@ def bind(source: TensorSource, specs: Iterable[WeightSpec], where: str = None
             wrong_shape.append((s.name, tuple(s.shape), got))
         elif not source.dtype(s.name).is_floating_point:
             wrong_dtype.append((s.name, str(source.dtype(s.name))))
-    unexpected = sorted(n for n in source.names() if n not in declared)
+    unexpected = sorted(n for n in source.names()
+                        if n not in declared and not any(fnmatchcase(n, pat) for pat in ignore))
     if missing or unexpected or wrong_shape or wrong_dtype:
         raise WeightError(where, missing, unexpected, wrong_shape, wrong_dtype)
-    return {s.name: source.tensor(s.name) for s in specs
+    return {s.name: source.tensor(s.name, copy=copy) for s in specs
             if s.name in source and s.role != "ignored"}

@@ -18,6 +18,7 @@ import json
 import mmap
 import os
 import struct
+import warnings
 from typing import Dict, Iterable, List, Mapping, Tuple
 
 import torch
@@ -103,12 +104,20 @@ class SafetensorsFile:
         dt = self.entries[name][0]
         return torch.int32 if dt == "I64" else _DTYPES[dt][0]
 
-    def tensor(self, name: str) -> torch.Tensor:
-        """A host copy of the tensor in its stored dtype (int64 narrowed to int32)."""
+    def tensor(self, name: str, copy: bool = True) -> torch.Tensor:
+        """The tensor in its stored dtype (int64 narrowed to int32): a host copy,
+        or with copy=False a read-only view of the mapped file that is valid while
+        the file is open -- a loader that sends it straight to the device then
+        copies each tensor once, not twice."""
         dt, shape, begin, end = self.entries[name]
-        tdt = _DTYPES[dt][0]
+        tdt, size = _DTYPES[dt]
         if end == begin:
             out = torch.empty(shape, dtype=tdt)
+        elif not copy and (self._base + begin) % size == 0:
+            with warnings.catch_warnings():
+                warnings.simplefilter("ignore", UserWarning)     # the map is read-only; nobody writes to the view
+                out = torch.frombuffer(self._mm, dtype=tdt, count=_numel(shape),
+                                       offset=self._base + begin).reshape(shape)
         else:
             buf = memoryview(self._mm)[self._base + begin: self._base + end]
             out = torch.frombuffer(bytearray(buf), dtype=tdt).reshape(shape)
@@ -121,6 +130,8 @@ class SafetensorsFile:
     def close(self) -> None:
         try:
             self._mm.close()
+        except BufferError:
+            pass              # a view handed out with copy=False is still alive; the map goes with it
         finally:
             self._f.close()
 
@@ -169,8 +180,8 @@ class TensorSource:
     def dtype(self, name: str) -> torch.dtype:
         return self._files[self._where[name]].dtype(name)
 
-    def tensor(self, name: str) -> torch.Tensor:
-        return self._files[self._where[name]].tensor(name)
+    def tensor(self, name: str, copy: bool = True) -> torch.Tensor:
+        return self._files[self._where[name]].tensor(name, copy=copy)
 
     def close(self) -> None:
         for f in self._files.values():

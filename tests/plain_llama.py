@@ -203,30 +203,54 @@ def swiglu_mlp(x, wg, wu, wd):
     return linear(silu_mul(linear(x, wg), linear(x, wu)), wd)
 
 
-def attention_block(x, positions, p, cfg, inv_freq, w, window=None):
+def _no_trace(op, value):
+    pass
+
+
+def attention_block(x, positions, p, cfg, inv_freq, w, window=None, trace=_no_trace):
     """q,k,v projections, RoPE on q and k, causal GQA attention, output
-    projection (model/llama.go:1111-1137, 1230-1233, 1259-1297)."""
+    projection (model/llama.go:1111-1137, 1230-1233, 1259-1297).  `trace(op,
+    value)` receives the values the reference hands to its per-op hook under
+    the same names (model/llama.go:1147-1153 q k v, :1236-1241 q_attn k_attn,
+    :1285-1287 attn, :1298-1300 o)."""
     nh, nkv, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
     q = linear(x, w[p + "self_attn.q_proj.weight"])
     k = linear(x, w[p + "self_attn.k_proj.weight"])
     v = linear(x, w[p + "self_attn.v_proj.weight"])
+    trace("q", q); trace("k", k); trace("v", v)
     q = rope(q, positions, inv_freq, nh, hd)
     k = rope(k, positions, inv_freq, nkv, hd)
+    trace("q_attn", q); trace("k_attn", k)
     a = causal_gqa_attention(q, k, v, nh, nkv, hd, window=window)
-    return linear(a, w[p + "self_attn.o_proj.weight"])
+    trace("attn", a)
+    o = linear(a, w[p + "self_attn.o_proj.weight"])
+    trace("o", o)
+    return o
 
 
-def decoder_layer(x, positions, layer, cfg, inv_freq, w):
+def decoder_layer(x, positions, layer, cfg, inv_freq, w, trace=_no_trace):
     """Pre-norm residual block: x += attn(norm1(x)); x += mlp(norm2(x))
-    (model/llama.go:1087-1097, 1311-1314, 1425)."""
+    (model/llama.go:1087-1097, 1311-1314, 1425).  `trace(op, value)`: the
+    reference's per-op hook names (model/llama.go:1089-1101 hidden_in normed,
+    :1351-1353 mlp_input, :1378-1391 gate_pre up gate_act, :1408-1410 down,
+    :1426-1428 hidden_post_ffn)."""
     p = f"model.layers.{layer}."
     eps = cfg["rms_norm_eps"]
+    trace("hidden_in", x)
     n = rms_norm(x, w[p + "input_layernorm.weight"], eps)
-    x = (x + attention_block(n, positions, p, cfg, inv_freq, w)).astype(F32)
+    trace("normed", n)
+    x = (x + attention_block(n, positions, p, cfg, inv_freq, w, trace=trace)).astype(F32)
     n2 = rms_norm(x, w[p + "post_attention_layernorm.weight"], eps)
-    d = swiglu_mlp(n2, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"],
-                   w[p + "mlp.down_proj.weight"])
-    return (x + d).astype(F32)
+    trace("mlp_input", n2)
+    gate, up = linear(n2, w[p + "mlp.gate_proj.weight"]), linear(n2, w[p + "mlp.up_proj.weight"])
+    trace("gate_pre", gate); trace("up", up)
+    act = silu_mul(gate, up)
+    trace("gate_act", act)
+    d = linear(act, w[p + "mlp.down_proj.weight"])
+    trace("down", d)
+    x = (x + d).astype(F32)
+    trace("hidden_post_ffn", x)
+    return x
 
 
 def lm_head(x, cfg, w):
@@ -238,16 +262,18 @@ def lm_head(x, cfg, w):
     return linear(xf, table)
 
 
-def forward(cfg, w, tokens, layer_order=None):
+def forward(cfg, w, tokens, layer_order=None, trace=None):
     """Logits [T, V] of one whole sequence (model/llama.go:1047-1473 run for
-    every position).  `layer_order` lists the layers to run (default 0..L-1)."""
+    every position).  `layer_order` lists the layers to run (default 0..L-1).
+    `trace(layer, op, value)` receives every layer's named intermediate values."""
     tokens = list(tokens)
     positions = list(range(len(tokens)))
     inv_freq = rope_inv_freq(cfg)
     x = embed(w["model.embed_tokens.weight"], tokens)
     order = range(cfg["num_hidden_layers"]) if layer_order is None else layer_order
     for layer in order:
-        x = decoder_layer(x, positions, layer, cfg, inv_freq, w)
+        layer_trace = _no_trace if trace is None else (lambda op, value, layer=layer: trace(layer, op, value))
+        x = decoder_layer(x, positions, layer, cfg, inv_freq, w, trace=layer_trace)
     return lm_head(x, cfg, w)
 
 

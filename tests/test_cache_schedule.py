@@ -93,10 +93,11 @@ def test_sequences_take_and_return_pages():
     with pytest.raises(CacheFull, match="full"):
         cache.reserve_many([(a, 65 + 128), (b, 64 + 128)])
     assert cache.free_pages() == [3, 3]                   # all or nothing
-    cache.truncate(a, 3)
-    assert cache.length(a) == 3 and cache.free_pages() == [3, 3]
-    with pytest.raises(CacheMisuse):
-        cache.truncate(a, 4)
+    # this cache holds a record of fixed size too: a shorter length would leave the
+    # record as it is, so rolling back is refused rather than silently wrong
+    with pytest.raises(CacheMisuse, match="fixed size"):
+        cache.truncate(a, 3)
+    assert cache.length(a) == 65
     cache.close_sequence(a)
     assert cache.free_pages() == [5, 5] and cache.open_slots() == [b]
     with pytest.raises(CacheMisuse, match="not open"):
@@ -105,6 +106,37 @@ def test_sequences_take_and_return_pages():
         cache.reserve(a, 1)
     cache.close_sequence(b)
     assert cache.free_pages() == [6, 6] and cache.open_slots() == [] and cache.tokens_held() == 0
+
+
+def test_truncate_forgets_tokens_of_a_cache_of_keys_and_values():
+    cache = Cache([[KVRequest(2, 16)], [KVRequest(1, 32, window=128)]], [None, None], max_tokens=64 * 4,
+                  max_slots=2, dtype=torch.float32, device="cpu")
+    a = cache.open_sequence()
+    cache.reserve(a, 65)
+    cache.advance(a, 65)
+    cache.truncate(a, 3)
+    assert cache.length(a) == 3 and cache.free_pages() == [2, 2]      # the pages stay with the sequence
+    with pytest.raises(CacheMisuse):
+        cache.truncate(a, 4)
+    cache.close_sequence(a)
+    assert cache.free_pages() == [4, 4]
+
+
+def test_the_longest_sequence_is_counted_in_tokens_not_pages():
+    # a model whose longest position is no multiple of the page size: positions up to
+    # 99 exist, position 100 does not, although its page is there
+    cache = Cache([[KVRequest(2, 16)]], [None], max_tokens=64 * 8, max_slots=2, max_position=100,
+                  dtype=torch.float32, device="cpu")
+    assert cache.max_sequence == 100 and cache.pages_per_seq == 2
+    a, b = cache.open_sequence(), cache.open_sequence()
+    cache.reserve(a, 100)
+    with pytest.raises(CacheFull, match="longest"):
+        cache.reserve(a, 101)
+    with pytest.raises(CacheFull, match="longest"):
+        cache.reserve_many([(b, 64), (a, 101)])
+    assert cache.free_pages() == [6]                      # the refused step took nothing for b either
+    cache.reserve_many([(b, 64), (a, 100)])
+    assert cache.free_pages() == [5]
 
 
 def test_slots_are_used_again_and_state_starts_at_zero():
@@ -128,7 +160,13 @@ def test_slots_are_used_again_and_state_starts_at_zero():
 def test_a_sequence_cannot_outgrow_the_table():
     cache = Cache([[KVRequest(1, 16)]], [None], max_tokens=64 * 10, max_slots=2, max_position=200,
                   dtype=torch.float32, device="cpu")
-    assert cache.pages_per_seq == 4
+    assert cache.pages_per_seq == 4 and cache.max_sequence == 200
+    s = cache.open_sequence()
+    cache.reserve(s, 200)
+    with pytest.raises(CacheFull, match="longest"):
+        cache.reserve(s, 201)
+    # without a model's limit the table's pages decide
+    cache = Cache([[KVRequest(1, 16)]], [None], max_tokens=64 * 4, max_slots=2, dtype=torch.float32, device="cpu")
     s = cache.open_sequence()
     cache.reserve(s, 256)
     with pytest.raises(CacheFull, match="longest"):

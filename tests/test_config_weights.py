@@ -239,3 +239,37 @@ def test_tied_head_tolerates_a_stray_lm_head_and_untied_needs_one(tmp_path):
     arch, cfg = read_model_config(folder_b)
     with TensorSource(folder_b) as src, pytest.raises(WeightError, match="lm_head.weight"):
         bind(src, plan_weight_specs(arch.plan(cfg)))
+
+
+def test_buffers_an_architecture_names_are_passed_over_and_nothing_else(tmp_path):
+    """Older exporters of this architecture store each layer's rotary frequencies
+    (self_attn.rotary_emb.inv_freq).  The architecture's registry entry names that
+    pattern; such tensors are not read and are no error, while any other tensor
+    nobody declared still is, and a view handed out without a copy reads the same
+    bytes as a copy."""
+    folder = str(tmp_path / "m")
+    lib.write_random_model(folder, TINY_A, seed=0, dtype="bfloat16")
+    path = os.path.join(folder, "model.safetensors")
+    with TensorSource(folder) as src:
+        tensors = {n: src.tensor(n) for n in src.names()}
+    for layer in range(2):
+        tensors[f"model.layers.{layer}.self_attn.rotary_emb.inv_freq"] = torch.ones(8)
+    write_safetensors(path, tensors)
+    arch, cfg = read_model_config(folder)
+    assert "*.rotary_emb.inv_freq" in arch.ignore
+    specs = plan_weight_specs(arch.plan(cfg))
+    with TensorSource(folder) as src, pytest.raises(WeightError) as err:
+        bind(src, specs)                                   # without the architecture's patterns: unexpected
+    assert len(err.value.unexpected) == 2
+    with TensorSource(folder) as src:
+        bound = bind(src, specs, ignore=arch.ignore)
+        views = bind(src, specs, ignore=arch.ignore, copy=False)
+        assert not any("inv_freq" in n for n in bound) and set(views) == set(bound)
+        for n in bound:
+            assert torch.equal(bound[n], views[n]) and bound[n].dtype == torch.bfloat16
+        del views
+    tensors["model.layers.0.self_attn.rotary_emb.cos_cached"] = torch.ones(8)
+    write_safetensors(path, tensors)
+    with TensorSource(folder) as src, pytest.raises(WeightError) as err:
+        bind(src, specs, ignore=arch.ignore)
+    assert err.value.unexpected == ["model.layers.0.self_attn.rotary_emb.cos_cached"]

@@ -197,3 +197,57 @@ def test_step_refuses_bad_batches(model_folders):
     assert cache.length(s) == 0 and cache.free_pages() == [2]      # nothing was taken
     assert step(model, cache, [StepEntry(s, [1, 2, 3], [])]).shape == (0, 256)
     assert cache.length(s) == 3
+
+
+# ------------------------------------------------------------------ the per-op hook
+OPS_OF_A_LAYER = ["hidden_in", "normed", "q", "k", "v", "q_attn", "attn", "o", "mlp_input",
+                  "gate_pre", "up", "gate_act", "down", "hidden_post_ffn"]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_the_op_hook_names_every_value_of_a_layer(model_folders, plain_models, name, dtype):
+    """With `model.op_hook` set, every layer hands its named intermediate values to
+    the hook, under the reference's names; the plain implementation emits the same
+    names, and the two are compared op by op -- the tool that says WHERE a model
+    that drifts starts to drift.  Without a hook nothing is called, and decode
+    steps of a generation are recorded as graphs again."""
+    import plain_llama
+    from go_tinygrad_b200.engine.generate import generate
+    model = Model.load(model_folders[name], dtype=dtype, device="cuda")
+    cfg, w = plain_models[name]
+    (p,) = make_prompts(name, [37], seed=21)
+    want = {}
+    plain_llama.forward(cfg, w, p, trace=lambda layer, op, value: want.__setitem__((layer, op), np.array(value)))
+    got, steps = {}, set()
+
+    def hook(step_index, layer, op, tensor):
+        steps.add(step_index)
+        got[(layer, op)] = tensor.float().cpu().numpy()
+    model.op_hook = hook
+    cache = model.new_cache(max_tokens=64 * 2)
+    slot = cache.open_sequence()
+    first = model.steps_run
+    step(model, cache, [StepEntry(slot, p, [len(p) - 1])])
+    assert steps == {first}
+    n_layers = cfg["num_hidden_layers"]
+    expected = set(OPS_OF_A_LAYER)
+    if dtype == "bfloat16" and cfg["intermediate_size"] % 8 == 0:
+        expected -= {"gate_pre", "up"}               # the activation is applied in the product's epilogue
+    assert {op for (layer, op) in got} == expected and {layer for (layer, op) in got} == set(range(n_layers))
+    for (layer, op), value in got.items():
+        ref = want[(layer, op)]
+        assert value.shape == ref.shape, (layer, op)
+        limit = (2e-5 if dtype == "float32" else 3e-2) * max(1.0, float(np.abs(ref).max()))
+        assert np.abs(value - ref).max() <= limit, f"layer {layer} {op}: {np.abs(value - ref).max():.3e} > {limit:.3e}"
+    # a decode step under the hook runs in the open and reports its one token
+    got.clear()
+    assert not model.capturable
+    out = generate(model, [p[:9]], max_new_tokens=3, stop=[])
+    assert len(out[0].tokens) == 3 and got[(0, "normed")].shape == (1, cfg["hidden_size"])
+    model.op_hook = None
+    got.clear()
+    assert model.capturable
+    again = generate(model, [p[:9]], max_new_tokens=3, stop=[])
+    assert [r.tokens for r in again] == [r.tokens for r in out] and not got
+    cache.close_sequence(slot)

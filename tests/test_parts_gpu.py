@@ -14,9 +14,9 @@ from go_tinygrad_b200.cache import Cache, StateRequest
 from go_tinygrad_b200.config import Architecture, LlamaConfig, register_architecture, unregister_architecture
 from go_tinygrad_b200.engine import Model, StepEntry, step
 from go_tinygrad_b200.models.llama import llama_plan
-from go_tinygrad_b200.parts import (FeedForward, LayerSpec, Mixer, ModelPlan, PartSpec, PositionEncoding,
+from go_tinygrad_b200.parts import (Block, FeedForward, LayerSpec, Mixer, ModelPlan, PartSpec, PositionEncoding,
                                     ResidualStream, Runtime, ScheduleEntry, StepContext, build_part,
-                                    register_part, unregister_part)
+                                    register_part, unregister_part, walk)
 from go_tinygrad_b200.weights import TensorSource, WeightSpec
 from conftest import TINY, assert_close, make_prompts
 
@@ -69,7 +69,7 @@ def test_parts_alone(model_folders, plain_models, name, dtype):
 
     # norm: the pending update is added in float32, then normalised
     layer = plan.layers[1]
-    norm = build_part("norm", layer.mixer_norm); norm.load(raw, rt)
+    norm = build_part("norm", layer.part("mixer_norm")); norm.load(raw, rt)
     res = torch.tensor(x_np, device=DEV)
     st = ResidualStream(res.clone(), x_act.clone())
     got = norm.forward(st, ctx)
@@ -80,7 +80,7 @@ def test_parts_alone(model_folders, plain_models, name, dtype):
     torch.testing.assert_close(got.float().cpu(), torch.tensor(want).to(dtype).float(), **tol(dtype))
 
     # position encoding: the angles of the step's tokens
-    pos = build_part("position", layer.mixer.params["position"]); pos.load(raw, rt)
+    pos = build_part("position", layer.part("mixer").params["position"]); pos.load(raw, rt)
     table = pos.rotation(ctx).cpu().numpy()
     inv = plain.rope_inv_freq(cfg)
     positions = list(range(70)) + list(range(9))
@@ -90,7 +90,9 @@ def test_parts_alone(model_folders, plain_models, name, dtype):
     assert pos.rotation(ctx) is pos.rotation(ctx)                 # computed once per step
 
     # mixer: attention over a cache of its own, two sequences in one step
-    mixer = build_part("mixer", layer.mixer); mixer.load(raw, rt)
+    mixer = build_part("mixer", layer.part("mixer"))
+    for part in walk(mixer):                                      # the mixer and the position encoding it owns
+        part.load(raw, rt)
     cache = Cache([mixer.cache_requests()], [None], max_tokens=64 * 4, max_slots=2, dtype=dtype, device=DEV)
     for _ in range(2):
         cache.open_sequence()
@@ -103,16 +105,18 @@ def test_parts_alone(model_folders, plain_models, name, dtype):
     assert np.abs(got - want).max() <= limit * max(1.0, scale)
 
     # feed-forward
-    ff = build_part("feed_forward", layer.feed_forward); ff.load(raw, rt)
+    ff = build_part("feed_forward", layer.part("feed_forward")); ff.load(raw, rt)
     got = ff.forward(x_act, ctx).float().cpu().numpy()
     p = "model.layers.1.mlp."
     want = plain.swiglu_mlp(x_ref, w[p + "gate_proj.weight"], w[p + "up_proj.weight"], w[p + "down_proj.weight"])
     assert np.abs(got - want).max() <= limit * max(1.0, np.abs(want).max())
 
     # block: the whole layer; its second update stays pending, or its product has added it already
-    block = build_part("block", layer.block)
-    block.assemble(norm, mixer, build_part("norm", layer.feed_forward_norm), ff)
-    block.ff_norm.load(raw, rt)
+    block = build_part("block", layer.block)                      # it builds and owns its four parts
+    assert [type(c) for c in block.children()] == [type(norm), type(mixer), type(norm), type(ff)]
+    assert block.cache_requests() == mixer.cache_requests()
+    for part in walk(block):
+        part.load(raw, rt)
     cache2 = Cache([mixer.cache_requests()], [None], max_tokens=64 * 4, max_slots=2, dtype=dtype, device=DEV)
     for _ in range(2):
         cache2.open_sequence()
@@ -175,11 +179,9 @@ def toy_plan(cfg):
     layers = []
     for i, layer in enumerate(base.layers):
         if i % 2 == 1:
-            layer = LayerSpec(layer.block, layer.mixer_norm,
-                              PartSpec("decay", {"hidden_size": cfg.hidden_size,
-                                                 "decay": f"model.layers.{i}.decay.a",
-                                                 "out": f"model.layers.{i}.decay.out.weight"}),
-                              layer.feed_forward_norm, layer.feed_forward)
+            layer = layer.replace(mixer=PartSpec("decay", {"hidden_size": cfg.hidden_size,
+                                                           "decay": f"model.layers.{i}.decay.a",
+                                                           "out": f"model.layers.{i}.decay.out.weight"}))
         layers.append(layer)
     return ModelPlan(base.hidden_size, base.vocab_size, base.embedding, tuple(layers), base.schedule,
                      base.final_norm, base.head, base.stop_tokens, base.max_position)
@@ -259,9 +261,7 @@ def test_a_layer_named_twice_and_a_layer_that_reads_another_cache(model_folders,
 
     # a third run: layer 1's queries over the keys and values that run 0 stored
     l1 = base.layers[1]
-    reader = LayerSpec(l1.block, l1.mixer_norm,
-                       PartSpec("gqa_attention", dict(l1.mixer.params, own_kv=False)),
-                       l1.feed_forward_norm, l1.feed_forward)
+    reader = l1.replace(mixer=PartSpec("gqa_attention", dict(l1.part("mixer").params, own_kv=False)))
     shared = ModelPlan(base.hidden_size, base.vocab_size, base.embedding, (base.layers[0], reader),
                        (ScheduleEntry(0), ScheduleEntry(1, cache=0)),
                        base.final_norm, base.head, base.stop_tokens, base.max_position)
@@ -360,12 +360,12 @@ def routed_plan(cfg):
     base = llama_plan(cfg)
     layers = []
     for i, layer in enumerate(base.layers):
-        mixer = PartSpec(layer.mixer.kind, dict(layer.mixer.params, position=PartSpec("none")))
-        ff = layer.feed_forward
+        mixer = PartSpec(layer.part("mixer").kind, dict(layer.part("mixer").params, position=PartSpec("none")))
+        ff = layer.part("feed_forward")
         if i == 1:
             ff = PartSpec("top1_experts", {"hidden_size": cfg.hidden_size, "intermediate_size": 40,
                                            "n_experts": N_EXPERTS, "prefix": f"model.layers.{i}.moe."})
-        layers.append(LayerSpec(layer.block, layer.mixer_norm, mixer, layer.feed_forward_norm, ff))
+        layers.append(layer.replace(mixer=mixer, feed_forward=ff))
     embedding = PartSpec(base.embedding.kind, dict(base.embedding.params, position=PartSpec(
         "learned_positions", {"max_position": 96, "hidden_size": cfg.hidden_size, "weight": "model.positions.weight"})))
     return ModelPlan(base.hidden_size, base.vocab_size, embedding, tuple(layers), base.schedule,
@@ -408,7 +408,7 @@ def test_a_routed_feed_forward_and_learned_positions_without_touching_the_librar
         cfg, w = plain.read_model(folder)
         assert f"model.layers.1.moe.experts.{N_EXPERTS - 1}.down.weight" in w and "model.layers.1.mlp.up_proj.weight" not in w
         model = Model.load(folder, dtype="float32", device="cuda")
-        assert type(model.blocks[1].ff) is Top1Experts
+        assert type(model.blocks[1].feed_forward) is Top1Experts
         cache = model.new_cache(max_tokens=64 * 4, max_slots=2)
         p, q = make_prompts("B", [40, 23], seed=77)
         want_p, want_q = plain_routed_forward(cfg, w, p), plain_routed_forward(cfg, w, q)
@@ -422,3 +422,199 @@ def test_a_routed_feed_forward_and_learned_positions_without_touching_the_librar
         unregister_architecture(arch)
         unregister_part("position", "learned_positions")
         unregister_part("feed_forward", "top1_experts")
+
+
+# ------------------------------------------- an arrangement that is not mixer + feed-forward behind two norms
+class SandwichBlock(Block):
+    """x += s * post1(mixer(pre1(x))); x += post2(feed_forward(pre2(x))): four norms
+    and a learned scalar s per layer.  The block declares what it is made of and a
+    tensor of its own; nothing in the library knows the arrangement.  The
+    additions are plain torch: a test's toy."""
+    sub_parts = (("pre_mixer_norm", "norm"), ("mixer", "mixer"), ("post_mixer_norm", "norm"),
+                 ("pre_ff_norm", "norm"), ("feed_forward", "feed_forward"), ("post_ff_norm", "norm"))
+
+    def weight_specs(self):
+        return [WeightSpec(self.param("scalar"), (1,), role="vector", mean=1.0)]
+
+    def load(self, tensors, rt):
+        self.scalar = rt.vector(tensors[self.param("scalar")])
+
+    def forward(self, stream, ctx, cache):
+        x = self.pre_mixer_norm.forward(stream, ctx)                 # adds what the layer before left pending
+        update = self.mixer.forward(x, ctx, cache)
+        update = self.post_mixer_norm.forward(ResidualStream(update.float().contiguous()), ctx)
+        stream.residual += self.scalar * update.float()
+        x = self.pre_ff_norm.forward(stream, ctx)
+        update = self.feed_forward.forward(x, ctx)
+        stream.pending = self.post_ff_norm.forward(ResidualStream(update.float().contiguous()), ctx)
+
+
+def sandwich_plan(cfg):
+    base = llama_plan(cfg)
+    layers = []
+    for i, layer in enumerate(base.layers):
+        p = f"model.layers.{i}."
+        norm = lambda name: PartSpec("rmsnorm", {"size": cfg.hidden_size, "eps": cfg.rms_norm_eps, "weight": p + name})
+        layers.append(LayerSpec(PartSpec("sandwich", {
+            "pre_mixer_norm": layer.part("mixer_norm"), "mixer": layer.part("mixer"),
+            "post_mixer_norm": norm("post_mixer_layernorm.weight"),
+            "pre_ff_norm": layer.part("feed_forward_norm"), "feed_forward": layer.part("feed_forward"),
+            "post_ff_norm": norm("post_feedforward_layernorm.weight"), "scalar": p + "layer_scalar"})))
+    return ModelPlan(base.hidden_size, base.vocab_size, base.embedding, tuple(layers), base.schedule,
+                     base.final_norm, base.head, base.stop_tokens, base.max_position)
+
+
+def plain_sandwich_forward(cfg, w, tokens):
+    positions = list(range(len(tokens)))
+    inv, eps = plain.rope_inv_freq(cfg), cfg["rms_norm_eps"]
+    x = plain.embed(w["model.embed_tokens.weight"], tokens)
+    for i in range(cfg["num_hidden_layers"]):
+        p = f"model.layers.{i}."
+        a = plain.attention_block(plain.rms_norm(x, w[p + "input_layernorm.weight"], eps), positions, p, cfg, inv, w)
+        x = (x + w[p + "layer_scalar"].astype(np.float32) *
+             plain.rms_norm(a, w[p + "post_mixer_layernorm.weight"], eps)).astype(np.float32)
+        d = plain.swiglu_mlp(plain.rms_norm(x, w[p + "post_attention_layernorm.weight"], eps),
+                             w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"])
+        x = (x + plain.rms_norm(d, w[p + "post_feedforward_layernorm.weight"], eps)).astype(np.float32)
+    return plain.lm_head(x, cfg, w)
+
+
+def test_a_block_with_four_norms_and_a_scalar_of_its_own(tmp_path):
+    register_part("block", "sandwich")(SandwichBlock)
+    arch = register_architecture(Architecture(("ToySandwichForCausalLM",), LlamaConfig.from_json, sandwich_plan))
+    try:
+        raw = dict(TINY["A"], architectures=["ToySandwichForCausalLM"], model_type="toy_sandwich")
+        folder = str(tmp_path / "sandwich")
+        lib.write_random_model(folder, raw, seed=3, dtype="float32", std=0.1, norm_std=0.05)
+        cfg, w = plain.read_model(folder)
+        assert w["model.layers.1.layer_scalar"].shape == (1,) and "model.layers.0.post_mixer_layernorm.weight" in w
+        model = Model.load(folder, dtype="float32", device="cuda")
+        names = {s.name for s in model.weight_specs()}
+        assert {"model.layers.0.layer_scalar", "model.layers.1.post_feedforward_layernorm.weight"} <= names
+        assert len(model.blocks[0].children()) == 6 and model.capturable
+        cache = model.new_cache(max_tokens=64 * 4, max_slots=2)
+        assert cache.groups[0].storage.shape[0] == 2              # the block passed its mixer's request on
+        p, q = make_prompts("A", [45, 18], seed=12)
+        want_p, want_q = plain_sandwich_forward(cfg, w, p), plain_sandwich_forward(cfg, w, q)
+        sp, sq = cache.open_sequence(), cache.open_sequence()
+        got = step(model, cache, [StepEntry(sp, p[:30], list(range(30))), StepEntry(sq, q, list(range(18)))]).cpu().numpy()
+        assert_close(got[:30], want_p[:30], "float32", "sandwich whole")
+        assert_close(got[30:], want_q, "float32", "sandwich second sequence")
+        rest = [step(model, cache, [StepEntry(sp, [p[t]], [0])]).cpu().numpy() for t in range(30, 45)]
+        assert_close(np.concatenate(rest), want_p[30:], "float32", "sandwich one by one")
+        # a missing tensor of the block itself is reported like any other
+        tensors = {k: v for k, v in tensors_of(folder).items() if k != "model.layers.1.layer_scalar"}
+        from go_tinygrad_b200.weights import write_safetensors
+        broken = tmp_path / "broken"
+        broken.mkdir()
+        (broken / "config.json").write_text((tmp_path / "sandwich" / "config.json").read_text())
+        write_safetensors(str(broken / "model.safetensors"), tensors)
+        with pytest.raises(lib.WeightError, match="layer_scalar"):
+            Model.load(str(broken), dtype="float32", device="cuda")
+    finally:
+        unregister_architecture(arch)
+        unregister_part("block", "sandwich")
+
+
+# ------------------------------------------------- another layout of the rotation
+def plain_rope_layout(x, positions, inv_freq, n_heads, hd, rot, interleaved):
+    """The first `rot` channels of every head rotate, pair i being (i, i + rot/2) or,
+    interleaved, (2i, 2i+1); the rest pass.  Written out element by element."""
+    x = np.asarray(x, dtype=np.float32).reshape(len(positions), n_heads, hd)
+    out = x.copy()
+    for t, pos in enumerate(positions):
+        for i in range(rot // 2):
+            c, s = np.float32(math.cos(pos * inv_freq[i])), np.float32(math.sin(pos * inv_freq[i]))
+            ia, ib = (2 * i, 2 * i + 1) if interleaved else (i, i + rot // 2)
+            a, b = x[t, :, ia], x[t, :, ib]
+            out[t, :, ia], out[t, :, ib] = a * c - b * s, a * s + b * c
+    return out.reshape(len(positions), n_heads * hd)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("name,pairing,rot", [("A", "interleaved", 16), ("A", "half", 8), ("B", "interleaved", 32)])
+def test_attention_with_another_rotary_layout(model_folders, plain_models, name, pairing, rot, dtype):
+    """Interleaved pairs and a rotated fraction of the head are a position
+    encoding's parameters: the attention part asks the encoding for its layout and
+    the general rotation kernel serves it, for prompts and for single tokens."""
+    cfg, w = plain_models[name]
+    raw = tensors_of(model_folders[name])
+    base = llama_plan(LlamaConfig.from_json(TINY[name])).layers[1].part("mixer")
+    nh, nkv, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    position = PartSpec("rotary", dict(base.params["position"].params, pairing=pairing, rotary_dim=rot))
+    rt = Runtime(DEV, dtype)
+    mixer = build_part("mixer", PartSpec(base.kind, dict(base.params, position=position)))
+    for part in walk(mixer):
+        part.load(raw, rt)
+    T, head = 75, 70
+    x_np = np.random.default_rng(3).standard_normal((T, cfg["hidden_size"])).astype(np.float32)
+    x_act = torch.tensor(x_np, device=DEV).to(dtype)
+    x_ref = x_act.float().cpu().numpy()
+    cache = Cache([mixer.cache_requests()], [None], max_tokens=64 * 2, max_slots=1, dtype=dtype, device=DEV)
+    slot = cache.open_sequence()
+    cache.reserve(slot, T); cache.flush_tables()
+    got = [mixer.forward(x_act[:head], context(rt, [head], [0], [slot]), cache.handles[0])]
+    cache.advance(slot, head)
+    for t in range(head, T):                                       # then token by token
+        got.append(mixer.forward(x_act[t:t + 1], context(rt, [1], [t], [slot]), cache.handles[0]))
+        cache.advance(slot, 1)
+    got = torch.cat(got).float().cpu().numpy()
+
+    theta = float(cfg["rope_theta"])
+    inv = np.array([theta ** (-2.0 * i / rot) for i in range(rot // 2)])
+    if cfg.get("rope_scaling"):
+        inv = np.array(plain.rope_inv_freq(dict(cfg, head_dim=rot)))
+    p = "model.layers.1.self_attn."
+    positions = list(range(T))
+    q = plain_rope_layout(plain.linear(x_ref, w[p + "q_proj.weight"]), positions, inv, nh, hd, rot, pairing == "interleaved")
+    k = plain_rope_layout(plain.linear(x_ref, w[p + "k_proj.weight"]), positions, inv, nkv, hd, rot, pairing == "interleaved")
+    v = plain.linear(x_ref, w[p + "v_proj.weight"])
+    want = plain.linear(plain.causal_gqa_attention(q, k, v, nh, nkv, hd), w[p + "o_proj.weight"])
+    limit = 1e-4 if dtype == torch.float32 else 4e-2
+    assert np.abs(got - want).max() <= limit * max(1.0, np.abs(want).max())
+    # and the layout matters: the default one gives another result
+    plain_default = plain.attention_block(x_ref, positions, "model.layers.1.", cfg, plain.rope_inv_freq(cfg), w)
+    assert np.abs(plain_default - want).max() > 20 * limit * max(1.0, np.abs(want).max())
+
+
+def test_a_rotary_layout_the_kernels_do_not_know_is_refused():
+    with pytest.raises(ValueError, match="pairing"):
+        build_part("position", PartSpec("rotary", {"head_dim": 16, "theta": 1e4, "pairing": "quarters"}))
+    with pytest.raises(ValueError, match="rotated channels"):
+        build_part("position", PartSpec("rotary", {"head_dim": 16, "theta": 1e4, "rotary_dim": 18}))
+    from go_tinygrad_b200.kernels import ops
+    qkv = torch.zeros((2, 64), dtype=torch.float32, device=DEV)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    with pytest.raises(ops.KernelError, match="pairing"):
+        ops.rope_kv_store(qkv, None, 4, 0, 16, None, i32([0, 0]), i32([0]), i32([0, 1]), pairing="quarters")
+    with pytest.raises(ops.KernelError, match="rotary_dim"):
+        ops.rope_kv_store(qkv, None, 4, 0, 16, None, i32([0, 0]), i32([0]), i32([0, 1]), rotary_dim=6 + 1)
+
+
+# ------------------------------------------------- parts that talk to the host are not recorded
+def test_generation_runs_a_model_that_cannot_be_captured(tmp_path):
+    """The toy mixer reads device values on the host in its forward, so a step with
+    it cannot be recorded as a CUDA graph; it says so (`capturable = False`) and
+    the generation loop launches its decode steps in the open instead of failing
+    in a capture."""
+    class HostDecayMixer(DecayMixer):
+        capturable = False
+    register_part("mixer", "decay")(HostDecayMixer)
+    arch = register_architecture(Architecture(("ToyDecayForCausalLM",), LlamaConfig.from_json, toy_plan))
+    try:
+        raw = dict(TINY["B"], architectures=["ToyDecayForCausalLM"], model_type="toy_decay")
+        folder = str(tmp_path / "toy")
+        lib.write_random_model(folder, raw, seed=5, dtype="float32", std=0.1, norm_std=0.05)
+        cfg, w = plain.read_model(folder)
+        model = Model.load(folder, dtype="float32", device="cuda")
+        assert not model.capturable
+        prompts = make_prompts("B", [12, 5], seed=8)
+        got = lib.generate(model, prompts, max_new_tokens=6, stop=[])          # use_graph defaults to True
+        for p, g in zip(prompts, got):
+            seq = list(p)
+            for tok in g.tokens:                                              # greedy against the plain toy
+                assert tok == int(np.argmax(plain_toy_forward(cfg, w, seq)[-1]))
+                seq.append(tok)
+    finally:
+        unregister_architecture(arch)
+        unregister_part("mixer", "decay")
