@@ -7,6 +7,12 @@ random weights.
 
     llmgen -model DIR [-prompt TEXT | -ids 1,2,3 [-ids ...] | -ids-file F] [-tokens N]
            [-temp T] [-seed S] [-stop 2,7] [-dtype bfloat16|float32] [-random-weights]
+           [-max-len N] [-slots N]
+
+``-slots`` is how many sequences run together (the cache's slots; more prompts
+than that run batch after batch) and ``-max-len`` the longest sequence, prompt
+and new tokens together, a slot holds: the cache is sized for ``slots`` sequences
+of ``max-len`` tokens, and a sequence that reaches it ends there.
 
 This library runs on the GPU only: ``-gpu`` is accepted and changes nothing,
 ``-gpu-layers`` must be 0 (all layers).  The reference's ``-turbo-quant``,
@@ -46,7 +52,10 @@ def parser() -> argparse.ArgumentParser:
     ap.add_argument("-dtype", "--dtype", default="bfloat16", choices=["bfloat16", "float32"], help="numeric path")
     ap.add_argument("-random-weights", "--random-weights", action="store_true",
                     help="write seeded random weights into the model directory if it has none")
-    ap.add_argument("-max-batch", "--max-batch", type=int, default=64, help="most prompts that run together")
+    ap.add_argument("-slots", "--slots", "-max-batch", "--max-batch", dest="slots", type=int, default=64,
+                    help="sequences that run together: the cache's slots")
+    ap.add_argument("-max-len", "--max-len", type=int, default=0,
+                    help="longest sequence (prompt + new tokens) a slot holds; 0: what the prompts need")
     for flag in ("turbo-quant", "speculative", "eager-load"):
         ap.add_argument(f"-{flag}", f"--{flag}", action="store_true", help=argparse.SUPPRESS)
     return ap
@@ -64,6 +73,9 @@ def main(argv: Optional[List[str]] = None) -> int:
         if getattr(args, flag):
             print(f"-{flag.replace('_', '-')} is not part of this library", file=sys.stderr)
             return 1
+    if args.slots <= 0 or args.max_len < 0:
+        print("-slots must be positive and -max-len non-negative", file=sys.stderr)
+        return 1
     if args.gpu_layers != 0:
         print("-gpu-layers: all layers run on the GPU; only 0 is supported", file=sys.stderr)
         return 1
@@ -118,8 +130,13 @@ def main(argv: Optional[List[str]] = None) -> int:
     torch.cuda.synchronize()
     start = time.time()
     try:
+        cache = None
+        if args.max_len:
+            slots = min(args.slots, len(prompts))
+            cache = model.new_cache(max_tokens=slots * ((args.max_len + 63) // 64 * 64), max_slots=slots)
         results = generate(model, prompts, args.tokens, temperature=args.temp, seed=args.seed,
-                           stop=args.stop, max_batch=args.max_batch)
+                           stop=args.stop, max_batch=args.slots, cache=cache,
+                           max_sequence=args.max_len or None)
     except ValueError as e:
         print(f"generate: {e}", file=sys.stderr)
         return 1

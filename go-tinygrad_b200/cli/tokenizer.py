@@ -42,7 +42,9 @@ class Tokenizer:
             if len(pair) == 2:
                 self.rank[pair] = i
         self.pieces = {i: t for t, i in self.vocab.items()}
-        self.marker = "Ġ" if any(t.startswith("Ġ") for t in self.vocab) else "▁"
+        # byte-level marker unless the vocabulary is a SentencePiece one (the reference's
+        # own test: does it hold "▁the"; loader/tokenizer/tokenizer.go:99-102)
+        self.marker = "▁" if "▁the" in self.vocab else "Ġ"
         self._bytes = _byte_table()
 
     def encode(self, text: str) -> List[int]:

@@ -43,11 +43,13 @@ def generate(model: Model, prompts: Sequence[Sequence[int]],
              max_new_tokens: Union[int, Sequence[int]] = 50, *, temperature: float = 0.0,
              seed: int = 0, stop: Optional[Sequence[int]] = None, cache: Optional[Cache] = None,
              max_batch: Optional[int] = None, max_tokens: Optional[int] = None,
-             use_graph: bool = True) -> List[GenerationResult]:
+             max_sequence: Optional[int] = None, use_graph: bool = True) -> List[GenerationResult]:
     """Generate for every prompt (lists of token ids).  `stop` defaults to the
     model's own end tokens (config.json's eos_token_id).  With no `cache` one
     is made that holds `max_tokens` tokens (default: what the largest batch
-    needs, up to `max_batch` requests at a time, default 64).  Decode steps of a
+    needs, up to `max_batch` requests at a time, default 64).  `max_sequence`
+    caps a sequence's length (prompt and new tokens) below the model's own longest
+    position: a request that reaches it ends with "capacity".  Decode steps of a
     batch whose membership does not change are replayed as a CUDA graph unless
     `use_graph` is False or the model cannot be captured (a part of it talks to
     the host in its forward, or a diagnostic hook is set: `Model.capturable`)."""
@@ -57,11 +59,19 @@ def generate(model: Model, prompts: Sequence[Sequence[int]],
         raise ValueError("max_new_tokens must be one number or one per prompt")
     stop_set = set(model.plan.stop_tokens if stop is None else stop)
     max_seq = model.plan.max_position
+    if max_sequence is not None:
+        if max_sequence <= 0:
+            raise ValueError("max_sequence must be positive")
+        max_seq = max_sequence if max_seq is None else min(max_seq, int(max_sequence))
+    if cache is not None:
+        max_seq = cache.max_sequence if max_seq is None else min(max_seq, cache.max_sequence)
     lengths = [len(p) for p in prompts]
     if cache is None:
         max_batch = max_batch or 64
         if max_tokens is None:
-            need = sorted((((l + max(0, m - 1)) + 63) // 64 * 64 for l, m in zip(lengths, limits)), reverse=True)
+            longest = max_seq if max_seq is not None else max(l + m for l, m in zip(lengths, limits))
+            need = sorted(((min(l + max(0, m - 1), longest) + 63) // 64 * 64 for l, m in zip(lengths, limits)),
+                          reverse=True)
             max_tokens = max(64, sum(need[:max_batch]))
         cache = model.new_cache(max_tokens=max_tokens, max_slots=max_batch)
     max_batch = min(max_batch or cache.n_slots, cache.n_slots)

@@ -51,6 +51,15 @@ TINY_B = {
     "eos_token_id": [5, 7],
 }
 TINY = {"A": TINY_A, "B": TINY_B}
+# The two tiny configurations exactly as the benchmark description words them (the
+# ones above are harder variants: a head size of 48, sizes that are no multiple of
+# 8, larger weights).  (configuration, seed, std of matrices, std of norm scales,
+# prompt lengths, decode steps, temperature, sampling seed)
+NAMED_TINY = {
+    "tiny-llama-A": (dict(TINY_A, max_position_embeddings=128), 0, 0.02, 0.01, (5, 17, 32), 16, 0.0, 0),
+    "tiny-llama-B": (dict(TINY_B, head_dim=32, intermediate_size=256, vocab_size=384, max_position_embeddings=256),
+                     1, 0.03, 0.02, (1, 9, 40, 64), 24, 0.8, 7),
+}
 # (seed, std of matrices, std of norm scales around 1).  The stds are far larger
 # than a trained model's so that attention is peaked and a wrong key, a wrong
 # position or a wrong page changes the logits visibly.

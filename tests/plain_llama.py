@@ -163,18 +163,20 @@ def linear(x, w):
     return (np.asarray(x, dtype=F32) @ np.asarray(w, dtype=F32).T).astype(F32)
 
 
-def causal_gqa_attention(q, k, v, n_heads, n_kv, hd, window=None):
+def causal_gqa_attention(q, k, v, n_heads, n_kv, hd, window=None, scale=None):
     """Scores (q.k)*scale with scale = float32(1/sqrt(hd)) applied after the dot,
     softmax as exp(float64(s-max)) rounded to float32 and normalised by 1/sum,
     then the weighted sum of V; head h reads KV head h // (n_heads/n_kv)
     (model/llama.go:1603-1661).  Token t sees keys 0..t (and, with `window`,
-    only the last `window` of them; the reference has no window for llama)."""
+    only the last `window` of them; the reference has no window for llama).
+    `scale` replaces 1/sqrt(hd) (the reference's function takes it as an argument:
+    gqaAttentionScale, model/attention_test.go:57)."""
     T = q.shape[0]
     q = q.reshape(T, n_heads, hd)
     k = k.reshape(T, n_kv, hd)
     v = v.reshape(T, n_kv, hd)
     group = n_heads // n_kv
-    scale = F32(1.0 / math.sqrt(hd))
+    scale = F32(1.0 / math.sqrt(hd)) if scale is None else F32(scale)
     out = np.zeros((T, n_heads, hd), dtype=F32)
     for h in range(n_heads):
         kvh = h // group

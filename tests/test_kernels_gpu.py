@@ -438,6 +438,23 @@ def test_attention_simple(dtype, n_heads, n_kv, hd, window):
                                                      else dict(rtol=2e-2, atol=2e-2)))
 
 
+def test_attention_simple_on_the_reference_vector():
+    """The reference's own attention case (model/attention_test.go:48-68: one query
+    over 17 keys, 6 heads on 2, heads of 32, sin(0.013 i) inputs, scale 0.37) through
+    the 32-bit attention kernel, against the float32 triple loop of that file, at its
+    tolerance of 2e-5."""
+    from test_plain import reference_attention_vector
+    q, k, v, want, (T, n_heads, n_kv, hd, scale) = reference_attention_vector()
+    cache = make_cache(n_kv, hd, torch.float32)
+    slot = cache.open_sequence()
+    fill_sequence(cache, 0, slot, torch.tensor(k, device=DEV).view(T, n_kv, hd), torch.tensor(v, device=DEV).view(T, n_kv, hd))
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+    out = torch.empty(1, n_heads * hd, dtype=torch.float32, device=DEV)
+    ops.attention_simple(torch.tensor(q, device=DEV).view(1, -1), out, cache.handles[0].kv, i32([0]), i32([slot]),
+                         i32([T - 1]), n_heads, scale, 0)
+    assert np.abs(out.cpu().numpy()[0] - want).max() < 2e-5
+
+
 @pytest.mark.parametrize("n_heads,n_kv,hd", [(1, 1, 64), (6, 2, 64), (5, 5, 64), (8, 1, 64), (6, 2, 128), (3, 3, 128)])
 @pytest.mark.parametrize("window", [0, 37, 64, 200])
 @pytest.mark.parametrize("lens_before,lens_new", [([0], [1]), ([0, 0, 0], [5, 129, 64]), ([0], [128]),

@@ -574,7 +574,7 @@ def test_attention_with_another_rotary_layout(model_folders, plain_models, name,
     assert np.abs(got - want).max() <= limit * max(1.0, np.abs(want).max())
     # and the layout matters: the default one gives another result
     plain_default = plain.attention_block(x_ref, positions, "model.layers.1.", cfg, plain.rope_inv_freq(cfg), w)
-    assert np.abs(plain_default - want).max() > 20 * limit * max(1.0, np.abs(want).max())
+    assert np.abs(plain_default - want).max() > 0.1 * max(1.0, np.abs(want).max())
 
 
 def test_a_rotary_layout_the_kernels_do_not_know_is_refused():

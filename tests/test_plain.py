@@ -32,26 +32,48 @@ def test_argmax_tie_goes_to_the_lowest_index():
     assert plain.argmax_first(np.array([1.0, 5.0, 5.0, 2.0], dtype=np.float32)) == 1
 
 
-def test_attention_against_a_triple_loop():
-    # the shape of model/attention_test.go:48-68: T=17, 6 heads on 2 key/value heads,
-    # head size 32, inputs sin(0.013 i), tolerance 2e-5 (scale here is 1/sqrt(32))
-    T, nh, nkv, hd = 17, 6, 2, 32
-    q = np.sin(0.013 * np.arange(T * nh * hd)).astype(np.float32).reshape(T, nh * hd)
-    k = np.sin(0.013 * np.arange(T * nkv * hd) + 1.0).astype(np.float32).reshape(T, nkv * hd)
-    v = np.sin(0.013 * np.arange(T * nkv * hd) + 2.0).astype(np.float32).reshape(T, nkv * hd)
-    got = plain.causal_gqa_attention(q, k, v, nh, nkv, hd)
-    scale = 1.0 / math.sqrt(hd)
-    for t in (0, 5, 16):
-        for h in range(nh):
-            kvh = h // (nh // nkv)
-            scores = [sum(float(q[t, h * hd + d]) * float(k[j, kvh * hd + d]) for d in range(hd)) * scale
-                      for j in range(t + 1)]
-            m = max(scores)
-            e = [math.exp(s - m) for s in scores]
-            z = sum(e)
-            for d in (0, 13, 31):
-                want = sum(e[j] / z * float(v[j, kvh * hd + d]) for j in range(t + 1))
-                assert abs(got[t, h * hd + d] - want) < 2e-5
+def reference_attention_vector():
+    """The case of model/attention_test.go:48-68: one query over seqLen = 17 keys, 6
+    heads on 2 key/value heads of 32 channels, q, k and v all benchSeq (x_i =
+    float32(sin(0.013 i)), model/cpu_hotpath_bench_test.go:12-18, each starting at
+    i = 0), scale 0.37; and what that file's own oracle, the triple loop
+    gqaAttentionScaleReference (:8-46), gives for it, restated with its float32
+    running sums."""
+    T, nh, nkv, hd, scale = 17, 6, 2, 32, np.float32(0.37)
+    seq = lambda n: np.sin(np.arange(n, dtype=np.float64) * 0.013).astype(np.float32)
+    q, k, v = seq(nh * hd), seq(T * nkv * hd), seq(T * nkv * hd)
+    kv_dim = nkv * hd
+    want = np.zeros(nh * hd, dtype=np.float32)
+    for head in range(nh):
+        kvh = head // (nh // nkv)
+        scores = np.zeros(T, dtype=np.float32)
+        for t in range(T):
+            total = np.float32(0)
+            for d in range(hd):
+                total = np.float32(total + q[head * hd + d] * k[t * kv_dim + kvh * hd + d])
+            scores[t] = total * scale
+        mx = scores.max()
+        exp_sum = np.float32(0)
+        for t in range(T):
+            scores[t] = np.float32(math.exp(float(scores[t] - mx)))
+            exp_sum = np.float32(exp_sum + scores[t])
+        scores = scores / exp_sum
+        for d in range(hd):
+            total = np.float32(0)
+            for t in range(T):
+                total = np.float32(total + scores[t] * v[t * kv_dim + kvh * hd + d])
+            want[head * hd + d] = total
+    return q, k.reshape(T, kv_dim), v.reshape(T, kv_dim), want, (T, nh, nkv, hd, float(scale))
+
+
+def test_attention_on_the_reference_vector():
+    # model/attention_test.go:48-68, tolerance 2e-5 as there
+    q, k, v, want, (T, nh, nkv, hd, scale) = reference_attention_vector()
+    queries = np.zeros((T, nh * hd), dtype=np.float32)
+    queries[T - 1] = q                                   # the query of the newest token sees all 17 keys
+    got = plain.causal_gqa_attention(queries, k, v, nh, nkv, hd, scale=scale)[T - 1]
+    assert np.abs(got - want).max() < 2e-5
+    assert np.abs(want).max() > 0.05                     # the vector is not trivially zero
 
 
 def test_attention_window_keeps_the_last_keys_only():
