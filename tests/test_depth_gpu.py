@@ -9,9 +9,12 @@ generation through the entry point.
 The tolerance in float32 does not grow with depth: the engine and the plain
 implementation differ in the order of their sums only, and the residual stream
 carries those differences forward without amplifying them (every layer's input is
-normalised); the bound is the one the shallow tests use, 5e-5 of the largest logit
-times the square root of (widest dot product / 256).  One module-scoped model
-folder per shape is written to a temporary place and read by both sides."""
+normalised).  Every comparison keeps the bound the shallow tests use (5e-5 of the
+largest logit times the square root of (widest dot product / 256)), and over all
+cuttings together the largest float32 error must stay below 5e-5 of the largest
+logit outright (measured: 1.4e-5 at 24 layers, 1.7e-5 at four layers of width
+4,096).  One module-scoped model folder per shape is written to a temporary place
+and read by both sides."""
 import math
 import os
 
@@ -25,7 +28,7 @@ from go_tinygrad_b200.config.registry import find_architecture
 from go_tinygrad_b200.engine import StepEntry, step
 from go_tinygrad_b200.parts.plan import plan_weight_specs
 from go_tinygrad_b200.weights import random_tensors, write_safetensors
-from test_real_shapes_gpu import BASE, LLAMA3, check
+from test_real_shapes_gpu import BASE, LLAMA3, check as check_logits
 
 pytestmark = pytest.mark.gpu
 
@@ -97,6 +100,13 @@ def test_every_cutting_at_depth_and_real_vocabulary(deep, dtype):
     model = lib.Model.load(folder, dtype=dtype, device="cuda")
     cache = model.new_cache(max_tokens=64 * 4, max_slots=3)
     logits = lambda entries: step(model, cache, entries).float().cpu().numpy()
+    worst = {"max": 0.0, "mean": 0.0}
+
+    def check(got, want, dtype, widest, what):
+        check_logits(got, want, dtype, widest, what)
+        scale = max(1.0, float(np.abs(want).max()))
+        err = np.abs(np.asarray(got, np.float64) - np.asarray(want, np.float64))
+        worst["max"], worst["mean"] = max(worst["max"], err.max() / scale), max(worst["mean"], err.mean() / scale)
 
     # the first request whole, logits everywhere
     r = requests[0]
@@ -130,5 +140,9 @@ def test_every_cutting_at_depth_and_real_vocabulary(deep, dtype):
     for i in live:
         cache.close_sequence(slots[i])
     assert cache.open_slots() == []
+    print(f"{name} {dtype}: largest error over all cuttings, relative to the largest logit: "
+          f"max {worst['max']:.2e}, mean {worst['mean']:.2e}")
+    if dtype == "float32":
+        assert worst["max"] <= 5e-5 and worst["mean"] <= 1e-5, worst
     from go_tinygrad_b200.kernels import ops
     assert ops.bounded_wait_failures() == 0
