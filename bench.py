@@ -12,11 +12,20 @@ at a context of 8192 tokens.  It prints ONE JSON line:
   e2e        the same through the public entry point DecodeBatch.step_host:
              every step uploads the tokens it feeds from pinned host memory and
              downloads the tokens it sampled
-  prefill    one prompt of 2,048 tokens through step(): tokens a second, and the
-             step's flops / time / the bfloat16 matrix peak
+  prefill    one prompt of 2,048 tokens through step(), its token ids handed over
+             as an array (the figure reported; `ms_from_list` is the same with a
+             Python list of ints): tokens a second, and the step's flops / time /
+             the bfloat16 matrix peak
   roofline   the decode step against HBM: bytes it has to read (every weight
              once, the cache of the live sequences) / its time / the copy peak
-  points     decode tokens a second at batch 1 and 64 (same context)
+  points     decode tokens a second at batch 1 and 64 (same context), and
+             decode_b{1,8,64}_u2048: batches whose prompts, of lengths drawn
+             uniformly from [128, 2048] (seeded), were really prefilled through
+             step() before the timed decode steps; points_ms and points_roofline
+             give every point's milliseconds per step and its fraction of the
+             HBM roofline at its own context lengths
+  cpu_baseline  for context only: the plain NumPy implementation of tests/ on the
+             host, tiny-llama-A, tokens a second
 
 Peaks come from MEASURED_PEAKS.json beside this file if present, else from the
 fallback figures of an earlier measurement on the same pool.  Inputs are larger
@@ -25,6 +34,7 @@ no flush is needed between steps.  For --gpus N > 1 it prints a line that says
 so and exits with 2: this library runs on one GPU.
 """
 import argparse
+import datetime
 import json
 import os
 import statistics
@@ -79,46 +89,62 @@ def peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons, sampled while the timed region runs."""
-    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+    """nvidia-smi clocks and throttle reasons while the timed region runs.  The
+    query polls every 20 ms from before the warm-up on; `mark()` at the start of the
+    timed region separates the samples.  The summary is taken over the timed region
+    when it is long enough to hold three samples, else over warm-up and timed region
+    together (`window` says which)."""
+    QUERY = ("timestamp,clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
              "clocks_event_reasons.sw_power_cap")
     NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
 
     def __init__(self):
         self.proc = None
+        self.marked_at = None
 
     def start(self):
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
 
+    def mark(self):
+        """The timed region begins now (samples carry nvidia-smi's own time stamps)."""
+        self.marked_at = datetime.datetime.now()
+
     def stop(self):
         if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"], "samples": 0}
+        time.sleep(0.03)                        # let the sample that covers the region's end be taken
+        ended_at = datetime.datetime.now()
         self.proc.terminate()
         try:
             out, _ = self.proc.communicate(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
             out, _ = self.proc.communicate()
-        sm, mx, reasons = [], [], set()
+        rows = []
         for line in out.splitlines():
             cells = [c.strip() for c in line.split(",")]
-            if len(cells) < 6:
+            if len(cells) < 7:
                 continue
             try:
-                sm.append(float(cells[0])); mx.append(float(cells[1]))
+                when = datetime.datetime.strptime(cells[0], "%Y/%m/%d %H:%M:%S.%f")
+                rows.append((when, float(cells[1]), float(cells[2]),
+                             [n for n, c in zip(self.NAMES, cells[3:7]) if c.lower().startswith("active")]))
             except ValueError:
                 continue
-            for name, cell in zip(self.NAMES, cells[2:6]):
-                if cell.lower().startswith("active"):
-                    reasons.add(name)
-        return {"sm_mhz": statistics.median(sm) if sm else None,
-                "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons), "samples": len(sm)}
+        timed = [r for r in rows if self.marked_at is not None and self.marked_at <= r[0] <= ended_at]
+        window = "timed region"
+        if len(timed) < 3:
+            timed, window = rows, "warm-up and timed region"
+        sm, mx = [r[1] for r in timed], [r[2] for r in timed]
+        reasons = sorted({n for r in timed for n in r[3]})
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm), "window": window, "poll_ms": 20}
 
 
 def decode_bytes(cfg, n_layers, batch, context):
@@ -237,39 +263,71 @@ def run_own(args):
         grp.storage.normal_(0.0, 1.0)
     gen = torch.Generator().manual_seed(0)
 
-    def decode_run(batch, steps, warmup, host):
-        """Tokens a second of `steps` decode steps that end at `context` tokens."""
+    kv_row = 2 * cfg["num_key_value_heads"] * cfg["head_dim"] * 2 * args.layers     # cache bytes of one token, all layers
+    weight_bytes = decode_bytes(cfg, args.layers, 0, 0)[1]
+    WARM_MS = 300.0                  # at least this much untimed device work before a timed region
+
+    def decode_run(batch, steps, warmup, host, prompts=None):
+        """`steps` timed decode steps of `batch` sequences.  Without `prompts` the
+        sequences are equal and end at `context` tokens over synthetic keys and values;
+        with them (token lists) every sequence is really prefilled through step(),
+        eight prompts a step, and decoding goes on from what the model sampled.
+        Returns tokens a second, ms per step, the clock record, launches per step and
+        the bytes a timed step reads on average."""
         slots = [cache.open_sequence() for _ in range(batch)]
-        total = warmup + steps + (6 if args.breakdown else 0)
-        for s in slots:
-            cache.reserve(s, context)
-            cache.advance(s, context - total)
-        cache.flush_tables()
+        if prompts is None:
+            starts = [context] * batch
+            est_ms = (weight_bytes + batch * context * kv_row) / (pk["hbm_gbs"] * 1e6)
+        else:
+            starts = [len(p) for p in prompts]
+            est_ms = (weight_bytes + sum(starts) * kv_row) / (pk["hbm_gbs"] * 1e6)
+        # the clocks settle under load: warm up for `warmup` steps and for WARM_MS at least
+        warm = max(warmup, int(WARM_MS / est_ms) + 1)
+        if prompts is None:
+            warm = max(warmup, min(warm, context - steps - 8))
+        total = warm + steps + (6 if args.breakdown else 0)
+        sampler = ClockSampler()
+        sampler.start()
+        if prompts is None:
+            for s in slots:
+                cache.reserve(s, context)
+                cache.advance(s, context - total)
+            cache.flush_tables()
+            tokens = torch.randint(0, vocab, (batch,), generator=gen).tolist()
+        else:
+            tokens = []
+            for lo in range(0, batch, 8):
+                part = list(zip(slots[lo:lo + 8], prompts[lo:lo + 8]))
+                logits = step(model, cache, [StepEntry(s, p, [len(p) - 1]) for s, p in part])
+                tokens += logits.argmax(dim=1).tolist()
+            for s, n in zip(slots, starts):
+                cache.reserve(s, n + total)
+            cache.flush_tables()
         db = DecodeBatch(model, cache, slots, list(range(batch)), lib.Sampler(0.0, 0),
                          use_graph=not args.eager, chained=not args.no_chain)
-        tokens = torch.randint(0, vocab, (batch,), generator=gen).tolist()
-        sampler = ClockSampler()
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         launches_before = ops.launch_count()
         if host:
             out = db.step_host(tokens, [0] * batch)      # eager: loads and configures kernels
             per_step = ops.launch_count() - launches_before
-            for i in range(1, warmup):
+            for i in range(1, warm):
                 out = db.step_host(out, [i] * batch)
             torch.cuda.synchronize()
-            sampler.start()
+            first = [cache.length(s) for s in slots]
+            sampler.mark()
             start.record()
             for i in range(steps):
-                out = db.step_host(out, [warmup + i] * batch)
+                out = db.step_host(out, [warm + i] * batch)
             stop.record()
         else:
             db.set_state(tokens, [0] * batch)
             db._launch()                                 # eager: loads and configures kernels
             per_step = ops.launch_count() - launches_before
-            for _ in range(warmup - 1):
+            for _ in range(warm - 1):
                 db.step_device()
             torch.cuda.synchronize()
-            sampler.start()
+            first = [cache.length(s) for s in slots]
+            sampler.mark()
             start.record()
             for _ in range(steps):
                 db.step_device()
@@ -277,50 +335,75 @@ def run_own(args):
         torch.cuda.synchronize()
         clocks = sampler.stop()
         ms = start.elapsed_time(stop) / steps
+        # a timed step attends over its sequences' keys: their lengths at the middle of the region
+        read_bytes = weight_bytes + sum(n + steps // 2 for n in first) * kv_row
         if args.breakdown and not host:
-            kernel_breakdown(db.step_device, 6, f"decode step, batch {batch}, context {context}", args.layers)
+            kernel_breakdown(db.step_device, 6, f"decode step, batch {batch}, mean context {sum(first) / batch:.0f}", args.layers)
         for s in slots:
             cache.close_sequence(s)
-        return batch / (ms * 1e-3), ms, clocks, per_step + 1      # +1: the kernel that feeds tokens back
+        return {"value": batch / (ms * 1e-3), "ms": ms, "clocks": clocks, "launches": per_step + 1,   # +1: the kernel that feeds tokens back
+                "bytes": read_bytes, "mean_context": sum(first) / batch + steps / 2}
+
+    def u2048_prompts(n):
+        """The decode workload as the benchmark description words it: prompts of lengths
+        uniform in [128, 2048], ids uniform in the vocabulary (seeded)."""
+        g = torch.Generator().manual_seed(1)
+        lengths = torch.randint(128, 2049, (64,), generator=g).tolist()
+        return [torch.randint(0, vocab, (k,), generator=g).tolist() for k in lengths][:n]
 
     if args.only == "decode":          # for profilers: the decode steps and nothing else
-        value, ms, _, launches = decode_run(args.batch, args.steps, args.warmup, host=False)
-        print(json.dumps({"only": "decode", "value": round(value, 1), "ms_per_step": round(ms, 4),
-                          "launches_per_step": launches, "eager": args.eager}))
+        r = decode_run(args.batch, args.steps, args.warmup, host=False,
+                       prompts=u2048_prompts(args.batch) if args.workload == "u2048" else None)
+        print(json.dumps({"only": "decode", "value": round(r["value"], 1), "ms_per_step": round(r["ms"], 4),
+                          "launches_per_step": r["launches"], "eager": args.eager}))
         return 0
     if args.only == "prefill":
         return prefill_only(args, model, cache, vocab, gen)
-    value, ms, clocks, launches = decode_run(args.batch, args.steps, args.warmup, host=False)
-    e2e_value, e2e_ms, _, _ = decode_run(args.batch, args.steps, args.warmup, host=True)
-    points = {}
-    if args.points:
-        for b in (1, 64):
-            points[f"decode_b{b}"] = round(decode_run(b, max(3, args.steps // 2), args.warmup, host=False)[0], 1)
+    main_run = decode_run(args.batch, args.steps, args.warmup, host=False)
+    e2e_run = decode_run(args.batch, args.steps, args.warmup, host=True)
+    points, points_ms, points_roofline, points_context = {}, {}, {}, {}
 
-    # prefill of one 2,048-token prompt through the step function
+    def point(name, r):
+        points[name] = round(r["value"], 1)
+        points_ms[name] = round(r["ms"], 4)
+        points_roofline[name] = round(r["bytes"] / (r["ms"] * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
+        points_context[name] = round(r["mean_context"], 1)
+    if args.points:
+        few = max(3, args.steps // 2)
+        for b in (1, 64):
+            point(f"decode_b{b}", decode_run(b, few, args.warmup, host=False))
+        prompts = u2048_prompts(64)            # really prefilled, then decoded
+        for b in (1, 8, 64):
+            point(f"decode_b{b}_u2048", decode_run(b, few if b != args.batch else args.steps, args.warmup,
+                                                   host=False, prompts=prompts[:b]))
+
+    # prefill of one 2,048-token prompt through the step function: its ids as an array
+    # (the figure reported) and as a Python list of ints (what build_context then converts)
     T = 2048
-    prompt = torch.randint(0, vocab, (T,), generator=gen).tolist()
-    times = []
-    for i in range(3 + 3):
-        slot = cache.open_sequence()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        torch.cuda.synchronize()
-        a.record()
-        step(model, cache, [StepEntry(slot, prompt, [T - 1])])
-        b.record()
-        torch.cuda.synchronize()
-        if i >= 3:
-            times.append(a.elapsed_time(b))
-        cache.close_sequence(slot)
-    pre_ms = statistics.median(times)
+    prompt = torch.randint(0, vocab, (T,), generator=gen)
+    pre = {}
+    for kind, tokens in (("array", prompt.numpy()), ("list", prompt.tolist())):
+        times = []
+        for i in range(3 + 5):
+            slot = cache.open_sequence()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            a.record()
+            step(model, cache, [StepEntry(slot, tokens, [T - 1])])
+            b.record()
+            torch.cuda.synchronize()
+            if i >= 3:
+                times.append(a.elapsed_time(b))
+            cache.close_sequence(slot)
+        pre[kind] = statistics.median(times)
+    pre_ms = pre["array"]
     flops = prefill_flops(cfg, args.layers, T)
 
-    # the timed steps attend over context - steps .. context - 1 keys: the bytes of their mean
-    total_bytes, w_bytes, kv_bytes = decode_bytes(cfg, args.layers, args.batch, context - (args.steps + 1) // 2)
-    achieved = total_bytes / (ms * 1e-3) / 1e9
+    ms = main_run["ms"]
+    achieved = main_run["bytes"] / (ms * 1e-3) / 1e9
     line = {
         "metric": f"decode tok/s at batch {args.batch}, context {context} ({shape_name} shape)",
-        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+        "value": round(main_run["value"], 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {
@@ -329,23 +412,58 @@ def run_own(args):
             "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
             "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"],
             "vocab": cfg["vocab_size"], "rope_theta": cfg["rope_theta"], "tied_head": bool(cfg["tie_word_embeddings"]),
-            "global_batch": args.batch, "seq_len": context, "context": context,
+            "global_batch": args.batch, "seq_len": context,
             "prefill_tokens": T, "parallelism": "single GPU", "l2": "inputs larger than L2",
             "peaks": pk["source"], "graph": "decode step replayed as a CUDA graph",
+            "warmup_floor_ms": WARM_MS,
         },
-        "clocks": clocks,
-        "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),
+        "clocks": main_run["clocks"],
+        "e2e": {"value": round(e2e_run["value"], 1), "unit": "tokens/s", "ms_per_step": round(e2e_run["ms"], 4),
                 "h2d_bytes_per_step": 3 * 4 * args.batch, "d2h_bytes_per_step": 4 * args.batch},
-        "gpu_launches": launches * args.steps,
+        "gpu_launches": main_run["launches"] * args.steps,
         "prefill": {"value": round(T / (pre_ms * 1e-3), 1), "tokens": T, "ms": round(pre_ms, 3),
-                    "frac": round(flops / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)},
+                    "frac": round(flops / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
+                    "tokens_given_as": "array", "ms_from_list": round(pre["list"], 3)},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"],
                      "unit": "GB/s", "frac": round(achieved / pk["hbm_gbs"], 4),
-                     "weight_gb": round(w_bytes / 1e9, 3), "cache_gb": round(kv_bytes / 1e9, 3)},
-        "points": points,
+                     "weight_gb": round(weight_bytes / 1e9, 3),
+                     "cache_gb": round((main_run["bytes"] - weight_bytes) / 1e9, 3)},
+        "points": points, "points_ms": points_ms, "points_roofline": points_roofline,
+        "points_context": points_context,
+        "cpu_baseline": cpu_baseline(),
     }
     print(json.dumps(line))
     return 0
+
+
+def cpu_baseline():
+    """For context only: the plain NumPy implementation that the tests use as their
+    oracle, on the host, at tiny-llama-A (three prompts of 5, 17 and 32 tokens, 16
+    greedy tokens each; it recomputes the whole sequence for every token).  The
+    reference itself is a Go program that cannot be built here; it reports tokens a
+    second the same way, new tokens over wall time (cmd/llmgen/main.go:121-133)."""
+    import tempfile
+    import numpy as np
+    import go_tinygrad_b200 as lib
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    try:
+        import plain_llama
+    except ImportError:
+        return {"unavailable": "tests/plain_llama.py not found"}
+    tiny = {"architectures": ["LlamaForCausalLM"], "model_type": "llama", "num_hidden_layers": 2,
+            "hidden_size": 64, "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 16,
+            "intermediate_size": 128, "vocab_size": 256, "rope_theta": 10000.0, "rms_norm_eps": 1e-5,
+            "tie_word_embeddings": True, "max_position_embeddings": 128}
+    with tempfile.TemporaryDirectory() as folder:
+        lib.write_random_model(folder, tiny, seed=0, dtype="float32", std=0.02, norm_std=0.01)
+        cfg, w = plain_llama.read_model(folder)
+    rng = np.random.default_rng(0)
+    prompts = [rng.integers(0, 256, n).tolist() for n in (5, 17, 32)]
+    t0 = time.time()
+    new = sum(len(plain_llama.generate(cfg, w, p, 16)) for p in prompts)
+    elapsed = time.time() - t0
+    return {"what": "plain NumPy implementation on the host CPU, tiny-llama-A, float32, no cache",
+            "value": round(new / elapsed, 1), "unit": "tokens/s", "tokens": new}
 
 
 def main():
@@ -364,6 +482,9 @@ def main():
                     help="skip the batch-1 and batch-64 decode points")
     ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
                     help="run one part only and print a short line (for profilers)")
+    ap.add_argument("--workload", default="context", choices=["context", "u2048"],
+                    help="with --only decode: equal sequences at --context over synthetic keys, or prompts of "
+                         "lengths uniform in [128, 2048] that are really prefilled")
     ap.add_argument("--breakdown", action="store_true",
                     help="with --only: also print, as comment lines, the time each kernel adds to a step")
     ap.add_argument("--eager", action="store_true",
