@@ -7,18 +7,19 @@
 // are its N dimension, so both operands go from shared memory to the tensor core
 // once.  The accumulator [128 features x 64 tokens] lives in TMEM.
 //
-//   kernel 1  persistent, one CTA per SM.  A unit of work is (128-row tile of W,
-//             slice of k); CTA c takes units c, c+G, c+2G ...  One thread keeps a
-//             ring of eight 24 KB stages (a 128 x 64 block of W and the 64 x 64
-//             block of X under it) full by TMA, across units; one thread issues
-//             the MMAs as the stages land; four warps move finished accumulators
-//             (two in TMEM, so a unit's epilogue runs under the next unit's MMAs)
-//             to a float workspace [slice, token, feature].
-//   kernel 2  adds the slices in order, applies the optional SwiGLU over
-//             interleaved gate/up features, converts and stores C.
-// The number of slices balances two costs: CTAs without work in the last round,
-// and the workspace traffic, which grows with every slice.  Waits are bounded as
-// in the other tcgen05 kernel; no cluster multicast is used.
+// One CTA takes one (128-row tile of W, slice of k), two CTAs to an SM.  One
+// thread keeps a ring of four 24 KB stages (a 128 x 64 block of W and the 64 x 64
+// block of X under it) full by TMA -- the weights from before the wait on the
+// kernel before, the activations after it -- one thread issues the MMAs as the
+// stages land, and four warps move the finished accumulator to shared memory.
+// The slices of a row tile are the CTAs of one thread-block cluster (up to
+// eight): after a cluster barrier every CTA adds up, for its share of the
+// tokens, the slices' partial sums in rank order through distributed shared
+// memory, applies the optional SwiGLU over interleaved gate/up features,
+// converts and stores C.  No workspace in global memory and no second kernel.
+// The number of slices is what fills the SMs (two CTAs each) without cutting k
+// below four blocks.  Waits are bounded as in the other tcgen05 kernel; no
+// cluster multicast is used.
 #include "common.cuh"
 #include <cuda.h>
 
@@ -26,10 +27,14 @@ namespace {
 constexpr int BR = 128;                       // rows of W per CTA (MMA M)
 constexpr int BT = 64;                        // tokens per CTA (MMA N)
 constexpr int BK = 64;
-constexpr int kStages = 8;                    // ring of k blocks
+constexpr int kStages = 4;                    // ring of k blocks
 constexpr int kWBytes = BR * BK * 2, kXBytes = BT * BK * 2, kBlockBytes = kWBytes + kXBytes;
 constexpr int kThreads = 192;
-constexpr int kTmemCols = 128;                // two accumulators of 64 columns
+constexpr int kTmemCols = 64;                 // one accumulator: 128 lanes x 64 columns
+constexpr int kPartFloats = BT * BR;          // the accumulator as [token][feature], after the ring is done
+constexpr int kCtasPerSm = 2;                 // what the ring's size lets an SM hold
+constexpr int kMaxSlices = 8;                 // CTAs of a cluster (the portable limit)
+static_assert(kPartFloats * 4 <= kStages * kBlockBytes, "the partial sums reuse the ring");
 constexpr int kSmemBytes = kStages * kBlockBytes + 1024 + 256;
 constexpr unsigned kSpinLimit = 1u << 22;
 
@@ -82,6 +87,10 @@ __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t a, uint64_t b, ui
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
 }
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
 __device__ __forceinline__ void tmem_ld32(uint32_t addr, uint32_t* r) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
                  "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
@@ -93,30 +102,55 @@ __device__ __forceinline__ void tmem_ld32(uint32_t addr, uint32_t* r) {
                  : "r"(addr));
 }
 
-// part[slice][token][feature] (float), feature stride N.
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+// Four consecutive floats at `addr` of this CTA's shared memory, read from the CTA of rank `rank`.
+__device__ __forceinline__ float4 remote_ld4(uint32_t addr, uint32_t rank) {
+    uint32_t ra;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(ra) : "r"(addr), "r"(rank));
+    float4 v;
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];\n"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(ra) : "memory");
+    return v;
+}
+
+// grid.x = row tiles x slices, clusters of `slices` CTAs along x: CTA rank r of a
+// cluster takes k blocks [r * kb_per, (r + 1) * kb_per) of its row tile.
+template <typename OutT>
 __global__ void __launch_bounds__(kThreads)
-swapab_partial_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-                      float* __restrict__ part, int M, int N, int K, int k_slice, int slices) {
+swapab_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+              OutT* __restrict__ C, int ldc, int M, int N, int K, int kb_per, int slices, int epi) {
     extern __shared__ unsigned char smem_raw[];
     const uint32_t base = (smem_addr(smem_raw) + 1023u) & ~1023u;
     unsigned char* aligned = smem_raw + (base - smem_addr(smem_raw));
-    const uint32_t bars = base + kStages * kBlockBytes;      // full[kStages], empty[kStages], acc_full[2], acc_empty[2]
+    const uint32_t bars = base + kStages * kBlockBytes;      // full[kStages], empty[kStages], acc_full
     auto full_bar = [&](int s) { return bars + 8u * s; };
     auto empty_bar = [&](int s) { return bars + 8u * (kStages + s); };
-    auto acc_full = [&](int a) { return bars + 8u * (2 * kStages + a); };
-    auto acc_empty = [&](int a) { return bars + 8u * (2 * kStages + 2 + a); };
+    const uint32_t acc_full = bars + 8u * (2 * kStages);
     uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(aligned + kStages * kBlockBytes + 192);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(aligned + kStages * kBlockBytes + 200);
+    float* part = reinterpret_cast<float*>(aligned);         // [token][feature], once the ring has been read
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n_units = ((N + BR - 1) / BR) * slices;
-    auto unit_k = [&](int unit, int* k_begin) {              // k blocks of the unit's slice
-        *k_begin = (unit % slices) * k_slice;
-        return (min(K, *k_begin + k_slice) - *k_begin + BK - 1) / BK;
-    };
+    const uint32_t rank = slices > 1 ? cluster_rank() : 0u;
+    const int n0 = (blockIdx.x / slices) * BR;
+    const int kb_total = (K + BK - 1) / BK;
+    const int kb_begin = (int)rank * kb_per;
+    const int n_kb = max(0, min(kb_total, kb_begin + kb_per) - kb_begin);
+    // CTAs of different row tiles walk the same k blocks of X: each starts at another
+    // block, so that they do not all ask the L2 for the same lines at the same time
+    const int kb_rot = n_kb > 0 ? (int)((blockIdx.x / slices) * 5u % (unsigned)n_kb) : 0;
+    auto k_of = [&](int kb) { int j = kb + kb_rot; if (j >= n_kb) j -= n_kb; return (kb_begin + j) * BK; };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-        for (int a = 0; a < 2; ++a) { mbar_init(acc_full(a), 1); mbar_init(acc_empty(a), 4); }
+        mbar_init(acc_full, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::);
     }
@@ -129,135 +163,131 @@ swapab_partial_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::);
     const uint32_t tmem_base = *tmem_holder;
+    chain_release();      // the kernel after this one may set itself up; it waits for this one before it reads
 
     if (warp == 4) {
         // ------------------------------------------------------------ producer
         if (lane == 0) {
             // The first ring fill: the weights depend on no earlier kernel, so their
             // copies start before the wait; the activations follow it.
-            uint32_t it = 0;
-            bool waited = false, ok = true;
-            int held[kStages][2];                            // (k, stage) of W copies whose X copy is still owed
-            int n_held = 0;
-            for (int unit = blockIdx.x; unit < n_units && ok; unit += gridDim.x) {
-                int k_begin;
-                const int n_kb = unit_k(unit, &k_begin);
-                const int n0 = (unit / slices) * BR;
-                for (int kb = 0; kb < n_kb; ++kb, ++it) {
-                    const int s = it % kStages;
-                    if (!waited && it == kStages) {          // the ring is full of weights: now the activations
-                        chain_wait();
-                        for (int h = 0; h < n_held; ++h)
-                            tma_load_2d(base + held[h][1] * kBlockBytes + kWBytes, &map_x, held[h][0], 0, full_bar(held[h][1]));
-                        waited = true;
-                    }
-                    if (!mbar_wait(empty_bar(s), ((it / kStages) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
-                    mbar_expect_tx(full_bar(s), kBlockBytes);
-                    tma_load_2d(base + s * kBlockBytes, &map_w, k_begin + kb * BK, n0, full_bar(s));
-                    if (waited) {
-                        tma_load_2d(base + s * kBlockBytes + kWBytes, &map_x, k_begin + kb * BK, 0, full_bar(s));
-                    } else {
-                        held[n_held][0] = k_begin + kb * BK;
-                        held[n_held][1] = s;
-                        ++n_held;
-                    }
-                }
+            const int first = min(n_kb, kStages);
+            for (int kb = 0; kb < first; ++kb) {
+                mbar_expect_tx(full_bar(kb), kBlockBytes);
+                tma_load_2d(base + kb * kBlockBytes, &map_w, k_of(kb), n0, full_bar(kb));
             }
-            if (!waited) {                                   // fewer blocks than stages in all
-                chain_wait();
-                for (int h = 0; h < n_held; ++h)
-                    tma_load_2d(base + held[h][1] * kBlockBytes + kWBytes, &map_x, held[h][0], 0, full_bar(held[h][1]));
+            chain_wait();
+            for (int kb = 0; kb < first; ++kb)
+                tma_load_2d(base + kb * kBlockBytes + kWBytes, &map_x, k_of(kb), 0, full_bar(kb));
+            for (int kb = first; kb < n_kb; ++kb) {
+                const int s = kb % kStages;
+                if (!mbar_wait(empty_bar(s), ((kb / kStages) & 1u) ^ 1u, abort_flag)) break;
+                mbar_expect_tx(full_bar(s), kBlockBytes);
+                tma_load_2d(base + s * kBlockBytes, &map_w, k_of(kb), n0, full_bar(s));
+                tma_load_2d(base + s * kBlockBytes + kWBytes, &map_x, k_of(kb), 0, full_bar(s));
             }
         }
     } else if (warp == 5) {
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             const uint32_t idesc = umma_idesc(BR, BT);
-            uint32_t it = 0, done = 0;
             bool ok = true;
-            for (int unit = blockIdx.x; unit < n_units && ok; unit += gridDim.x, ++done) {
-                int k_begin;
-                const int n_kb = unit_k(unit, &k_begin);
-                const int a = done & 1;
-                if (!mbar_wait(acc_empty(a), ((done >> 1) & 1u) ^ 1u, abort_flag)) break;
+            for (int kb = 0; kb < n_kb; ++kb) {
+                const int s = kb % kStages;
+                if (!mbar_wait(full_bar(s), (kb / kStages) & 1u, abort_flag)) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::);
-                for (int kb = 0; kb < n_kb; ++kb, ++it) {
-                    const int s = it % kStages;
-                    if (!mbar_wait(full_bar(s), (it / kStages) & 1u, abort_flag)) { ok = false; break; }
-                    asm volatile("tcgen05.fence::after_thread_sync;\n" ::);
-                    const uint64_t da = umma_desc(base + s * kBlockBytes);
-                    const uint64_t db = umma_desc(base + s * kBlockBytes + kWBytes);
+                const uint64_t da = umma_desc(base + s * kBlockBytes);
+                const uint64_t db = umma_desc(base + s * kBlockBytes + kWBytes);
 #pragma unroll
-                    for (int j = 0; j < BK / 16; ++j)
-                        umma(tmem_base + 64 * a, da + 2 * j, db + 2 * j, idesc, (kb > 0 || j > 0) ? 1u : 0u);
-                    umma_commit(empty_bar(s));               // the stage is free once these MMAs have read it
-                }
-                if (ok) umma_commit(acc_full(a));
+                for (int j = 0; j < BK / 16; ++j)
+                    umma(tmem_base, da + 2 * j, db + 2 * j, idesc, (kb > 0 || j > 0) ? 1u : 0u);
+                umma_commit(empty_bar(s));                   // the stage is free once these MMAs have read it
             }
+            if (ok && n_kb > 0) umma_commit(acc_full);       // arrives when every MMA above has completed
+            else mbar_arrive(acc_full);                      // nothing to wait for (or given up): let the epilogue go on
         }
     } else {
-        // ------------------------------------------------------------ epilogue: TMEM -> workspace
-        chain_wait();                                       // the workspace may still be read by an earlier kernel
-        uint32_t done = 0;
-        for (int unit = blockIdx.x; unit < n_units; unit += gridDim.x, ++done) {
-            const int a = done & 1;
-            const bool ready = mbar_wait(acc_full(a), (done >> 1) & 1u, abort_flag);
-            if (!__all_sync(0xffffffffu, ready)) break;
-            asm volatile("tcgen05.fence::after_thread_sync;\n" ::);
-            const int feature = (unit / slices) * BR + warp * 32 + lane;
-            float* dst = part + (size_t)(unit % slices) * M * N + feature;
+        // ------------------------------------------------------------ accumulator -> shared memory, [token][feature]
+        chain_wait();
+        const bool ready = mbar_wait(acc_full, 0u, abort_flag);
+        const bool use = __all_sync(0xffffffffu, ready) && n_kb > 0 && !*abort_flag;
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::);
+        const int feature = warp * 32 + lane;
 #pragma unroll 1
-            for (int c = 0; c < BT / 32; ++c) {
-                uint32_t v[32];
-                tmem_ld32(tmem_base + 64 * a + ((uint32_t)(warp * 32) << 16) + (uint32_t)(c * 32), v);
+        for (int c = 0; c < BT / 32; ++c) {
+            uint32_t v[32];
+            if (use) {
+                tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(c * 32), v);
                 asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-                if (feature < N) {
+            } else {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const int token = c * 32 + i;
-                        if (token < M) dst[(size_t)token * N] = __uint_as_float(v[i]);   // a warp writes 32 consecutive features
+                for (int i = 0; i < 32; ++i) v[i] = 0u;      // a slice without k blocks adds nothing
+            }
+#pragma unroll
+            for (int i = 0; i < 32; ++i) part[(c * 32 + i) * BR + feature] = __uint_as_float(v[i]);
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;\n" ::);
+    }
+    // Every thread of every CTA of the cluster comes here, whatever its role did.
+    __syncthreads();
+    if (slices > 1) cluster_sync_all();                      // all slices' partial sums are in place
+
+    if (warp < 4) {
+        // this CTA's share of the tokens: the slices added in rank order, then the epilogue
+        const int per = (BT + slices - 1) / slices;
+        const int t_end = min(min(BT, M), (int)(rank + 1) * per);
+        const uint32_t part_addr = smem_addr(part);
+        const bool vec_ok = (ldc % 4 == 0) && (((uintptr_t)C) % 16 == 0);
+        for (int t = (int)rank * per + warp; t < t_end; t += 4) {
+            float4 acc;
+            if (slices > 1) {
+                acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int r = 0; r < slices; ++r) {
+                    const float4 v = remote_ld4(part_addr + (uint32_t)(t * BR + lane * 4) * 4u, (uint32_t)r);
+                    acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+                }
+            } else {
+                acc = *reinterpret_cast<const float4*>(part + t * BR + lane * 4);
+            }
+            if (!epi) {
+                const int f = n0 + lane * 4;
+                OutT* dst = C + (size_t)t * ldc + f;
+                if (vec_ok && f + 3 < N) {
+                    if constexpr (sizeof(OutT) == 4) {
+                        *reinterpret_cast<float4*>(dst) = acc;
+                    } else {
+                        uint2 o;
+                        o.x = pack_bf16x2(acc.x, acc.y);
+                        o.y = pack_bf16x2(acc.z, acc.w);
+                        *reinterpret_cast<uint2*>(dst) = o;
                     }
+                } else {
+                    const float a[4] = {acc.x, acc.y, acc.z, acc.w};
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        if (f + i < N) dst[i] = from_f32<OutT>(a[i]);
+                }
+            } else {
+                // features come in blocks of 8 gate + 8 up: lane l holds 4 of one half of block l / 4;
+                // the matching half sits two lanes further (gate in lanes 4b, 4b+1; up in 4b+2, 4b+3)
+                const float4 other = make_float4(__shfl_xor_sync(0xffffffffu, acc.x, 2), __shfl_xor_sync(0xffffffffu, acc.y, 2),
+                                                 __shfl_xor_sync(0xffffffffu, acc.z, 2), __shfl_xor_sync(0xffffffffu, acc.w, 2));
+                if ((lane & 2) == 0) {
+                    const float g[4] = {acc.x, acc.y, acc.z, acc.w}, u[4] = {other.x, other.y, other.z, other.w};
+                    const int j = (n0 >> 1) + (lane >> 2) * 8 + (lane & 1) * 4;     // first of this lane's four outputs
+                    OutT* dst = C + (size_t)t * ldc + j;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        if (j + i < (N >> 1)) dst[i] = from_f32<OutT>(g[i] / (1.0f + expf(-g[i])) * u[i]);
                 }
             }
-            asm volatile("tcgen05.fence::before_thread_sync;\n" ::);
-            __syncwarp();
-            if (lane == 0) mbar_arrive(acc_empty(a));
         }
     }
-    chain_release();
+    if (slices > 1) cluster_sync_all();                      // nobody leaves while its partial sums are being read
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::);
     __syncthreads();
     if (warp == 5) {
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::);
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(kTmemCols));
-    }
-}
-
-// C[m][n] = sum over slices, in order; epi 1: SwiGLU over blocks of 8 gate + 8 up features.
-template <typename OutT>
-__global__ void swapab_reduce_kernel(const float* __restrict__ part, OutT* __restrict__ C, int ldc,
-                                     int M, int N, int slices, int epi) {
-    chain_wait();
-    chain_release();
-    const int n_out = epi ? N / 2 : N;
-    const size_t total = (size_t)M * n_out;
-    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
-         idx += (size_t)gridDim.x * blockDim.x) {
-        const int m = (int)(idx / n_out), j = (int)(idx - (size_t)m * n_out);
-        if (!epi) {
-            float s = 0.f;
-            for (int sl = 0; sl < slices; ++sl) s += part[((size_t)sl * M + m) * N + j];
-            C[(size_t)m * ldc + j] = from_f32<OutT>(s);
-        } else {
-            const int col = (j >> 3) * 16 + (j & 7);     // gate feature j; its up feature is 8 further
-            float g = 0.f, u = 0.f;
-            for (int sl = 0; sl < slices; ++sl) {
-                const float* row = part + ((size_t)sl * M + m) * N;
-                g += row[col];
-                u += row[col + 8];
-            }
-            C[(size_t)m * ldc + j] = from_f32<OutT>(g / (1.0f + expf(-g)) * u);
-        }
     }
 }
 
@@ -288,27 +318,49 @@ int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int ld, int box
     return r == CUDA_SUCCESS ? 0 : kErrBadArgument;
 }
 
-// Slices of k per row tile.  More slices fill the last round of the persistent
-// grid better but add workspace traffic (every slice writes and re-reads M x 128
-// floats per tile against 128 x k_slice weights): take the count with the least
-// estimated time.
-void plan(int M, int N, int K, int* slices, int* k_slice) {
-    const int row_tiles = (N + BR - 1) / BR, k_blocks = (K + BK - 1) / BK, grid = 148;
-    int best = 1;
-    double best_cost = 1e30;
-    for (int s = 1; s <= k_blocks && s <= 64; ++s) {
-        const int per = (k_blocks + s - 1) / s;                 // k blocks per slice
-        const int real = (k_blocks + per - 1) / per;            // slices that exist with this size
-        if (real != s) continue;
-        const long long units = (long long)row_tiles * s;
-        const long long rounds = (units + grid - 1) / grid;
-        const double weights = (double)per * BK * 2 * BR, spill = 2.0 * M * 4 * BR;   // bytes per unit
-        const double cost = (double)rounds * (weights + spill + 4096.0);              // + a fixed cost per unit
-        if (cost < best_cost) { best_cost = cost; best = s; }
+// Slices of k per row tile: as many as fill the device's CTA slots (two to an SM)
+// without cutting k below four blocks a slice, at most eight (one cluster), and
+// such that every slice has blocks.
+void plan(int N, int K, int sms, int* slices, int* kb_per) {
+    const int row_tiles = (N + BR - 1) / BR, k_blocks = (K + BK - 1) / BK;
+    int s = (kCtasPerSm * sms) / row_tiles;
+    if (s > kMaxSlices) s = kMaxSlices;
+    if (s > k_blocks / 4) s = k_blocks / 4;
+    if (s < 1) s = 1;
+    while (s & (s - 1)) s &= s - 1;                           // a power of two: clusters of 3, 5, 6 or 7 CTAs pack the
+                                                              // processor clusters unevenly and run in two waves
+    int per = (k_blocks + s - 1) / s;
+    s = (k_blocks + per - 1) / per;                           // slices that exist with this size
+    *slices = s;
+    *kb_per = per;
+}
+
+int device_sms() {
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0, n = 0;
+        if (cudaGetDevice(&dev) == cudaSuccess &&
+            cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0)
+            sms = n;
+        else
+            sms = 148;
     }
-    const int per = (k_blocks + best - 1) / best;
-    *k_slice = per * BK;
-    *slices = best;
+    return sms;
+}
+
+template <typename OutT>
+int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, OutT* C, int ldc, int M, int N, int K,
+           int kb_per, int slices, int epilogue, cudaStream_t stream) {
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(swapab_kernel<OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    const long long ctas = (long long)((N + BR - 1) / BR) * slices;
+    if (ctas > 0x7fffffff) return kErrUnsupported;
+    return launch_chained_cluster(swapab_kernel<OutT>, dim3((unsigned)ctas), dim3(kThreads), slices, (size_t)kSmemBytes,
+                                  stream, map_w, map_x, C, ldc, M, N, K, kb_per, slices, epilogue);
 }
 }  // namespace
 
@@ -318,53 +370,30 @@ GTG_API int gtg_gemm_bf16_swapab_status() {
     return v;
 }
 
-// Floats of workspace a call needs.
+// Floats of workspace a call needs: none, the slices meet in shared memory.
 GTG_API long long gtg_gemm_bf16_swapab_scratch_floats(int M, int N, int K) {
-    int slices, k_slice;
-    plan(M, N, K, &slices, &k_slice);
-    return (long long)slices * M * N;
+    (void)M; (void)N; (void)K;
+    return 0;
 }
 
-// M <= 64.  epilogue as in gtg_gemm_bf16_tcgen05.
+// M <= 64.  epilogue as in gtg_gemm_bf16_tcgen05.  `scratch` is not used and may be null.
 GTG_API int gtg_gemm_bf16_swapab(const void* X, int ldx, const void* W, int ldw, void* C, int ldc,
                                  int out_f32, int M, int N, int K, int epilogue, float* scratch,
                                  cudaStream_t stream) {
+    (void)scratch;
     if (M <= 0 || N <= 0) return 0;
     if (M > BT) return kErrUnsupported;
     if (epilogue != 0 && epilogue != 1) return kErrBadArgument;
     if (epilogue == 1 && N % 16 != 0) return kErrUnsupported;
-    if (K <= 0 || ldx < K || ldw < K || ldc < (epilogue ? N / 2 : N) || scratch == nullptr) return kErrBadArgument;
+    if (K <= 0 || ldx < K || ldw < K || ldc < (epilogue ? N / 2 : N)) return kErrBadArgument;
     if (K % 8 || ldx % 8 || ldw % 8 || ((uintptr_t)X % 16) || ((uintptr_t)W % 16)) return kErrUnsupported;
-    int slices, k_slice;
-    plan(M, N, K, &slices, &k_slice);
+    int slices, kb_per;
+    plan(N, K, device_sms(), &slices, &kb_per);
     CUtensorMap map_w, map_x;
     int st = make_map(&map_w, W, N, K, ldw, BR);
     if (st != 0) return st;
     st = make_map(&map_x, X, M, K, ldx, BT);
     if (st != 0) return st;
-    static bool configured = false;
-    static int sms = 148;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(swapab_partial_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-        if (e != cudaSuccess) return (int)e;
-        int dev = 0, n = 0;
-        if (cudaGetDevice(&dev) == cudaSuccess &&
-            cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0)
-            sms = n;
-        configured = true;
-    }
-    const long long units = (long long)((N + BR - 1) / BR) * slices;
-    if (units > 0x7fffffff) return kErrUnsupported;
-    const int grid = (int)(units < sms ? units : sms);
-    st = launch_chained(swapab_partial_kernel, dim3(grid), dim3(kThreads), (size_t)kSmemBytes, stream,
-                        map_w, map_x, scratch, M, N, K, k_slice, slices);
-    if (st != 0) return st;
-    const int n_out = epilogue ? N / 2 : N;
-    int blocks = (int)(((long long)M * n_out + 255) / 256);
-    if (blocks > 148 * 8) blocks = 148 * 8;
-    if (out_f32)
-        return launch_chained(swapab_reduce_kernel<float>, dim3(blocks), dim3(256), 0, stream,
-                              (const float*)scratch, (float*)C, ldc, M, N, slices, epilogue);
-    return launch_chained(swapab_reduce_kernel<bf16>, dim3(blocks), dim3(256), 0, stream,
-                          (const float*)scratch, (bf16*)C, ldc, M, N, slices, epilogue);
+    if (out_f32) return launch<float>(map_w, map_x, (float*)C, ldc, M, N, K, kb_per, slices, epilogue, stream);
+    return launch<bf16>(map_w, map_x, (bf16*)C, ldc, M, N, K, kb_per, slices, epilogue, stream);
 }

@@ -270,15 +270,25 @@ def test_linear_bfloat16(out_dtype, kind, M, N, K):
     assert ops.bounded_wait_failures() == 0
 
 
-@pytest.mark.parametrize("M,N,K", [(40, 38000, 136), (64, 19100, 520), (17, 300, 16384)])
-def test_linear_swapab_many_units_per_block(M, N, K):
-    """More (row tile, slice) units than SMs: every persistent block walks several
-    units, its ring wraps and its two accumulators alternate."""
+@pytest.mark.parametrize("M,N,K", [(40, 38000, 136), (64, 19100, 520), (17, 300, 16384), (64, 2048, 2048), (33, 6144, 2048),
+                                   (64, 2048, 8192), (20, 16384, 2048), (64, 130, 520), (50, 4096, 14336)])
+def test_linear_swapab_slices_meet_in_a_cluster(M, N, K):
+    """One CTA per (128-row tile, slice of k): more CTAs than the device holds at once
+    (several waves), clusters of two, four and eight slices whose partial sums meet
+    through distributed shared memory, a row tile that is not full, and the same
+    bits on a second run (the slices are added in rank order)."""
     x, w = rnd(M, K, dtype=torch.bfloat16, seed=1), rnd(N, K, dtype=torch.bfloat16, seed=2)
     out = torch.empty(M, N, dtype=torch.float32, device=DEV)
     ops.linear(x, w, out, kind="swapab")
     want = (x.double() @ w.double().T).float()
     torch.testing.assert_close(out, want, rtol=1e-4, atol=2e-3 * math.sqrt(K / 64))
+    again = torch.full_like(out, float("nan"))
+    ops.linear(x, w, again, kind="swapab")
+    assert torch.equal(out, again)
+    wide = torch.zeros(M, N + 24, dtype=torch.bfloat16, device=DEV)          # an output that is a column slice
+    ops.linear(x, w, wide[:, 10:N + 10], kind="swapab")
+    torch.testing.assert_close(wide[:, 10:N + 10].float(), want.to(torch.bfloat16).float(), rtol=1.6e-2, atol=1e-2 * math.sqrt(K / 64))
+    assert float(wide[:, :10].abs().sum()) == 0 and float(wide[:, N + 10:].abs().sum()) == 0
     assert ops.bounded_wait_failures() == 0
 
 
