@@ -275,6 +275,8 @@ def run_own(args):
         Returns tokens a second, ms per step, the clock record, launches per step and
         the bytes a timed step reads on average."""
         slots = [cache.open_sequence() for _ in range(batch)]
+        if prompts is not None:
+            prompts = sorted(prompts, key=len, reverse=True)     # longest first, as the generation loop orders a batch
         if prompts is None:
             starts = [context] * batch
             est_ms = (weight_bytes + batch * context * kv_row) / (pk["hbm_gbs"] * 1e6)

@@ -85,7 +85,11 @@ def generate(model: Model, prompts: Sequence[Sequence[int]],
         seqs = [SequenceProgress(i, lengths[i], limits[i], stop_set, max_seq) for i in batch]
         for s in seqs:
             s.start()
-        running = live(seqs)
+        # The longest sequences come first in the batch, in the prompt step and in every
+        # decode step: kernels hand out their blocks sequence by sequence in batch
+        # order, and the long ones should not be the last to start.  Sequences grow
+        # together, so the order holds while the batch lives.
+        running = sorted(live(seqs), key=lambda s: -s.prompt_length)
         slots = {s.request: cache.open_sequence() for s in running}
         try:
             if running:

@@ -3,7 +3,8 @@ attention over 8,192 keys per sequence at the split counts the library picks for
 1, 8 and 64 sequences; prompt attention and the projection that rotates and stores
 in its epilogue at 2,048 and 8,192 tokens; decode steps of 17, 33 and 64 sequences
 through the engine at the layer shapes of the three models (the tensor-core product
-with swapped operands, its reduce kernel and fused SwiGLU); and a decode batch
+with swapped operands, whose slices of k meet in a cluster, and its fused SwiGLU);
+and a decode batch
 replayed as a CUDA graph against the same steps launched in the open."""
 import math
 
