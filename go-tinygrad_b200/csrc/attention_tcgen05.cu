@@ -36,6 +36,17 @@ constexpr int kThreads = 192;
 constexpr int kBlockBytes = kPageTokens * 64 * 2;   // 64 tokens x 64 channels: one swizzled block of a page
 constexpr int kTmemCols = 256;
 constexpr unsigned kSpinLimit = 1u << 22;
+// The kernels of this library exist twice: as they run, and (kTest) in the form the
+// test of the give-up path launches, whose waits poll a thousand times instead of
+// millions and whose asynchronous copies are not issued at all, so that every
+// barrier it waits on never completes.  The second form is the first form's code
+// with these two constants changed; see the test hook at the end of this file.
+template <bool kTest> struct Waits {
+    static constexpr unsigned kLimit = kTest ? 1024u : kSpinLimit;
+    static constexpr bool kSkipCopies = kTest;
+};
+static bool g_test_waits = false;       // set by the test hook: launches take the kTest form
+
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRaiseBy = 8.0f;        // the running maximum follows only jumps above 2^8
 
@@ -68,8 +79,9 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
 }
+template <bool kTest>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-    for (unsigned i = 0; i < kSpinLimit; ++i) {
+    for (unsigned i = 0; i < Waits<kTest>::kLimit; ++i) {
         uint32_t done;
         asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
                      "selp.u32 %0, 1, 0, p;\n}\n" : "=r"(done) : "r"(bar), "r"(parity) : "memory");
@@ -80,7 +92,9 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     atomicExch(&g_status, 1);
     return false;
 }
+template <bool kTest>
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+    if (Waits<kTest>::kSkipCopies) return;
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
                  ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
 }
@@ -169,7 +183,7 @@ __device__ __forceinline__ float exp2_in_order(float x) {
 // grid: (query heads, sequences, query tiles), the longest tiles first.
 // A stage of the ring: the step's keys, then its values, each as HD/64 blocks of
 // [BK tokens][64 channels] (a block holds the step's pages one after the other).
-template <int HD>
+template <int HD, bool kTest>
 __global__ void __launch_bounds__(kThreads, 2)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
                             bf16* __restrict__ out, int ldo,
@@ -234,10 +248,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         if (lane == 0) {
             mbar_expect_tx(q_full, S::kQBytes);
             for (int hh = 0; hh < S::kHalves; ++hh)
-                tma_load_2d(base + hh * (BQ * 128), &map_q, h * HD + 64 * hh, q_begin + tile * BQ, q_full);
+                tma_load_2d<kTest>(base + hh * (BQ * 128), &map_q, h * HD + 64 * hh, q_begin + tile * BQ, q_full);
             for (int i = 0; i < n_steps; ++i) {
                 const int s = i % S::kStages;
-                if (!mbar_wait(kv_empty(s), (((uint32_t)i / S::kStages) & 1u) ^ 1u, abort_flag)) break;
+                if (!mbar_wait<kTest>(kv_empty(s), (((uint32_t)i / S::kStages) & 1u) ^ 1u, abort_flag)) break;
                 const uint32_t dst = base + S::kOffKV + s * S::kStageBytes;
                 mbar_expect_tx(kv_full(s), S::kStageBytes);
                 for (int pg = 0; pg < S::kPages; ++pg) {
@@ -247,7 +261,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     for (int kv = 0; kv < 2; ++kv) {
                         const int row = ((page * 2 + kv) * n_kv + kvh) * kPageTokens;
                         for (int hh = 0; hh < S::kHalves; ++hh)
-                            tma_load_2d(dst + kv * S::kTileBytes + (hh * S::kPages + pg) * kBlockBytes, &map_kv,
+                            tma_load_2d<kTest>(dst + kv * S::kTileBytes + (hh * S::kPages + pg) * kBlockBytes, &map_kv,
                                         64 * hh, row, kv_full(s));
                     }
                 }
@@ -258,10 +272,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         if (lane == 0) {
             const uint32_t idesc_s = umma_idesc(BQ, BK, 0);               // S[128 x BK keys], key pages K-major
             const uint32_t idesc_pv = umma_idesc(BQ, HD, 1);              // O[128 x HD channels], value pages MN-major
-            bool ok = mbar_wait(q_full, 0, abort_flag);
+            bool ok = mbar_wait<kTest>(q_full, 0, abort_flag);
             auto issue_s = [&](int i) {
                 const int s = i % S::kStages;
-                if (!mbar_wait(kv_full(s), ((uint32_t)i / S::kStages) & 1u, abort_flag)) return false;
+                if (!mbar_wait<kTest>(kv_full(s), ((uint32_t)i / S::kStages) & 1u, abort_flag)) return false;
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::);
                 const uint32_t kbase = base + S::kOffKV + s * S::kStageBytes;
 #pragma unroll
@@ -276,10 +290,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             if (ok) ok = issue_s(0);
             for (int i = 0; i < n_steps && ok; ++i) {
                 if (i + 1 < n_steps) {                                     // S_i is in registers: the tile takes S_{i+1}
-                    ok = mbar_wait(s_free, (uint32_t)i & 1u, abort_flag) && issue_s(i + 1);
+                    ok = mbar_wait<kTest>(s_free, (uint32_t)i & 1u, abort_flag) && issue_s(i + 1);
                     if (!ok) break;
                 }
-                ok = mbar_wait(p_full, (uint32_t)i & 1u, abort_flag);     // P_i is in TMEM, O rescaled if it had to be
+                ok = mbar_wait<kTest>(p_full, (uint32_t)i & 1u, abort_flag);     // P_i is in TMEM, O rescaled if it had to be
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::);
                 const int s = i % S::kStages;
@@ -303,7 +317,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         bool ok = true;
         for (int i = 0; i < n_steps; ++i) {
             const int key0 = (j_lo + S::kPages * i) * kPageTokens;   // position of the step's first key
-            ok = __all_sync(full, mbar_wait(s_full, (uint32_t)i & 1u, abort_flag));
+            ok = __all_sync(full, mbar_wait<kTest>(s_full, (uint32_t)i & 1u, abort_flag));
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::);
 #pragma unroll
@@ -337,7 +351,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 const bool raise = m_page > m_run + kRaiseBy;    // also: the first visible key of a row
                 if (__any_sync(full, raise)) {
                     // O may only be touched between products (rare after the first steps)
-                    ok = __all_sync(full, mbar_wait(pv_done, (uint32_t)(i - 1) & 1u, abort_flag));
+                    ok = __all_sync(full, mbar_wait<kTest>(pv_done, (uint32_t)(i - 1) & 1u, abort_flag));
                     if (!ok) break;
                     float corr = 1.0f;
                     if (raise) {
@@ -380,7 +394,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             // P_i goes where P_{i-1} was: its product must have read it (it has, long ago,
             // unless the tensor pipe is the slower side)
             if (i > 0) {
-                ok = __all_sync(full, mbar_wait(pv_done, (uint32_t)(i - 1) & 1u, abort_flag));
+                ok = __all_sync(full, mbar_wait<kTest>(pv_done, (uint32_t)(i - 1) & 1u, abort_flag));
                 if (!ok) break;
             }
 #pragma unroll
@@ -391,7 +405,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             __syncwarp();
             if (lane == 0) mbar_arrive(p_full);
         }
-        if (ok) ok = __all_sync(full, mbar_wait(pv_done, (uint32_t)(n_steps - 1) & 1u, abort_flag));
+        if (ok) ok = __all_sync(full, mbar_wait<kTest>(pv_done, (uint32_t)(n_steps - 1) & 1u, abort_flag));
         if (ok) {
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::);
             const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
@@ -452,19 +466,19 @@ int make_map(CUtensorMap* map, const void* ptr, long long rows, int cols, long l
     return r == CUDA_SUCCESS ? 0 : kErrBadArgument;
 }
 
-template <int HD>
+template <int HD, bool kTest>
 int launch(const CUtensorMap& map_q, const CUtensorMap& map_kv, bf16* out, int ldo, const int* block_table,
            int table_stride, const int* cu_seqlens, const int* slots, const int* start_pos, int B, int max_q_len,
            int n_heads, int n_kv, float scale, int window, cudaStream_t stream) {
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<HD, kTest>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              Shape<HD>::kSmemBytes);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
     dim3 grid(n_heads, B, (max_q_len + BQ - 1) / BQ);
-    return launch_chained(attention_prefill_tc_kernel<HD>, grid, dim3(kThreads), (size_t)Shape<HD>::kSmemBytes, stream,
+    return launch_chained(attention_prefill_tc_kernel<HD, kTest>, grid, dim3(kThreads), (size_t)Shape<HD>::kSmemBytes, stream,
                           map_q, map_kv, out, ldo, block_table, table_stride, cu_seqlens, slots, start_pos,
                           n_heads, n_kv, scale, window);
 }
@@ -502,9 +516,24 @@ GTG_API int gtg_attention_prefill_tcgen05(const void* q, int ldq, int n_tokens, 
     if (st != 0) return st;
     st = make_map(&map_kv, kc, (long long)n_pages * kv_rows, hd, hd, kPageTokens);
     if (st != 0) return st;
-    if (hd == 64)
-        return launch<64>(map_q, map_kv, (bf16*)out, ldo, block_table, table_stride, cu_seqlens, slots, start_pos,
-                          B, max_q_len, n_heads, n_kv, scale, window, stream);
-    return launch<128>(map_q, map_kv, (bf16*)out, ldo, block_table, table_stride, cu_seqlens, slots, start_pos,
-                       B, max_q_len, n_heads, n_kv, scale, window, stream);
+#define GTG_ARGS map_q, map_kv, (bf16*)out, ldo, block_table, table_stride, cu_seqlens, slots, start_pos, \
+                 B, max_q_len, n_heads, n_kv, scale, window, stream
+    if (g_test_waits) return hd == 64 ? launch<64, true>(GTG_ARGS) : launch<128, true>(GTG_ARGS);
+    return hd == 64 ? launch<64, false>(GTG_ARGS) : launch<128, false>(GTG_ARGS);
+#undef GTG_ARGS
+}
+
+// ---- test hook --------------------------------------------------------------
+// For the test that makes bounded waits run out: while `test_waits` is set, every
+// launch of this library takes the kTest form of its kernel (see Waits above): no
+// asynchronous copy is issued, so no barrier completes, and every wait gives up
+// after a thousand polls.  Such a kernel returns without a result and the status
+// word reads non-zero; nothing faults and nothing hangs.  The kernels as they
+// normally run are not touched by this.  The call also clears the status word.
+GTG_API int gtg_attention_tcgen05_test_hooks(int test_waits) {
+    const int zero = 0;
+    cudaError_t e = cudaDeviceSynchronize();
+    g_test_waits = test_waits != 0;
+    if (e == cudaSuccess) e = cudaMemcpyToSymbol(g_status, &zero, sizeof(zero));
+    return (int)e;
 }

@@ -40,6 +40,17 @@ constexpr int kRowPad = 64;                              // bytes between rows o
 constexpr int kRowStride = kPassK * 2 + kRowPad;
 constexpr int kTileBytes = 16 * kRowStride;
 constexpr unsigned kSpinLimit = 1u << 22;
+// The kernels of this library exist twice: as they run, and (kTest) in the form the
+// test of the give-up path launches, whose waits poll a thousand times instead of
+// millions and whose asynchronous copies are not issued at all, so that every
+// barrier it waits on never completes.  The second form is the first form's code
+// with these two constants changed; see the test hook at the end of this file.
+template <bool kTest> struct Waits {
+    static constexpr unsigned kLimit = kTest ? 1024u : kSpinLimit;
+    static constexpr bool kSkipCopies = kTest;
+};
+static bool g_test_waits = false;       // set by the test hook: launches take the kTest form
+
 
 __device__ int g_status = 0;                             // 1: a wait on the copies gave up
 
@@ -53,13 +64,16 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
 }
+template <bool kTest>
 __device__ __forceinline__ void bulk_copy(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    if (Waits<kTest>::kSkipCopies) return;
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
                  ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
 // True once the phase with this parity has completed; gives up after kSpinLimit polls.
+template <bool kTest>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    for (unsigned i = 0; i < kSpinLimit; ++i) {
+    for (unsigned i = 0; i < Waits<kTest>::kLimit; ++i) {
         uint32_t done;
         asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
                      "selp.u32 %0, 1, 0, p;\n}\n" : "=r"(done) : "r"(bar), "r"(parity) : "memory");
@@ -87,7 +101,7 @@ __device__ __forceinline__ void store_feature(OutT* C, int ldc, int m, int n0, i
 
 // grid = (ceil(N/16), S) with clusters of (1, S, 1): blockIdx.y is the CTA's
 // rank in its cluster and the index of its slice [rank*k_slice, +k_slice) of k.
-template <int NT, typename OutT>
+template <int NT, typename OutT, bool kTest>
 __global__ void __launch_bounds__(kWarps * 32)
 gemm_skinny_kernel(const bf16* __restrict__ X, int ldx, const bf16* __restrict__ W, int ldw,
                    OutT* __restrict__ C, int ldc, int M, int N, int K, int k_slice, int epi) {
@@ -118,13 +132,17 @@ gemm_skinny_kernel(const bf16* __restrict__ X, int ldx, const bf16* __restrict__
         if (threadIdx.x == 0) {
             mbar_expect_tx(bar, 16u * (uint32_t)k_len * 2u);
             for (int r = 0; r < 16; ++r)                       // rows beyond N repeat the last one; dropped at the store
-                bulk_copy(tile_addr + r * kRowStride, W + (size_t)min(n0 + r, N - 1) * ldw + base,
+                bulk_copy<kTest>(tile_addr + r * kRowStride, W + (size_t)min(n0 + r, N - 1) * ldw + base,
                           (uint32_t)k_len * 2u, bar);
         }
-        if (!mbar_wait(bar, parity)) {
+        // The CTA decides as one whether the copies arrived (a block barrier ends every
+        // pass, so its threads may not part ways here).  If a wait gave up: say so and
+        // stop copying -- a barrier whose phase never completed must not be armed again
+        // -- but stay for the sums and the cluster barriers below, where the peers of a
+        // cluster wait; the status word tells the host that the result is void.
+        if (__syncthreads_or(!mbar_wait<kTest>(bar, parity))) {
             if (threadIdx.x == 0) atomicExch(&g_status, 1);
-            mbar_wait(bar, parity);                            // give the copies in flight one more bounded chance
-            return;
+            break;
         }
         parity ^= 1;
 #pragma unroll
@@ -202,7 +220,7 @@ gemm_skinny_kernel(const bf16* __restrict__ X, int ldx, const bf16* __restrict__
     }
 }
 
-template <int NT, typename OutT>
+template <int NT, typename OutT, bool kTest = false>
 int launch_typed(const bf16* X, int ldx, const bf16* W, int ldw, OutT* C, int ldc,
                  int M, int N, int K, int epi, cudaStream_t stream) {
     // the fewest ranks (a power of two, at most 8) whose slice fits one pass
@@ -215,7 +233,7 @@ int launch_typed(const bf16* X, int ldx, const bf16* W, int ldw, OutT* C, int ld
     cfg.dynamicSmemBytes = kTileBytes;
     static bool configured = false;
     if (!configured) {
-        cudaError_t ce = cudaFuncSetAttribute(gemm_skinny_kernel<NT, OutT>,
+        cudaError_t ce = cudaFuncSetAttribute(gemm_skinny_kernel<NT, OutT, kTest>,
                                               cudaFuncAttributeMaxDynamicSharedMemorySize, kTileBytes);
         if (ce != cudaSuccess) return (int)ce;
         configured = true;
@@ -230,7 +248,7 @@ int launch_typed(const bf16* X, int ldx, const bf16* W, int ldw, OutT* C, int ld
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = g_chained_launch ? 2 : 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_skinny_kernel<NT, OutT>, X, ldx, W, ldw, C, ldc, M, N, K, k_slice, epi);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_skinny_kernel<NT, OutT, kTest>, X, ldx, W, ldw, C, ldc, M, N, K, k_slice, epi);
     if (e != cudaSuccess) return (int)e;
     return launch_status();
 }
@@ -257,12 +275,14 @@ constexpr int kPieceBlocks = kPieceK / (kWarps * 32);    // k blocks of 32 per w
 constexpr int kPieceBytes = 16 * kPieceK * 2;
 constexpr int kRing = 3;
 
+template <bool kTest>
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, uint32_t bar) {
+    if (Waits<kTest>::kSkipCopies) return;
     asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];\n"
                  ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
 }
 
-template <int NT, typename OutT>
+template <int NT, typename OutT, bool kTest>
 __global__ void __launch_bounds__(kWarps * 32, 2)
 gemm_stream_kernel(const bf16* __restrict__ X, int ldx, const __grid_constant__ CUtensorMap map_w,
                    OutT* __restrict__ C, int ldc, int M, int N, int K, int k_slice, int epi) {
@@ -294,7 +314,7 @@ gemm_stream_kernel(const bf16* __restrict__ X, int ldx, const __grid_constant__ 
         const int tile = blockIdx.x + (item / n_pieces) * gridDim.x, piece = item % n_pieces;
         const uint32_t bar = bar0 + 8 * stage;
         mbar_expect_tx(bar, (uint32_t)kPieceBytes);             // rows beyond N and blocks beyond K arrive as zeros
-        tma_load_3d(ring0 + stage * kPieceBytes, &map_w, 0, tile * 16, (k_begin + piece * kPieceK) / 64, bar);
+        tma_load_3d<kTest>(ring0 + stage * kPieceBytes, &map_w, 0, tile * 16, (k_begin + piece * kPieceK) / 64, bar);
     };
     if (threadIdx.x == 0) {
         for (int item = 0; item < kRing && item < n_items; ++item) issue(item);
@@ -325,7 +345,10 @@ gemm_stream_kernel(const bf16* __restrict__ X, int ldx, const __grid_constant__ 
     float acc[NT][4];
     for (int item = 0; item < n_items; ++item) {
         const int stage = item % kRing, piece = item % n_pieces;
-        if (!mbar_wait(bar0 + 8 * stage, (uint32_t)(item / kRing) & 1u)) failed = true;   // keep going: peers wait at the barriers below
+        // A wait that gives up ends all waiting and all copying of this CTA (a barrier whose
+        // phase never completed must not be armed again), but not its walk through the
+        // tiles: its peers wait for it at the cluster barriers below.
+        if (!failed && !mbar_wait<kTest>(bar0 + 8 * stage, (uint32_t)(item / kRing) & 1u)) failed = true;
         const unsigned char* tl = ring + stage * kPieceBytes;
         if (piece == 0) {
 #pragma unroll
@@ -354,7 +377,7 @@ gemm_stream_kernel(const bf16* __restrict__ X, int ldx, const __grid_constant__ 
         };
         if (piece == 0) multiply(0); else multiply(kPieceBlocks);   // register indices stay constant
         __syncthreads();                                            // the piece has been read: its stage is free,
-        if (threadIdx.x == 0 && item + kRing < n_items) issue(item + kRing);   // and so is `red` (read before this barrier)
+        if (threadIdx.x == 0 && !failed && item + kRing < n_items) issue(item + kRing);   // and so is `red` (read before this barrier)
         if (piece != n_pieces - 1) continue;
         const int tile_no = item / n_pieces;                        // among this CTA's row tiles
 #pragma unroll
@@ -434,7 +457,7 @@ bool stream_map(CUtensorMap* map, const bf16* W, int ldw, int N, int K) {
 }
 
 // kErrUnsupported when this form does not serve the sizes (the caller then takes the other one).
-template <int NT, typename OutT>
+template <int NT, typename OutT, bool kTest = false>
 int launch_stream(const bf16* X, int ldx, const bf16* W, int ldw, OutT* C, int ldc,
                   int M, int N, int K, int epi, cudaStream_t stream) {
     if (K % 64) return kErrUnsupported;
@@ -450,7 +473,7 @@ int launch_stream(const bf16* X, int ldx, const bf16* W, int ldw, OutT* C, int l
     const int smem = kRing * kPieceBytes + 1024;
     static bool configured = false;
     if (!configured) {
-        cudaError_t ce = cudaFuncSetAttribute(gemm_stream_kernel<NT, OutT>,
+        cudaError_t ce = cudaFuncSetAttribute(gemm_stream_kernel<NT, OutT, kTest>,
                                               cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (ce != cudaSuccess) return (int)ce;
         configured = true;
@@ -480,7 +503,7 @@ int launch_stream(const bf16* X, int ldx, const bf16* W, int ldw, OutT* C, int l
     static int resident[kMaxCluster + 1] = {};
     if (ranks > 1 && resident[ranks] == 0) {
         int n = 0;
-        resident[ranks] = cudaOccupancyMaxActiveClusters(&n, gemm_stream_kernel<NT, OutT>, &cfg) == cudaSuccess && n > 0
+        resident[ranks] = cudaOccupancyMaxActiveClusters(&n, gemm_stream_kernel<NT, OutT, kTest>, &cfg) == cudaSuccess && n > 0
                               ? n : -1;
         cudaGetLastError();
         if (ranks > 2 && resident[ranks] > 12) resident[ranks] -= (resident[ranks] + 11) / 12;
@@ -491,7 +514,7 @@ int launch_stream(const bf16* X, int ldx, const bf16* W, int ldw, OutT* C, int l
         cfg.gridDim.x = (row_tiles + rounds - 1) / rounds;
     }
     cfg.numAttrs = g_chained_launch ? 2 : 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_stream_kernel<NT, OutT>, X, ldx, map_w, C, ldc, M, N, K, k_slice, epi);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_stream_kernel<NT, OutT, kTest>, X, ldx, map_w, C, ldc, M, N, K, k_slice, epi);
     if (e != cudaSuccess) return (int)e;
     return launch_status();
 }
@@ -499,6 +522,17 @@ int launch_stream(const bf16* X, int ldx, const bf16* W, int ldw, OutT* C, int l
 template <int NT>
 int launch(const bf16* X, int ldx, const bf16* W, int ldw, void* C, int ldc, int out_f32,
            int M, int N, int K, int epi, cudaStream_t stream) {
+    if (g_test_waits) {                        // the give-up test: bfloat16 results of up to 16 rows
+        if constexpr (NT <= 2) {
+            if (out_f32) return kErrUnsupported;
+            if (K <= kMaxCluster * kPassK) {
+                const int st = launch_stream<NT, bf16, true>(X, ldx, W, ldw, (bf16*)C, ldc, M, N, K, epi, stream);
+                if (st != kErrUnsupported) return st;
+            }
+            return launch_typed<NT, bf16, true>(X, ldx, W, ldw, (bf16*)C, ldc, M, N, K, epi, stream);
+        }
+        return kErrUnsupported;
+    }
     if constexpr (NT <= 2) {
         if (K <= kMaxCluster * kPassK) {
             const int st = out_f32 ? launch_stream<NT, float>(X, ldx, W, ldw, (float*)C, ldc, M, N, K, epi, stream)
@@ -539,4 +573,20 @@ GTG_API int gtg_gemm_bf16_skinny(const void* X, int ldx, const void* W, int ldw,
     if (M <= 16) return launch<2>(x, ldx, w, ldw, C, ldc, out_f32, M, N, K, epilogue, stream);
     if (M <= 32) return launch<4>(x, ldx, w, ldw, C, ldc, out_f32, M, N, K, epilogue, stream);
     return launch<8>(x, ldx, w, ldw, C, ldc, out_f32, M, N, K, epilogue, stream);
+}
+
+// ---- test hook --------------------------------------------------------------
+// For the test that makes bounded waits run out: while `test_waits` is set, every
+// launch of this library takes the kTest form of its kernel (see Waits above): no
+// asynchronous copy is issued, so no barrier completes, and every wait gives up
+// after a thousand polls.  Such a kernel returns without a result and the status
+// word reads non-zero; nothing faults and nothing hangs.  The kernels as they
+// normally run are not touched by this (the test form exists for bfloat16 results
+// of up to 16 rows).  The call also clears the status word.
+GTG_API int gtg_gemm_bf16_skinny_test_hooks(int test_waits) {
+    const int zero = 0;
+    cudaError_t e = cudaDeviceSynchronize();
+    g_test_waits = test_waits != 0;
+    if (e == cudaSuccess) e = cudaMemcpyToSymbol(g_status, &zero, sizeof(zero));
+    return (int)e;
 }

@@ -37,6 +37,17 @@ constexpr int kMaxSlices = 8;                 // CTAs of a cluster (the portable
 static_assert(kPartFloats * 4 <= kStages * kBlockBytes, "the partial sums reuse the ring");
 constexpr int kSmemBytes = kStages * kBlockBytes + 1024 + 256;
 constexpr unsigned kSpinLimit = 1u << 22;
+// The kernels of this library exist twice: as they run, and (kTest) in the form the
+// test of the give-up path launches, whose waits poll a thousand times instead of
+// millions and whose asynchronous copies are not issued at all, so that every
+// barrier it waits on never completes.  The second form is the first form's code
+// with these two constants changed; see the test hook at the end of this file.
+template <bool kTest> struct Waits {
+    static constexpr unsigned kLimit = kTest ? 1024u : kSpinLimit;
+    static constexpr bool kSkipCopies = kTest;
+};
+static bool g_test_waits = false;       // set by the test hook: launches take the kTest form
+
 
 __device__ int g_status = 0;
 
@@ -50,8 +61,9 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
 }
+template <bool kTest>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-    for (unsigned i = 0; i < kSpinLimit; ++i) {
+    for (unsigned i = 0; i < Waits<kTest>::kLimit; ++i) {
         uint32_t done;
         asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
                      "selp.u32 %0, 1, 0, p;\n}\n" : "=r"(done) : "r"(bar), "r"(parity) : "memory");
@@ -62,7 +74,9 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     atomicExch(&g_status, 1);
     return false;
 }
+template <bool kTest>
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+    if (Waits<kTest>::kSkipCopies) return;
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
                  ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
 }
@@ -123,7 +137,7 @@ __device__ __forceinline__ float4 remote_ld4(uint32_t addr, uint32_t rank) {
 
 // grid.x = row tiles x slices, clusters of `slices` CTAs along x: CTA rank r of a
 // cluster takes k blocks [r * kb_per, (r + 1) * kb_per) of its row tile.
-template <typename OutT>
+template <typename OutT, bool kTest>
 __global__ void __launch_bounds__(kThreads)
 swapab_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
               OutT* __restrict__ C, int ldc, int M, int N, int K, int kb_per, int slices, int epi) {
@@ -173,17 +187,17 @@ swapab_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
             const int first = min(n_kb, kStages);
             for (int kb = 0; kb < first; ++kb) {
                 mbar_expect_tx(full_bar(kb), kBlockBytes);
-                tma_load_2d(base + kb * kBlockBytes, &map_w, k_of(kb), n0, full_bar(kb));
+                tma_load_2d<kTest>(base + kb * kBlockBytes, &map_w, k_of(kb), n0, full_bar(kb));
             }
             chain_wait();
             for (int kb = 0; kb < first; ++kb)
-                tma_load_2d(base + kb * kBlockBytes + kWBytes, &map_x, k_of(kb), 0, full_bar(kb));
+                tma_load_2d<kTest>(base + kb * kBlockBytes + kWBytes, &map_x, k_of(kb), 0, full_bar(kb));
             for (int kb = first; kb < n_kb; ++kb) {
                 const int s = kb % kStages;
-                if (!mbar_wait(empty_bar(s), ((kb / kStages) & 1u) ^ 1u, abort_flag)) break;
+                if (!mbar_wait<kTest>(empty_bar(s), ((kb / kStages) & 1u) ^ 1u, abort_flag)) break;
                 mbar_expect_tx(full_bar(s), kBlockBytes);
-                tma_load_2d(base + s * kBlockBytes, &map_w, k_of(kb), n0, full_bar(s));
-                tma_load_2d(base + s * kBlockBytes + kWBytes, &map_x, k_of(kb), 0, full_bar(s));
+                tma_load_2d<kTest>(base + s * kBlockBytes, &map_w, k_of(kb), n0, full_bar(s));
+                tma_load_2d<kTest>(base + s * kBlockBytes + kWBytes, &map_x, k_of(kb), 0, full_bar(s));
             }
         }
     } else if (warp == 5) {
@@ -193,7 +207,7 @@ swapab_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
             bool ok = true;
             for (int kb = 0; kb < n_kb; ++kb) {
                 const int s = kb % kStages;
-                if (!mbar_wait(full_bar(s), (kb / kStages) & 1u, abort_flag)) { ok = false; break; }
+                if (!mbar_wait<kTest>(full_bar(s), (kb / kStages) & 1u, abort_flag)) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::);
                 const uint64_t da = umma_desc(base + s * kBlockBytes);
                 const uint64_t db = umma_desc(base + s * kBlockBytes + kWBytes);
@@ -208,7 +222,7 @@ swapab_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
     } else {
         // ------------------------------------------------------------ accumulator -> shared memory, [token][feature]
         chain_wait();
-        const bool ready = mbar_wait(acc_full, 0u, abort_flag);
+        const bool ready = mbar_wait<kTest>(acc_full, 0u, abort_flag);
         const bool use = __all_sync(0xffffffffu, ready) && n_kb > 0 && !*abort_flag;
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::);
         const int feature = warp * 32 + lane;
@@ -348,18 +362,18 @@ int device_sms() {
     return sms;
 }
 
-template <typename OutT>
+template <typename OutT, bool kTest>
 int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, OutT* C, int ldc, int M, int N, int K,
            int kb_per, int slices, int epilogue, cudaStream_t stream) {
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(swapab_kernel<OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        cudaError_t e = cudaFuncSetAttribute(swapab_kernel<OutT, kTest>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
     const long long ctas = (long long)((N + BR - 1) / BR) * slices;
     if (ctas > 0x7fffffff) return kErrUnsupported;
-    return launch_chained_cluster(swapab_kernel<OutT>, dim3((unsigned)ctas), dim3(kThreads), slices, (size_t)kSmemBytes,
+    return launch_chained_cluster(swapab_kernel<OutT, kTest>, dim3((unsigned)ctas), dim3(kThreads), slices, (size_t)kSmemBytes,
                                   stream, map_w, map_x, C, ldc, M, N, K, kb_per, slices, epilogue);
 }
 }  // namespace
@@ -394,6 +408,25 @@ GTG_API int gtg_gemm_bf16_swapab(const void* X, int ldx, const void* W, int ldw,
     if (st != 0) return st;
     st = make_map(&map_x, X, M, K, ldx, BT);
     if (st != 0) return st;
-    if (out_f32) return launch<float>(map_w, map_x, (float*)C, ldc, M, N, K, kb_per, slices, epilogue, stream);
-    return launch<bf16>(map_w, map_x, (bf16*)C, ldc, M, N, K, kb_per, slices, epilogue, stream);
+    if (g_test_waits) {
+        if (out_f32) return launch<float, true>(map_w, map_x, (float*)C, ldc, M, N, K, kb_per, slices, epilogue, stream);
+        return launch<bf16, true>(map_w, map_x, (bf16*)C, ldc, M, N, K, kb_per, slices, epilogue, stream);
+    }
+    if (out_f32) return launch<float, false>(map_w, map_x, (float*)C, ldc, M, N, K, kb_per, slices, epilogue, stream);
+    return launch<bf16, false>(map_w, map_x, (bf16*)C, ldc, M, N, K, kb_per, slices, epilogue, stream);
+}
+
+// ---- test hook --------------------------------------------------------------
+// For the test that makes bounded waits run out: while `test_waits` is set, every
+// launch of this library takes the kTest form of its kernel (see Waits above): no
+// asynchronous copy is issued, so no barrier completes, and every wait gives up
+// after a thousand polls.  Such a kernel returns without a result and the status
+// word reads non-zero; nothing faults and nothing hangs.  The kernels as they
+// normally run are not touched by this.  The call also clears the status word.
+GTG_API int gtg_gemm_bf16_swapab_test_hooks(int test_waits) {
+    const int zero = 0;
+    cudaError_t e = cudaDeviceSynchronize();
+    g_test_waits = test_waits != 0;
+    if (e == cudaSuccess) e = cudaMemcpyToSymbol(g_status, &zero, sizeof(zero));
+    return (int)e;
 }

@@ -32,6 +32,17 @@ constexpr int kThreads = 192;
 constexpr int kABytes = BM * BK * 2, kBBytes = BN * BK * 2, kStageBytes = kABytes + kBBytes;
 constexpr int kTmemCols = 512;                     // two accumulators of BN columns
 constexpr unsigned kSpinLimit = 1u << 22;
+// The kernels of this library exist twice: as they run, and (kTest) in the form the
+// test of the give-up path launches, whose waits poll a thousand times instead of
+// millions and whose asynchronous copies are not issued at all, so that every
+// barrier it waits on never completes.  The second form is the first form's code
+// with these two constants changed; see the test hook at the end of this file.
+template <bool kTest> struct Waits {
+    static constexpr unsigned kLimit = kTest ? 1024u : kSpinLimit;
+    static constexpr bool kSkipCopies = kTest;
+};
+static bool g_test_waits = false;       // set by the test hook: launches take the kTest form
+
 constexpr int kStoreBytes = 32 * 128;              // one staged box: 32 rows x 64 bfloat16
 constexpr int kSmemBytes = STAGES * kStageBytes + 1024 /* barriers */ + 4 * 2 * kStoreBytes /* staging */ +
                            1024 /* alignment slack */;
@@ -50,8 +61,9 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
 }
 // Polls until the phase with `parity` completes, the abort flag is raised, or the limit is hit.
+template <bool kTest>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-    for (unsigned i = 0; i < kSpinLimit; ++i) {
+    for (unsigned i = 0; i < Waits<kTest>::kLimit; ++i) {
         uint32_t done;
         asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
                      "selp.u32 %0, 1, 0, p;\n}\n" : "=r"(done) : "r"(bar), "r"(parity) : "memory");
@@ -62,7 +74,9 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     atomicExch(&g_status, 1);
     return false;
 }
+template <bool kTest>
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+    if (Waits<kTest>::kSkipCopies) return;
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
                  ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
 }
@@ -141,7 +155,7 @@ struct RopeKV {
     int n_heads, n_kv;
 };
 
-template <typename OutT>
+template <typename OutT, bool kTest>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     const __grid_constant__ CUtensorMap map_c, int use_store_map,
@@ -192,11 +206,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 for (int kb = 0; kb < n_kb; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t round = it / STAGES;
-                    ok = mbar_wait(empty_bar(s), (round & 1u) ^ 1u, abort_flag);   // passes at once in round 0
+                    ok = mbar_wait<kTest>(empty_bar(s), (round & 1u) ^ 1u, abort_flag);   // passes at once in round 0
                     if (!ok) break;
                     mbar_expect_tx(full_bar(s), kStageBytes);
-                    tma_load_2d(base + s * kStageBytes, &map_a, kb * BK, m0, full_bar(s));
-                    tma_load_2d(base + s * kStageBytes + kABytes, &map_w, kb * BK, n0, full_bar(s));
+                    tma_load_2d<kTest>(base + s * kStageBytes, &map_a, kb * BK, m0, full_bar(s));
+                    tma_load_2d<kTest>(base + s * kStageBytes + kABytes, &map_w, kb * BK, n0, full_bar(s));
                 }
             }
         }
@@ -209,14 +223,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             int t = 0;                                         // tiles done by this CTA
             for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++t) {
                 const int acc = t & 1;
-                ok = mbar_wait(acc_empty_bar(acc), (((uint32_t)t >> 1) & 1u) ^ 1u, abort_flag);   // epilogue drained it
+                ok = mbar_wait<kTest>(acc_empty_bar(acc), (((uint32_t)t >> 1) & 1u) ^ 1u, abort_flag);   // epilogue drained it
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::);
                 const uint32_t tmem_acc = tmem_base + (uint32_t)(acc * BN);
                 for (int kb = 0; kb < n_kb; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t round = it / STAGES;
-                    ok = mbar_wait(full_bar(s), round & 1u, abort_flag);
+                    ok = mbar_wait<kTest>(full_bar(s), round & 1u, abort_flag);
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;\n" ::);
                     const uint64_t da = umma_desc(base + s * kStageBytes);
@@ -243,7 +257,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++t) {
             const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
             const int acc = t & 1;
-            if (!mbar_wait(acc_full_bar(acc), ((uint32_t)t >> 1) & 1u, abort_flag)) break;
+            if (!mbar_wait<kTest>(acc_full_bar(acc), ((uint32_t)t >> 1) & 1u, abort_flag)) break;
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::);
             const int row = m0 + warp * 32 + lane;
             const uint32_t tmem_row = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(acc * BN);
@@ -532,9 +546,13 @@ int run(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int ou
     static bool configured = false;
     static int sms = 148;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<float, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
         if (e != cudaSuccess) return (int)e;
-        e = cudaFuncSetAttribute(gemm_tcgen05_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        e = cudaFuncSetAttribute(gemm_tcgen05_kernel<bf16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        if (e != cudaSuccess) return (int)e;
+        e = cudaFuncSetAttribute(gemm_tcgen05_kernel<bf16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        if (e != cudaSuccess) return (int)e;
+        e = cudaFuncSetAttribute(gemm_tcgen05_kernel<float, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
         if (e != cudaSuccess) return (int)e;
         int dev = 0, n = 0;
         if (cudaGetDevice(&dev) == cudaSuccess &&
@@ -543,10 +561,17 @@ int run(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int ou
         configured = true;
     }
     const int grid = (int)(tiles < sms ? tiles : sms);
+    if (g_test_waits) {
+        if (out_f32)
+            return launch_chained(gemm_tcgen05_kernel<float, true>, dim3(grid), dim3(kThreads), (size_t)kSmemBytes, stream,
+                                  map_a, map_w, map_c, use_store_map, (float*)C, ldc, M, N, K, epilogue, rope);
+        return launch_chained(gemm_tcgen05_kernel<bf16, true>, dim3(grid), dim3(kThreads), (size_t)kSmemBytes, stream,
+                              map_a, map_w, map_c, use_store_map, (bf16*)C, ldc, M, N, K, epilogue, rope);
+    }
     if (out_f32)
-        return launch_chained(gemm_tcgen05_kernel<float>, dim3(grid), dim3(kThreads), (size_t)kSmemBytes, stream,
+        return launch_chained(gemm_tcgen05_kernel<float, false>, dim3(grid), dim3(kThreads), (size_t)kSmemBytes, stream,
                               map_a, map_w, map_c, use_store_map, (float*)C, ldc, M, N, K, epilogue, rope);
-    return launch_chained(gemm_tcgen05_kernel<bf16>, dim3(grid), dim3(kThreads), (size_t)kSmemBytes, stream,
+    return launch_chained(gemm_tcgen05_kernel<bf16, false>, dim3(grid), dim3(kThreads), (size_t)kSmemBytes, stream,
                           map_a, map_w, map_c, use_store_map, (bf16*)C, ldc, M, N, K, epilogue, rope);
 }
 }  // namespace
@@ -585,4 +610,19 @@ GTG_API int gtg_gemm_bf16_tcgen05_qkv_rope(const void* A, int lda, const void* W
     RopeKV rope{(const float2*)cos_sin, token_seq, slots, positions, block_table, table_stride,
                 (bf16*)kc, (bf16*)vc, page_stride, n_heads, n_kv};
     return run(A, lda, W, ldw, C, ldc, 0, M, (n_heads + 2 * n_kv) * 64, K, 2, rope, stream);
+}
+
+// ---- test hook --------------------------------------------------------------
+// For the test that makes bounded waits run out: while `test_waits` is set, every
+// launch of this library takes the kTest form of its kernel (see Waits above): no
+// asynchronous copy is issued, so no barrier completes, and every wait gives up
+// after a thousand polls.  Such a kernel returns without a result and the status
+// word reads non-zero; nothing faults and nothing hangs.  The kernels as they
+// normally run are not touched by this.  The call also clears the status word.
+GTG_API int gtg_gemm_bf16_tcgen05_test_hooks(int test_waits) {
+    const int zero = 0;
+    cudaError_t e = cudaDeviceSynchronize();
+    g_test_waits = test_waits != 0;
+    if (e == cudaSuccess) e = cudaMemcpyToSymbol(g_status, &zero, sizeof(zero));
+    return (int)e;
 }

@@ -31,6 +31,10 @@ _SIGNATURES = {
     "gtg_gemm_bf16_mma": ("gemm_bf16_mma", [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _P]),
     "gtg_gemm_bf16_skinny": ("gemm_bf16_skinny", [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _P]),
     "gtg_gemm_bf16_skinny_status": ("gemm_bf16_skinny", []),
+    "gtg_gemm_bf16_skinny_test_hooks": ("gemm_bf16_skinny", [_I]),
+    "gtg_gemm_bf16_tcgen05_test_hooks": ("gemm_bf16_tcgen05", [_I]),
+    "gtg_gemm_bf16_swapab_test_hooks": ("gemm_bf16_swapab", [_I]),
+    "gtg_attention_tcgen05_test_hooks": ("attention_tcgen05", [_I]),
     "gtg_gemm_bf16_tcgen05": ("gemm_bf16_tcgen05", [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _P]),
     "gtg_gemm_bf16_tcgen05_add": ("gemm_bf16_tcgen05", [_P, _I, _P, _I, _P, _I, _I, _I, _I, _P]),
     "gtg_gemm_bf16_tcgen05_status": ("gemm_bf16_tcgen05", []),
@@ -407,6 +411,23 @@ def bounded_wait_failures() -> int:
         if _SIGNATURES[symbol][0] in build._LOADED:        # only libraries that have run can have failed
             total += int(_fn(symbol)())
     return total
+
+
+WAITING_LIBRARIES = ("gemm_bf16_skinny", "gemm_bf16_tcgen05", "gemm_bf16_swapab", "attention_tcgen05")
+
+
+def wait_test_hooks(library: str, test_waits: bool) -> None:
+    """For tests of the give-up path only.  While set, every launch of `library`
+    (one of WAITING_LIBRARIES) takes the test form of its kernel: the same code
+    compiled so that it issues none of its asynchronous copies -- the barriers it
+    waits on then never complete -- and so that a wait polls a thousand times
+    before it gives up.  A kernel launched so returns without a result and
+    `bounded_wait_failures()` reads non-zero.  The call synchronises the device and
+    clears the library's status word; False restores normal operation."""
+    _need(library in WAITING_LIBRARIES, f"wait_test_hooks: {library!r} has no bounded waits; known: {WAITING_LIBRARIES}")
+    code = int(_fn(f"gtg_{library}_test_hooks")(1 if test_waits else 0))
+    if code != 0:
+        raise KernelError(f"wait_test_hooks({library}): CUDA error {code}")
 
 
 # ----------------------------------------------------------------------- attention
