@@ -265,7 +265,9 @@ def run_own(args):
 
     kv_row = 2 * cfg["num_key_value_heads"] * cfg["head_dim"] * 2 * args.layers     # cache bytes of one token, all layers
     weight_bytes = decode_bytes(cfg, args.layers, 0, 0)[1]
-    WARM_MS = 300.0                  # at least this much untimed device work before a timed region
+    # at least this much untimed device work before a timed region (not in the --only modes,
+    # which are for profilers and want few launches before the captured ones)
+    WARM_MS = 300.0 if args.only == "all" else 0.0
 
     def decode_run(batch, steps, warmup, host, prompts=None):
         """`steps` timed decode steps of `batch` sequences.  Without `prompts` the
