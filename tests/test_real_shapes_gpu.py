@@ -101,3 +101,44 @@ def test_decode_steps_of_more_sequences_than_the_streaming_products_take(shaped)
         want = plain_llama.forward(cfg, w, requests[i])
         have = np.stack([got[t][i] for t in range(decoded)])
         check(have, want[lengths[i]:lengths[i] + decoded], "bfloat16", cfg["intermediate_size"], f"{name} sequence {i} of {n_seqs}")
+
+
+def test_keys_in_the_cache_depend_on_the_cutting_within_rounding_only(shaped):
+    """In bfloat16 a token's key is rounded where it is made, and prompts, short chunks
+    and single tokens make it in different kernels (rotation on the float accumulators
+    of the prompt projection; on the rounded projection in steps of up to 64 rows and
+    inside the decode attention).  The same 130 tokens fed whole, as 40 + 90 and as 129
+    + 1 must leave the same keys and values up to that rounding.  The first layer's inputs
+    are identical; a rotated channel a cos - b sin inherits the rounding of both a and b,
+    so the bound is three units of the last place of the head's largest channel (values,
+    which are not rotated: of the value itself)."""
+    import torch
+    name, folder, prompts, _ = shaped
+    tokens = prompts[0][:130]
+    model = lib.Model.load(folder, dtype="bfloat16", device="cuda")
+
+    def run(cuts):
+        cache = model.new_cache(max_tokens=64 * 3, max_slots=1)
+        slot = cache.open_sequence()
+        done = 0
+        for n in cuts:
+            step(model, cache, [StepEntry(slot, tokens[done:done + n], [])])
+            done += n
+        t = torch.arange(done)
+        pages = cache.groups[0].table_host[slot][t // 64].long().cuda()
+        out = []
+        for entry in (0, len(model.plan.schedule) - 1):
+            kv = cache.handles[entry].kv
+            out.append((kv.k[pages, :, (t % 64).cuda(), :].float(), kv.v[pages, :, (t % 64).cuda(), :].float()))
+        return out
+    whole, chunks, last_alone = run([130]), run([40, 90]), run([129, 1])
+    for other, what in ((chunks, "40 + 90"), (last_alone, "129 + 1")):
+        (k0, v0), (k1, v1) = whole[0], other[0]                 # the first layer: same inputs, other kernels
+        ulp = 2.0 ** -8
+        for a, b, which in ((k0, k1, "keys"), (v0, v1, "values")):
+            size = a.abs().amax(dim=-1, keepdim=True) if which == "keys" else torch.maximum(a.abs(), b.abs())
+            worst = float(((a - b).abs() / (size + 1e-3)).max())
+            assert worst <= 3 * ulp, f"{name}: first layer's {which}, whole against {what}: {worst / ulp:.2f} units"
+        (k0, v0), (k1, v1) = whole[1], other[1]                 # the last layer: its inputs carry the rounding on
+        for a, b in ((k0, k1), (v0, v1)):
+            assert float((a - b).abs().max()) <= 5e-2 * max(1.0, float(a.abs().max()))
