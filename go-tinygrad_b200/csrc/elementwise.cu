@@ -371,3 +371,62 @@ GTG_API int gtg_advance(int* tokens, int* positions, int* steps, const int* samp
     st = launch_chained(advance_kernel, dim3((B + 127) / 128), dim3(128), 0, stream, tokens, positions, steps, sampled, B);
     return st;
 }
+
+// ------------------------------------------- a step's cache addresses, checked
+// The debug pass that stands in for a memory checker: before a kernel that finds
+// its keys and values through (sequence -> slot -> block table -> page), walk the
+// same indices and record the first one that would leave its array -- in a flag
+// the host reads, never by trapping -- so that the host can refuse the launch.
+//   mode 0  per token:    item n has sequence token_seq[n], position positions[n]
+//   mode 1  per sequence: item b is read up to position positions[b] (a decode step)
+//   mode 2  per sequence: item b is read up to start_pos[b] + its run in cu_seqlens (a prompt step)
+// flag[0]: 0 or what is wrong (1 sequence index, 2 slot, 3 negative position or run,
+// 4 position beyond the block table's row, 5 page index outside the cache);
+// flag[1]: the item.
+__global__ void check_cache_access_kernel(int mode, int n_items, const int* __restrict__ token_seq,
+                                          const int* __restrict__ slots, const int* __restrict__ positions,
+                                          const int* __restrict__ start_pos, const int* __restrict__ cu_seqlens,
+                                          int n_seqs, const int* __restrict__ block_table, int table_stride,
+                                          int n_slots, int n_pages, int* __restrict__ flag) {
+    const int item = blockIdx.x * blockDim.x + threadIdx.x;
+    if (item >= n_items) return;
+    int bad = 0;
+    int seq = item, first_page = 0, last_pos = 0;
+    if (mode == 0) {
+        seq = token_seq[item];
+        if (seq < 0 || seq >= n_seqs) bad = 1;
+        last_pos = positions[item];
+        first_page = last_pos >= 0 ? last_pos / kPageTokens : 0;          // earlier pages were other tokens' to check
+    } else if (mode == 1) {
+        last_pos = positions[item];
+    } else {
+        const int run = cu_seqlens[item + 1] - cu_seqlens[item];
+        if (run < 0 || start_pos[item] < 0) bad = 3;
+        last_pos = start_pos[item] + run - 1;
+        if (run == 0) last_pos = -2;                                      // nothing is read
+    }
+    if (!bad && last_pos != -2) {
+        const int slot = slots[seq];
+        if (slot < 0 || slot >= n_slots) bad = 2;
+        else if (last_pos < 0) bad = 3;
+        else if (last_pos / kPageTokens >= table_stride) bad = 4;
+        else {
+            for (int p = first_page; p <= last_pos / kPageTokens; ++p) {
+                const int page = block_table[(size_t)slot * table_stride + p];
+                if (page < 0 || page >= n_pages) { bad = 5; break; }
+            }
+        }
+    }
+    if (bad && atomicCAS(&flag[0], 0, bad) == 0) flag[1] = item;
+}
+
+GTG_API int gtg_check_cache_access(int mode, int n_items, const int* token_seq, const int* slots,
+                                   const int* positions, const int* start_pos, const int* cu_seqlens, int n_seqs,
+                                   const int* block_table, int table_stride, int n_slots, int n_pages, int* flag,
+                                   cudaStream_t stream) {
+    if (n_items <= 0) return 0;
+    if (mode < 0 || mode > 2 || flag == nullptr || slots == nullptr || block_table == nullptr) return kErrBadArgument;
+    check_cache_access_kernel<<<(n_items + 127) / 128, 128, 0, stream>>>(mode, n_items, token_seq, slots, positions,
+        start_pos, cu_seqlens, n_seqs, block_table, table_stride, n_slots, n_pages, flag);
+    return launch_status();
+}

@@ -98,7 +98,7 @@ class DecodeBatch:
 
     def _forward(self) -> None:
         ctx = self._context()
-        with ops.chained_launches(self.chained):
+        with ops.chained_launches(self.chained), ops.checked_access(self.model.rt.check_access):
             stream = run_layers(self.model, self.cache, ctx)
             self.logits = logits_at(self.model, stream, ctx, self.rows)
             self.sampler.pick(self.logits, self.requests, self.steps, out=self.sampled)
@@ -108,7 +108,7 @@ class DecodeBatch:
         self.cache.reserve_many([(s, self.cache.length(s) + 1) for s in self.slots])
         self.cache.flush_tables()
         longest = max(self.cache.length(s) for s in self.slots) + 1
-        if self.model.op_hook is not None:                # a hook listens now: this step runs in the open
+        if self.model.op_hook is not None or self.model.rt.check_access:   # a hook listens or checks run: in the open
             self.graph = None
             self._planned_len = max(longest, int(longest * self.AHEAD))
             self._forward()

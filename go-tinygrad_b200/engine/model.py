@@ -62,8 +62,9 @@ class Model:
     @property
     def capturable(self) -> bool:
         """Whether a step of this model can be recorded as a CUDA graph: every part
-        says so and no diagnostic hook listens."""
-        return self.op_hook is None and all(part.capturable for part in self.parts())
+        says so, no diagnostic hook listens and no access checks run."""
+        return (self.op_hook is None and not self.rt.check_access
+                and all(part.capturable for part in self.parts()))
 
     def weight_specs(self) -> List[WeightSpec]:
         specs: List[WeightSpec] = []

@@ -168,7 +168,7 @@ def step(model: Model, cache: Cache, entries: Sequence[StepEntry]) -> torch.Tens
     ctx, rows = build_context(model, cache, entries)
     # each kernel may set itself up while its predecessor drains (kernels that take
     # no part in this are launched the plain way and order themselves fully)
-    with ops.chained_launches(model.rt.device.type == "cuda"):
+    with ops.chained_launches(model.rt.device.type == "cuda"), ops.checked_access(model.rt.check_access):
         stream = run_layers(model, cache, ctx)
         logits = logits_at(model, stream, ctx, rows)
     for e in entries:

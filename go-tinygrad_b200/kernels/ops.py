@@ -27,6 +27,7 @@ _SIGNATURES = {
     "gtg_rope_table": ("elementwise", [_P, _P, _P, _I, _I, _P]),
     "gtg_rope_kv_store": ("elementwise", [_I, _P, _I, _P, _I, _I, _I, _I, _I, _P, _P, _L, _P, _I, _P, _P, _P, _I, _P]),
     "gtg_advance": ("elementwise", [_P, _P, _P, _P, _I, _P]),
+    "gtg_check_cache_access": ("elementwise", [_I, _I, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _P, _P]),
     "gtg_gemm_f32": ("gemm_f32", [_P, _I, _P, _I, _P, _I, _I, _I, _I, _P]),
     "gtg_gemm_bf16_mma": ("gemm_bf16_mma", [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _P]),
     "gtg_gemm_bf16_skinny": ("gemm_bf16_skinny", [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _P]),
@@ -176,6 +177,53 @@ def _rows2d(t: torch.Tensor, name: str) -> None:
                                              f"got shape {tuple(t.shape)} strides {t.stride()}")
 
 
+# ------------------------------------------------- the debug pass over cache addresses
+_checked = False
+_ACCESS_FAULTS = {1: "a token names a sequence outside the batch", 2: "a sequence's slot is outside the cache",
+                  3: "a position or a run of tokens is negative", 4: "a position lies beyond the block table's row",
+                  5: "the block table names a page outside the cache"}
+
+
+class checked_access:
+    """Within this context every kernel that finds keys and values through the block
+    table is preceded by a pass over the same indices (sequence -> slot -> table row
+    -> page); the first index that would leave its array is reported as a
+    `KernelError` and the kernel is not launched.  The stand-in for a memory
+    checker: it costs a kernel and a synchronisation per call, so it is for
+    debugging, not for serving, and a step under it is not recorded as a graph."""
+
+    def __init__(self, on: bool = True):
+        self.on = bool(on)
+
+    def __enter__(self):
+        global _checked
+        self.before, _checked = _checked, self.on
+        return self
+
+    def __exit__(self, *exc):
+        global _checked
+        _checked = self.before
+
+
+def _check_access(what: str, mode: int, kv, slots, positions=None, token_seq=None, start_pos=None,
+                  cu_seqlens=None, n_items: Optional[int] = None) -> None:
+    if not _checked or kv is None:
+        return
+    n_seqs = slots.numel()
+    if n_items is None:
+        n_items = n_seqs
+    flag = torch.zeros(2, dtype=torch.int32, device=slots.device)
+    code = _fn("gtg_check_cache_access")(mode, int(n_items), _ptr(token_seq), _ptr(slots), _ptr(positions),
+                                         _ptr(start_pos), _ptr(cu_seqlens), n_seqs, _ptr(kv.block_table),
+                                         kv.table_stride, kv.block_table.shape[0], kv.k.shape[0], _ptr(flag), _stream())
+    if code != 0:
+        raise KernelError(f"{what}: the access check could not run (code {code})")
+    bad, item = flag.tolist()
+    if bad:
+        unit = "token" if mode == 0 else "sequence"
+        raise KernelError(f"{what}: {_ACCESS_FAULTS.get(bad, bad)} ({unit} {item} of the step); the kernel was not launched")
+
+
 # ------------------------------------------------------------------ elementwise
 def embed(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> None:
     """out[n,:] (float32) = table[tokens[n],:]."""
@@ -253,6 +301,7 @@ def rope_kv_store(qkv: torch.Tensor, cos_sin: Optional[torch.Tensor], n_heads: i
     if n_kv_store > 0:
         _need(kv is not None and kv.k.dtype == qkv.dtype and kv.head_dim == head_dim
               and kv.n_kv_heads == n_kv_store, "rope_kv_store: cache entry does not match the heads to store")
+        _check_access("rope_kv_store", 0, kv, slots, positions, token_seq, n_items=N)
         args = (_ptr(kv.k), _ptr(kv.v), kv.page_stride, _ptr(kv.block_table), kv.table_stride)
     else:
         args = (None, None, 0, None, 0)
@@ -396,6 +445,7 @@ def linear_qkv_rope(x: torch.Tensor, w: torch.Tensor, qkv: torch.Tensor, cos_sin
           "linear_qkv_rope: cos_sin must be float32 [M, 32, 2]")
     for name, t in (("token_seq", token_seq), ("slots", slots), ("positions", positions)):
         _need(t.dtype == torch.int32 and t.is_contiguous(), f"linear_qkv_rope: {name} must be contiguous int32")
+    _check_access("linear_qkv_rope", 0, kv, slots, positions, token_seq, n_items=M)
     _check(_fn("gtg_gemm_bf16_tcgen05_qkv_rope")(
         _ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(qkv), qkv.stride(0), M, K, _ptr(cos_sin),
         _ptr(token_seq), _ptr(slots), _ptr(positions), _ptr(kv.block_table), kv.table_stride,
@@ -443,6 +493,7 @@ def attention_simple(q: torch.Tensor, out: torch.Tensor, kv, token_seq, slots, p
     N = q.shape[0]
     _need(kv.k.dtype == q.dtype == out.dtype, "attention: q, out and the cache must share a dtype")
     _need(kv.head_dim <= 256, f"attention: head_dim {kv.head_dim} exceeds 256")
+    _check_access("attention_simple", 0, kv, slots, positions, token_seq, n_items=N)
     _check(_fn("gtg_attention_simple")(_dt(q), _ptr(q), q.stride(0), _ptr(out), out.stride(0),
                                        _ptr(kv.k), _ptr(kv.v), kv.page_stride, _ptr(kv.block_table),
                                        kv.table_stride, _ptr(token_seq), _ptr(slots), _ptr(positions),
@@ -457,6 +508,7 @@ def attention_prefill_bf16(q, out, kv, cu_seqlens, slots, start_pos, n_seqs: int
           "attention_prefill_bf16: bfloat16 only")
     _need(attention_bf16_supports(kv.head_dim),
           f"attention_prefill_bf16: head_dim {kv.head_dim} is not a multiple of 16 up to 128")
+    _check_access("attention_prefill_bf16", 2, kv, slots, start_pos=start_pos, cu_seqlens=cu_seqlens, n_items=n_seqs)
     _check(_fn("gtg_attention_prefill_bf16")(_ptr(q), q.stride(0), _ptr(out), out.stride(0),
                                              _ptr(kv.k), _ptr(kv.v), kv.page_stride, _ptr(kv.block_table),
                                              kv.table_stride, _ptr(cu_seqlens), _ptr(slots), _ptr(start_pos),
@@ -480,6 +532,7 @@ def attention_prefill_tcgen05(q, out, kv, cu_seqlens, slots, start_pos, n_seqs: 
     _need(q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16, "attention_prefill_tcgen05: bfloat16 only")
     _need(attention_tcgen05_supports(kv),
           "attention_prefill_tcgen05: needs head_dim 64 or 128 and keys and values of a page side by side")
+    _check_access("attention_prefill_tcgen05", 2, kv, slots, start_pos=start_pos, cu_seqlens=cu_seqlens, n_items=n_seqs)
     _check(_fn("gtg_attention_prefill_tcgen05")(_ptr(q), q.stride(0), q.shape[0], _ptr(out), out.stride(0),
                                                 _ptr(kv.k), _ptr(kv.v), kv.page_stride, kv.k.shape[0],
                                                 _ptr(kv.block_table), kv.table_stride, _ptr(cu_seqlens),
@@ -520,6 +573,7 @@ def attention_decode_bf16(q, out, kv, slots, positions, n_heads: int, scale: flo
           "attention_decode_bf16: bfloat16 only")
     _need(attention_bf16_supports(kv.head_dim),
           f"attention_decode_bf16: head_dim {kv.head_dim} is not a multiple of 16 up to 128")
+    _check_access("attention_decode_bf16", 1, kv, slots, positions, n_items=B)
     if n_splits > 1:
         need = attention_decode_scratch_floats(B, n_heads, kv.head_dim, n_splits)
         _need(scratch is not None and scratch.dtype == torch.float32 and scratch.is_contiguous()

@@ -61,6 +61,10 @@ class Runtime:
     true 32-bit)."""
     device: torch.device
     dtype: torch.dtype
+    # debugging: every kernel that reads the cache through the block table is preceded by a
+    # pass that checks the same indices on the device (ops.checked_access); steps then
+    # synchronise and are not recorded as graphs
+    check_access: bool = False
     _shared: Dict[str, torch.Tensor] = field(default_factory=dict, repr=False)
 
     def matrix(self, t: torch.Tensor, share_as: Optional[str] = None) -> torch.Tensor:
