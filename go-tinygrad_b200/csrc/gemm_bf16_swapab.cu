@@ -1,15 +1,16 @@
-// bfloat16 product for decode batches of 17..64 tokens: C[M,N] = X[M,K] . W[N,K]^T.
+// bfloat16 product for decode batches of 17..128 tokens: C[M,N] = X[M,K] . W[N,K]^T.
 //
 // With this many tokens the work is still reading W once, but a CUDA-core or
 // warp-level kernel would re-read X from L2 or shared memory several times per
 // byte of W.  Here the roles of the operands are swapped on the tensor core:
-// 128 rows of W are the M dimension of tcgen05.mma and the tokens (padded to 64)
-// are its N dimension, so both operands go from shared memory to the tensor core
-// once.  The accumulator [128 features x 64 tokens] lives in TMEM.
+// 128 rows of W are the M dimension of tcgen05.mma and the tokens (padded to 64,
+// or to 128 for more than 64) are its N dimension, so both operands go from
+// shared memory to the tensor core once.  The accumulator [128 features x 64 or
+// 128 tokens] lives in TMEM.
 //
 // One CTA takes one (128-row tile of W, slice of k), two CTAs to an SM.  One
 // thread keeps a ring of four 24 KB stages (a 128 x 64 block of W and the 64 x 64
-// block of X under it) full by TMA -- the weights from before the wait on the
+// block of X under it; three stages of 32 KB with 128 tokens) full by TMA -- the weights from before the wait on the
 // kernel before, the activations after it -- one thread issues the MMAs as the
 // stages land, and four warps move the finished accumulator to shared memory.
 // The slices of a row tile are the CTAs of one thread-block cluster (up to
@@ -25,17 +26,22 @@
 
 namespace {
 constexpr int BR = 128;                       // rows of W per CTA (MMA M)
-constexpr int BT = 64;                        // tokens per CTA (MMA N)
 constexpr int BK = 64;
-constexpr int kStages = 4;                    // ring of k blocks
-constexpr int kWBytes = BR * BK * 2, kXBytes = BT * BK * 2, kBlockBytes = kWBytes + kXBytes;
+constexpr int kWBytes = BR * BK * 2;
 constexpr int kThreads = 192;
-constexpr int kTmemCols = 64;                 // one accumulator: 128 lanes x 64 columns
-constexpr int kPartFloats = BT * BR;          // the accumulator as [token][feature], after the ring is done
 constexpr int kCtasPerSm = 2;                 // what the ring's size lets an SM hold
 constexpr int kMaxSlices = 8;                 // CTAs of a cluster (the portable limit)
-static_assert(kPartFloats * 4 <= kStages * kBlockBytes, "the partial sums reuse the ring");
-constexpr int kSmemBytes = kStages * kBlockBytes + 1024 + 256;
+// What depends on the tokens a CTA takes (BT, the MMA's N: 64, or 128 for batches
+// of 65 to 128): the stage, the ring (about 96 KB either way, so that two CTAs
+// share an SM), the accumulator's TMEM columns.
+template <int BT> struct Tile {
+    static constexpr int kStages = BT == 64 ? 4 : 3;              // ring of k blocks
+    static constexpr int kXBytes = BT * BK * 2, kBlockBytes = kWBytes + kXBytes;
+    static constexpr int kTmemCols = BT;                          // one accumulator: 128 lanes x BT columns
+    static constexpr int kPartFloats = BT * BR;                   // the accumulator as [token][feature], after the ring is done
+    static constexpr int kSmemBytes = kStages * kBlockBytes + 1024 + 256;
+    static_assert(kPartFloats * 4 <= kStages * kBlockBytes, "the partial sums reuse the ring");
+};
 constexpr unsigned kSpinLimit = 1u << 22;
 // The kernels of this library exist twice: as they run, and (kTest) in the form the
 // test of the give-up path launches, whose waits poll a thousand times instead of
@@ -137,10 +143,11 @@ __device__ __forceinline__ float4 remote_ld4(uint32_t addr, uint32_t rank) {
 
 // grid.x = row tiles x slices, clusters of `slices` CTAs along x: CTA rank r of a
 // cluster takes k blocks [r * kb_per, (r + 1) * kb_per) of its row tile.
-template <typename OutT, bool kTest>
+template <typename OutT, int BT, bool kTest>
 __global__ void __launch_bounds__(kThreads)
 swapab_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
               OutT* __restrict__ C, int ldc, int M, int N, int K, int kb_per, int slices, int epi) {
+    constexpr int kStages = Tile<BT>::kStages, kBlockBytes = Tile<BT>::kBlockBytes, kTmemCols = Tile<BT>::kTmemCols;
     extern __shared__ unsigned char smem_raw[];
     const uint32_t base = (smem_addr(smem_raw) + 1023u) & ~1023u;
     unsigned char* aligned = smem_raw + (base - smem_addr(smem_raw));
@@ -362,18 +369,20 @@ int device_sms() {
     return sms;
 }
 
-template <typename OutT, bool kTest>
+template <typename OutT, int BT, bool kTest>
 int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, OutT* C, int ldc, int M, int N, int K,
            int kb_per, int slices, int epilogue, cudaStream_t stream) {
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(swapab_kernel<OutT, kTest>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        cudaError_t e = cudaFuncSetAttribute(swapab_kernel<OutT, BT, kTest>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             Tile<BT>::kSmemBytes);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
     const long long ctas = (long long)((N + BR - 1) / BR) * slices;
     if (ctas > 0x7fffffff) return kErrUnsupported;
-    return launch_chained_cluster(swapab_kernel<OutT, kTest>, dim3((unsigned)ctas), dim3(kThreads), slices, (size_t)kSmemBytes,
+    return launch_chained_cluster(swapab_kernel<OutT, BT, kTest>, dim3((unsigned)ctas), dim3(kThreads), slices,
+                                  (size_t)Tile<BT>::kSmemBytes,
                                   stream, map_w, map_x, C, ldc, M, N, K, kb_per, slices, epilogue);
 }
 }  // namespace
@@ -390,30 +399,33 @@ GTG_API long long gtg_gemm_bf16_swapab_scratch_floats(int M, int N, int K) {
     return 0;
 }
 
-// M <= 64.  epilogue as in gtg_gemm_bf16_tcgen05.  `scratch` is not used and may be null.
+// M <= 128.  epilogue as in gtg_gemm_bf16_tcgen05.  `scratch` is not used and may be null.
 GTG_API int gtg_gemm_bf16_swapab(const void* X, int ldx, const void* W, int ldw, void* C, int ldc,
                                  int out_f32, int M, int N, int K, int epilogue, float* scratch,
                                  cudaStream_t stream) {
     (void)scratch;
     if (M <= 0 || N <= 0) return 0;
-    if (M > BT) return kErrUnsupported;
+    if (M > 128) return kErrUnsupported;
     if (epilogue != 0 && epilogue != 1) return kErrBadArgument;
     if (epilogue == 1 && N % 16 != 0) return kErrUnsupported;
     if (K <= 0 || ldx < K || ldw < K || ldc < (epilogue ? N / 2 : N)) return kErrBadArgument;
     if (K % 8 || ldx % 8 || ldw % 8 || ((uintptr_t)X % 16) || ((uintptr_t)W % 16)) return kErrUnsupported;
     int slices, kb_per;
     plan(N, K, device_sms(), &slices, &kb_per);
+    const int bt = M <= 64 ? 64 : 128;                       // tokens a CTA takes: the MMA's N
     CUtensorMap map_w, map_x;
     int st = make_map(&map_w, W, N, K, ldw, BR);
     if (st != 0) return st;
-    st = make_map(&map_x, X, M, K, ldx, BT);
+    st = make_map(&map_x, X, M, K, ldx, bt);
     if (st != 0) return st;
-    if (g_test_waits) {
-        if (out_f32) return launch<float, true>(map_w, map_x, (float*)C, ldc, M, N, K, kb_per, slices, epilogue, stream);
-        return launch<bf16, true>(map_w, map_x, (bf16*)C, ldc, M, N, K, kb_per, slices, epilogue, stream);
+#define GTG_ARGS(T) map_w, map_x, (T*)C, ldc, M, N, K, kb_per, slices, epilogue, stream
+    if (g_test_waits) {                                      // the give-up test: up to 64 rows
+        if (bt != 64) return kErrUnsupported;
+        return out_f32 ? launch<float, 64, true>(GTG_ARGS(float)) : launch<bf16, 64, true>(GTG_ARGS(bf16));
     }
-    if (out_f32) return launch<float, false>(map_w, map_x, (float*)C, ldc, M, N, K, kb_per, slices, epilogue, stream);
-    return launch<bf16, false>(map_w, map_x, (bf16*)C, ldc, M, N, K, kb_per, slices, epilogue, stream);
+    if (bt == 64) return out_f32 ? launch<float, 64, false>(GTG_ARGS(float)) : launch<bf16, 64, false>(GTG_ARGS(bf16));
+    return out_f32 ? launch<float, 128, false>(GTG_ARGS(float)) : launch<bf16, 128, false>(GTG_ARGS(bf16));
+#undef GTG_ARGS
 }
 
 // ---- test hook --------------------------------------------------------------

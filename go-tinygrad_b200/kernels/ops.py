@@ -320,8 +320,9 @@ def advance(tokens: torch.Tensor, positions: torch.Tensor, steps: torch.Tensor,
 
 
 # ---------------------------------------------------------------- matrix products
-SKINNY_MAX_ROWS = 64          # most rows the weight-streaming kernels take
+SKINNY_MAX_ROWS = 128         # most rows the weight-streaming kernels take (beyond: the prompt-sized product)
 STREAM_MAX_ROWS = 16          # up to here: warp-level MMA fed by bulk copies; beyond: tcgen05 with swapped operands
+WARP_LEVEL_MAX_ROWS = 64      # most rows the warp-level kernel takes when asked for by name
 TILED_KIND = "tcgen05"        # what "auto" uses beyond SKINNY_MAX_ROWS rows
 
 
@@ -339,7 +340,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, kind: str = "aut
     kernel; bfloat16 operands accumulate in float and write bfloat16 or float32.
     `kind` picks the bfloat16 kernel: "auto" (by the number of rows), "skinny"
     (weight streaming, up to 64 rows), "swapab" (weight streaming on tcgen05 with
-    the tokens as the N dimension, up to 64 rows), "tcgen05" (TMA + tensor memory)
+    the tokens as the N dimension, up to 128 rows), "tcgen05" (TMA + tensor memory)
     or "tiled" (warp-level MMA).  epilogue="swiglu" (bfloat16, not "tiled"): w is laid out by
     `interleave_gate_up` and out[M, N/2] = silu(gate) * up, computed from the
     float accumulators."""
@@ -367,7 +368,8 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, kind: str = "aut
               "tcgen05": "gtg_gemm_bf16_tcgen05"}.get(kind)
     _need(symbol is not None, f"linear: unknown kind {kind!r}")
     if kind in ("skinny", "swapab"):
-        _need(M <= SKINNY_MAX_ROWS, f"linear: the weight-streaming kernels take at most {SKINNY_MAX_ROWS} rows")
+        most = WARP_LEVEL_MAX_ROWS if kind == "skinny" else SKINNY_MAX_ROWS
+        _need(M <= most, f"linear: the weight-streaming kernel {kind!r} takes at most {most} rows")
     out_f32 = 1 if out.dtype == torch.float32 else 0
     if kind == "tiled":
         _need(epilogue == "none", "linear: the warp-level kernel has no fused epilogue")

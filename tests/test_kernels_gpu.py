@@ -255,9 +255,9 @@ def test_linear_float32_does_not_depend_on_the_batch():
 @pytest.mark.parametrize("M,N,K", [(1, 17, 8), (5, 96, 264), (64, 391, 96), (130, 130, 40),
                                    (257, 1000, 2048), (3, 2048, 8192), (8, 6144, 2048),
                                    (300, 144, 96), (9, 50, 1000), (17, 33, 72), (40, 1001, 2056),
-                                   (33, 16, 8200)])
+                                   (33, 16, 8200), (65, 200, 136), (128, 2048, 2048), (100, 1000, 8192)])
 def test_linear_bfloat16(out_dtype, kind, M, N, K):
-    if kind in ("skinny", "swapab") and M > ops.SKINNY_MAX_ROWS:
+    if (kind == "skinny" and M > ops.WARP_LEVEL_MAX_ROWS) or (kind == "swapab" and M > ops.SKINNY_MAX_ROWS):
         pytest.skip("more rows than the weight-streaming kernels take")
     x, w = rnd(M, K, dtype=torch.bfloat16, seed=1), rnd(N, K, dtype=torch.bfloat16, seed=2)
     out = torch.empty(M, N, dtype=out_dtype, device=DEV)
@@ -271,7 +271,8 @@ def test_linear_bfloat16(out_dtype, kind, M, N, K):
 
 
 @pytest.mark.parametrize("M,N,K", [(40, 38000, 136), (64, 19100, 520), (17, 300, 16384), (64, 2048, 2048), (33, 6144, 2048),
-                                   (64, 2048, 8192), (20, 16384, 2048), (64, 130, 520), (50, 4096, 14336)])
+                                   (64, 2048, 8192), (20, 16384, 2048), (64, 130, 520), (50, 4096, 14336),
+                                   (65, 6144, 2048), (128, 2048, 8192), (97, 391, 264), (120, 16384, 2048)])
 def test_linear_swapab_slices_meet_in_a_cluster(M, N, K):
     """One CTA per (128-row tile, slice of k): more CTAs than the device holds at once
     (several waves), clusters of two, four and eight slices whose partial sums meet
@@ -323,10 +324,10 @@ def test_linear_skinny_long_rows_split_over_a_cluster(M, N, K):
 
 @pytest.mark.parametrize("kind", ["skinny", "swapab", "tcgen05"])
 @pytest.mark.parametrize("M,I,K", [(1, 8, 96), (8, 264, 96), (16, 1000, 2048), (33, 24, 8192), (64, 264, 264),
-                                   (200, 264, 96), (130, 1000, 2048)])
+                                   (200, 264, 96), (130, 1000, 2048), (96, 8192, 2048), (128, 264, 8192)])
 def test_linear_with_fused_swiglu(kind, M, I, K):
     """The product over interleaved gate/up rows writes silu(gate) * up directly."""
-    if kind in ("skinny", "swapab") and M > ops.SKINNY_MAX_ROWS:
+    if (kind == "skinny" and M > ops.WARP_LEVEL_MAX_ROWS) or (kind == "swapab" and M > ops.SKINNY_MAX_ROWS):
         pytest.skip("more rows than the weight-streaming kernels take")
     x = rnd(M, K, dtype=torch.bfloat16, seed=1, scale=0.5)
     gate, up = rnd(I, K, dtype=torch.bfloat16, seed=2, scale=0.2), rnd(I, K, dtype=torch.bfloat16, seed=3, scale=0.2)
@@ -341,8 +342,8 @@ def test_linear_with_fused_swiglu(kind, M, I, K):
     assert ops.bounded_wait_failures() == 0
 
 
-@pytest.mark.parametrize("M,N,K", [(65, 64, 64), (2048, 2048, 2048), (300, 144, 96), (130, 1000, 2056), (257, 2048, 8192),
-                                   (128, 48, 64), (1000, 391, 264)])
+@pytest.mark.parametrize("M,N,K", [(129, 64, 64), (2048, 2048, 2048), (300, 144, 96), (130, 1000, 2056), (257, 2048, 8192),
+                                   (192, 48, 64), (1000, 391, 264)])
 def test_linear_adds_to_a_residual_stream(M, N, K):
     """residual += bfloat16(x . w^T) by tensor reductions in the product's epilogue:
     bit for bit what the product into a bfloat16 update, then the addition, give;
@@ -366,7 +367,8 @@ def test_linear_adds_to_a_residual_stream(M, N, K):
 
 
 def test_linear_does_not_add_to_a_residual_stream_what_it_cannot_serve():
-    for M, N, K, dt in ((64, 64, 64, torch.bfloat16), (200, 64, 64, torch.float32), (200, 64, 12, torch.bfloat16)):
+    for M, N, K, dt in ((64, 64, 64, torch.bfloat16), (128, 64, 64, torch.bfloat16), (200, 64, 64, torch.float32),
+                        (200, 64, 12, torch.bfloat16)):
         x, w = rnd(M, K, dtype=dt, seed=1), rnd(N, K, dtype=dt, seed=2)
         residual = rnd(M, N, seed=3)
         before = residual.clone()
