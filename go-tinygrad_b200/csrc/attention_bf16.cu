@@ -264,7 +264,7 @@ attention_decode_kernel(const bf16* __restrict__ q, int ldq, bf16* __restrict__ 
                         const int* __restrict__ slots, const int* __restrict__ positions,
                         int n_heads, int n_kv, int hd, float scale, int window,
                         int n_splits, float* __restrict__ part_o, float* __restrict__ part_ml,
-                        const DecodeRope rope) {
+                        const DecodeRope rope, int chunk_pages) {
     chain_release();
     constexpr int kDecodeStages = decode_stages<DP>();
     constexpr int CPR = DP / 8;
@@ -289,9 +289,24 @@ attention_decode_kernel(const bf16* __restrict__ q, int ldq, bf16* __restrict__ 
     const int k_min = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
     const int p_first = k_min / kPageTokens, p_last = pos / kPageTokens;
     const int n_pages = p_last - p_first + 1;
-    const int per_split = (n_pages + n_splits - 1) / n_splits;
+    // With `chunk_pages` (the pages one split was planned to take) a sequence is cut into
+    // as many equal parts as give parts of about that size, at most n_splits: a short
+    // sequence costs few blocks of full size instead of as many small ones as the
+    // longest.  With chunk_pages 0 every sequence is cut into n_splits parts.
+    const int my_splits = chunk_pages > 0 ? min(n_splits, (n_pages + chunk_pages - 1) / chunk_pages) : n_splits;
+    const int per_split = (n_pages + my_splits - 1) / my_splits;
     const int p_begin = p_first + split * per_split;
-    const int p_end = min(p_last + 1, p_begin + per_split);      // exclusive
+    const int p_end = split < my_splits ? min(p_last + 1, p_begin + per_split) : p_begin;    // exclusive
+    if (n_splits > 1 && p_begin >= p_end) {
+        // nothing of this sequence falls to this split: say so (the merge passes over it) and leave
+        chain_wait();
+        for (int r = threadIdx.x; r < rows; r += blockDim.x) {
+            const size_t pidx = ((size_t)b * n_heads + h0 + r) * n_splits + split;
+            part_ml[pidx * 2] = -INFINITY;
+            part_ml[pidx * 2 + 1] = 0.f;
+        }
+        return;
+    }
 
     auto load_page = [&](int stage, int p) {
         const size_t base = (size_t)table[p] * page_stride + (size_t)kvh * kPageTokens * hd;
@@ -521,7 +536,9 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_o, const
     float acc = 0.f, L = 0.f;
     for (int s = 0; s < n_splits; ++s) {
         const size_t pidx = (size_t)bh * n_splits + s;
-        const float f = exp2f(part_ml[pidx * 2] - Mu);
+        const float m = part_ml[pidx * 2];
+        if (m == -INFINITY) continue;              // a split without keys wrote no sums
+        const float f = exp2f(m - Mu);
         acc += f * part_o[pidx * DP + d];
         L += f * part_ml[pidx * 2 + 1];
     }
@@ -561,7 +578,7 @@ int launch_decode(const bf16* q, int ldq, bf16* out, int ldo, const bf16* kc, co
                   long long page_stride, const int* block_table, int table_stride,
                   const int* slots, const int* positions, int B, int n_heads, int n_kv, int hd,
                   float scale, int window, int n_splits, float* part_o, float* part_ml,
-                  cudaStream_t stream, const DecodeRope rope = DecodeRope{}) {
+                  cudaStream_t stream, const DecodeRope rope = DecodeRope{}, int chunk_pages = 0) {
     static bool configured = false;
     const int smem = decode_smem_bytes<DP>();
     if (!configured) {
@@ -574,7 +591,7 @@ int launch_decode(const bf16* q, int ldq, bf16* out, int ldo, const bf16* kc, co
     dim3 grid(n_splits, n_kv * ((group + 15) / 16), B);
     int st = launch_chained(attention_decode_kernel<DP>, grid, dim3(128), smem, stream, q, ldq, out, ldo, kc, vc,
                             page_stride, block_table, table_stride, slots, positions, n_heads, n_kv, hd, scale,
-                            window, n_splits, part_o, part_ml, rope);
+                            window, n_splits, part_o, part_ml, rope, n_splits > 1 ? chunk_pages : 0);
     if (st != 0 || n_splits == 1) return st;
     return launch_chained(attention_combine_kernel<DP>, dim3(B * n_heads), dim3(DP), 0, stream,
                           (const float*)part_o, (const float*)part_ml, out, ldo, n_heads, hd, n_splits);
@@ -607,17 +624,29 @@ static int decode_block_slots() {
     return cached[dev];
 }
 
-// Blocks run in waves of what the device holds at once: a count just above a
-// whole number of waves leaves the last wave nearly empty, and a split of very
-// few pages pays its fixed cost (query load, merge, partial write) for little
-// work.  The choice depends on the batch, on the longest sequence and on the
-// window only, never on the data.  A layer with a window reads the pages its
-// window spans, however long the sequence is.  Returns the split count (>= 1),
-// or a negative error code.
-GTG_API int gtg_attention_decode_plan(int B, int n_heads, int n_kv, int hd, int max_kv_len, int window) {
+// Into how many blocks to split the keys of a (sequence, key/value head), for a
+// batch whose longest sequence has max_kv_len keys and whose sequences have
+// total_kv_len keys together (0: take all B as long as the longest).  A block
+// costs a fixed latency (its first pages' round trip, the merge of its warps, its
+// partial result) and then a page time each; blocks run in waves of what the
+// device holds at once.  The estimate below is the time of blocks of `chunk`
+// pages (side by side while the device holds them all, their times added up over
+// its slots beyond that), or the time the memory needs for all keys, whichever
+// is longer; the chunk with the least estimate wins.  A sequence then takes
+// ceil(its pages / chunk) splits (the kernel works that out from its length), so
+// the choice depends on the batch's lengths and the window only, never on the
+// data.  A layer with a window reads the pages its window spans.  Returns the
+// split count for the longest sequence (1 to 64), or a negative error code;
+// *chunk_pages: the pages a split takes.  A sequence that has outgrown
+// splits x chunk pages (a recorded step replayed while its sequences grow) is cut
+// into `splits` parts of more pages each: the plan is a matter of speed only.
+GTG_API int gtg_attention_decode_plan(int B, int n_heads, int n_kv, int hd, int max_kv_len, long long total_kv_len,
+                                      int window, int* chunk_pages) {
+    if (chunk_pages) *chunk_pages = 0;
     if (B <= 0 || n_heads <= 0 || n_kv <= 0 || n_heads % n_kv != 0) return kErrBadArgument;
     int slots = 0;
-    switch (padded_head_dim(hd)) {
+    const int dp = padded_head_dim(hd);
+    switch (dp) {
         case 16: slots = decode_block_slots<16>(); break;
         case 32: slots = decode_block_slots<32>(); break;
         case 64: slots = decode_block_slots<64>(); break;
@@ -625,26 +654,56 @@ GTG_API int gtg_attention_decode_plan(int B, int n_heads, int n_kv, int hd, int 
         default: return kErrUnsupported;
     }
     if (slots <= 0) return 1;
-    const long long base = (long long)B * n_kv * ((n_heads / n_kv + 15) / 16);
-    int keys = max_kv_len > 1 ? max_kv_len : 1;
-    int pages = (keys + kPageTokens - 1) / kPageTokens;
-    if (window > 0 && window < keys) {
-        // `window` consecutive keys touch at most this many pages
-        const int span = (window + kPageTokens - 2) / kPageTokens + 1;
-        if (span < pages) pages = span;
+    const long long units = (long long)n_kv * ((n_heads / n_kv + 15) / 16);      // blocks per split of one sequence
+    auto span = [&](long long keys) {                                              // pages that hold `keys` keys
+        long long pages = (keys + kPageTokens - 1) / kPageTokens;
+        if (window > 0 && window < keys) {
+            const long long w = (window + kPageTokens - 2) / kPageTokens + 1;      // `window` consecutive keys touch at most this many
+            if (w < pages) pages = w;
+        }
+        return pages < 1 ? 1 : pages;
+    };
+    const int max_pages = (int)span(max_kv_len > 1 ? max_kv_len : 1);
+    long long mean_keys = total_kv_len > 0 ? (total_kv_len + B - 1) / B : max_kv_len;
+    if (mean_keys > max_kv_len) mean_keys = max_kv_len;
+    const double mean_pages = (double)span(mean_keys > 1 ? mean_keys : 1);
+    // measured on a B200: about 3.5 us before a block's first page is in use; a block
+    // keeps three pages in flight over that latency, 1.15 us a page; the memory's own
+    // time for all keys, once enough blocks run to saturate it
+    const double kFixedUs = 3.5, kPageUs = 1.15, kMergeUs = 3.0, kBytesPerUs = 6.0e6;
+    const double page_bytes = 2.0 * kPageTokens * dp * 2;
+    const double memory_us = (double)B * mean_pages * units * page_bytes / kBytesPerUs;
+    int best_chunk = max_pages;
+    double best = 1e30;
+    for (int chunk = 1; chunk <= max_pages; ++chunk) {
+        const int splits = (max_pages + chunk - 1) / chunk;
+        if (splits > 64) continue;
+        // blocks of the batch: a sequence of the mean length takes about mean / chunk + 1/2 splits
+        const double per_seq = mean_pages >= max_pages ? (double)splits
+                             : mean_pages / chunk < 1.0 ? 1.0 : (mean_pages / chunk + 0.5);
+        const double blocks = (double)B * units * per_seq;
+        const int longest = (max_pages + splits - 1) / splits;                     // pages of the longest sequence's splits
+        const double longest_us = kFixedUs + kPageUs * longest;
+        // What the device holds at once runs side by side.  Beyond that: blocks of one
+        // length run in whole waves; blocks of many lengths (the long ones started first)
+        // fill the slots evenly, their times add up over the slots and the last ends half
+        // a typical block after the rest -- unless one long block outlasts all that.
+        double us;
+        if (blocks <= slots) {
+            us = longest_us;
+        } else if (mean_pages >= max_pages) {
+            us = (double)(((long long)blocks + slots - 1) / slots) * longest_us;
+        } else {
+            const double typical_us = kFixedUs + kPageUs * (mean_pages < chunk ? mean_pages : chunk);
+            us = (blocks * kFixedUs + kPageUs * B * units * mean_pages) / slots + 0.5 * typical_us;
+            if (us < longest_us) us = longest_us;
+        }
+        if (us < memory_us) us = memory_us;
+        if (splits > 1) us += kMergeUs;
+        if (us < best - 1e-9) { best = us; best_chunk = chunk; }
     }
-    int best = 1;
-    double best_score = -1.0;
-    const int most = pages < 64 ? pages : 64;
-    for (int s = 1; s <= most; ++s) {
-        const long long blocks = base * s;
-        const long long waves = (blocks + slots - 1) / slots;
-        const int per_split = (pages + s - 1) / s;
-        double score = (double)blocks / (double)(waves * slots) * per_split / (per_split + 1.0);
-        if (s > 1) score *= 0.93;             // the partial results and the kernel that merges them
-        if (score > best_score + 1e-9) { best = s; best_score = score; }
-    }
-    return best;
+    if (chunk_pages) *chunk_pages = best_chunk;
+    return (max_pages + best_chunk - 1) / best_chunk;
 }
 
 // Floats of scratch a decode call needs: (part_o, part_ml) for `n_splits` > 1.
@@ -675,6 +734,12 @@ GTG_API int gtg_attention_prefill_bf16(const void* q, int ldq, void* out, int ld
 #undef GTG_ARGS
 }
 
+// For both decode entry points: with `chunk_pages` (0, or what gtg_attention_decode_plan
+// gave) a sequence is cut into as many equal parts as give parts of about that many
+// pages, at most n_splits, instead of into n_splits parts whatever its length.
+// Blocks are handed out sequence by sequence in batch order: a caller whose
+// sequences differ much in length does well to put the long ones first.
+//
 // Decode attention that also does what rope_kv_store does for a decode step (see
 // DecodeRope): q, k_new and v_new are the unrotated columns of the projection's
 // output (rows of ldq elements); cos_sin float [B][hd/2][2] or null for no rotation;
@@ -686,7 +751,8 @@ GTG_API int gtg_attention_decode_rope_bf16(const void* q, int ldq, void* out, in
                                            const int* slots, const int* positions,
                                            int B, int n_heads, int n_kv, int hd, float scale, int window,
                                            int n_splits, float* scratch, const float* cos_sin,
-                                           const void* k_new, const void* v_new, int store, cudaStream_t stream) {
+                                           const void* k_new, const void* v_new, int store,
+                                           int chunk_pages, cudaStream_t stream) {
     if (B <= 0) return 0;
     if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv != 0 || ldq % 8 != 0 || n_splits < 1) return kErrBadArgument;
     if (k_new != nullptr && v_new == nullptr) return kErrBadArgument;
@@ -702,7 +768,7 @@ GTG_API int gtg_attention_decode_rope_bf16(const void* q, int ldq, void* out, in
     if (k_new != nullptr && store) { rope.kc_w = (bf16*)kc; rope.vc_w = (bf16*)vc; }
 #define GTG_ARGS (const bf16*)q, ldq, (bf16*)out, ldo, (const bf16*)kc, (const bf16*)vc, page_stride, \
         block_table, table_stride, slots, positions, B, n_heads, n_kv, hd, scale, window, n_splits, part_o, part_ml, \
-        stream, rope
+        stream, rope, chunk_pages
     switch (dp) {
         case 16: return launch_decode<16>(GTG_ARGS);
         case 32: return launch_decode<32>(GTG_ARGS);
@@ -718,7 +784,7 @@ GTG_API int gtg_attention_decode_bf16(const void* q, int ldq, void* out, int ldo
                                       const int* block_table, int table_stride,
                                       const int* slots, const int* positions,
                                       int B, int n_heads, int n_kv, int hd, float scale, int window,
-                                      int n_splits, float* scratch, cudaStream_t stream) {
+                                      int n_splits, float* scratch, int chunk_pages, cudaStream_t stream) {
     if (B <= 0) return 0;
     if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv != 0 || ldq % 8 != 0 || n_splits < 1) return kErrBadArgument;
     const int dp = padded_head_dim(hd);
@@ -727,7 +793,8 @@ GTG_API int gtg_attention_decode_bf16(const void* q, int ldq, void* out, int ldo
     float* part_o = scratch;
     float* part_ml = scratch ? scratch + (size_t)B * n_heads * n_splits * dp : nullptr;
 #define GTG_ARGS (const bf16*)q, ldq, (bf16*)out, ldo, (const bf16*)kc, (const bf16*)vc, page_stride, \
-        block_table, table_stride, slots, positions, B, n_heads, n_kv, hd, scale, window, n_splits, part_o, part_ml, stream
+        block_table, table_stride, slots, positions, B, n_heads, n_kv, hd, scale, window, n_splits, part_o, part_ml, stream, \
+        DecodeRope{}, chunk_pages
     switch (dp) {
         case 16: return launch_decode<16>(GTG_ARGS);
         case 32: return launch_decode<32>(GTG_ARGS);

@@ -15,8 +15,9 @@ random draw) and the sampled tokens.  Two ways to drive it:
 The first run of a batch executes eagerly (it loads and configures kernels,
 which a capture must not do), the second is captured.  A recording fixes what
 the parts chose from the batch's longest sequence (into how many blocks the
-keys of a sequence are split): it is made for a length a little ahead of the
-current one and made again when the sequences have outgrown it, or when the
+keys of a sequence are split; a sequence that outgrows the plan is still computed
+right, in larger parts): it is made again when the sequences have outgrown it by
+a sixth, or when the
 object is given much shorter sequences (`rebind`).  Which sequences the batch
 holds is data (slots and request ids in a device buffer), so one recording
 serves every set of as many sequences.
@@ -66,8 +67,7 @@ class DecodeBatch:
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self._runs = 0
         self._planned_len = 0                             # the longest sequence the recording was made for
-
-    AHEAD = 1.2                                           # a recording is planned for this much more than the current length
+        self._planned_total = 0                           # ... and all sequences' lengths together
 
     def rebind(self, slots: Sequence[int], requests: Sequence[int]) -> None:
         """The same number of sequences, other slots and request ids: the
@@ -93,7 +93,7 @@ class DecodeBatch:
         return StepContext(rt=self.model.rt, n_tokens=self.B, n_seqs=self.B, tokens=self.tokens,
                            positions=self.positions, token_seq=self.token_seq, cu_seqlens=self.cu,
                            slots=self.slot_ids, start_pos=self.positions, max_q_len=1,
-                           max_kv_len=self._planned_len, is_decode=True,
+                           max_kv_len=self._planned_len, is_decode=True, total_kv_len=self._planned_total,
                            step=self.model.steps_run, op_hook=self.model.op_hook)
 
     def _forward(self) -> None:
@@ -107,18 +107,19 @@ class DecodeBatch:
         """Run the step for the state now on the device; grows every sequence by one."""
         self.cache.reserve_many([(s, self.cache.length(s) + 1) for s in self.slots])
         self.cache.flush_tables()
-        longest = max(self.cache.length(s) for s in self.slots) + 1
+        lengths = [self.cache.length(s) + 1 for s in self.slots]
+        longest = max(lengths)
         if self.model.op_hook is not None or self.model.rt.check_access:   # a hook listens or checks run: in the open
             self.graph = None
-            self._planned_len = max(longest, int(longest * self.AHEAD))
+            self._planned_len, self._planned_total = longest, sum(lengths)
             self._forward()
             self._finish_step()
             return
         if self.graph is None or not self.use_graph:
-            self._planned_len = max(longest, int(longest * self.AHEAD))
+            self._planned_len, self._planned_total = longest, sum(lengths)
         elif longest > self._planned_len * 1.17 or longest * 2 < self._planned_len:
             self.graph = None                             # outgrown (or far too long a plan): record again
-            self._planned_len = max(longest, int(longest * self.AHEAD))
+            self._planned_len, self._planned_total = longest, sum(lengths)
         if not self.use_graph:
             self._forward()
         elif self.graph is not None:

@@ -135,6 +135,7 @@ def build_context(model: Model, cache: Cache, entries: Sequence[StepEntry]):
         max_q_len=max(len(e.tokens) for e in entries),
         max_kv_len=max(s + len(e.tokens) for s, e in zip(start, entries)),
         is_decode=all(len(e.tokens) == 1 for e in entries),
+        total_kv_len=sum(s + len(e.tokens) for s, e in zip(start, entries)),
         step=model.steps_run, op_hook=model.op_hook,
     )
     rows = take(n_want) if n_want else None

@@ -48,13 +48,13 @@ _SIGNATURES = {
                                                   _I, _I, _I, _I, _F, _I, _P]),
     "gtg_attention_bf16_supports": ("attention_bf16", [_I]),
     "gtg_attention_decode_scratch_floats": ("attention_bf16", [_I, _I, _I, _I]),
-    "gtg_attention_decode_plan": ("attention_bf16", [_I, _I, _I, _I, _I, _I]),
+    "gtg_attention_decode_plan": ("attention_bf16", [_I, _I, _I, _I, _I, _L, _I, _P]),
     "gtg_attention_prefill_bf16": ("attention_bf16", [_P, _I, _P, _I, _P, _P, _L, _P, _I, _P, _P, _P,
                                                       _I, _I, _I, _I, _I, _F, _I, _P]),
     "gtg_attention_decode_rope_bf16": ("attention_bf16", [_P, _I, _P, _I, _P, _P, _L, _P, _I, _P, _P,
-                                                          _I, _I, _I, _I, _F, _I, _I, _P, _P, _P, _P, _I, _P]),
+                                                          _I, _I, _I, _I, _F, _I, _I, _P, _P, _P, _P, _I, _I, _P]),
     "gtg_attention_decode_bf16": ("attention_bf16", [_P, _I, _P, _I, _P, _P, _L, _P, _I, _P, _P,
-                                                     _I, _I, _I, _I, _F, _I, _I, _P, _P]),
+                                                     _I, _I, _I, _I, _F, _I, _I, _P, _I, _P]),
     "gtg_attention_tcgen05_supports": ("attention_tcgen05", [_I]),
     "gtg_attention_tcgen05_status": ("attention_tcgen05", []),
     "gtg_attention_prefill_tcgen05": ("attention_tcgen05", [_P, _I, _I, _P, _I, _P, _P, _L, _I, _P, _I, _P, _P, _P,
@@ -544,16 +544,22 @@ def attention_prefill_tcgen05(q, out, kv, cu_seqlens, slots, start_pos, n_seqs: 
 
 
 def attention_decode_plan(n_seqs: int, n_heads: int, n_kv_heads: int, head_dim: int, max_kv_len: int,
-                          window: int = 0) -> int:
-    """Into how many thread blocks `attention_decode_bf16` should split the keys of
-    one (sequence, key/value head): the library weighs whole waves of blocks on
-    this device (its multiprocessor count and the kernel's own occupancy) against
-    the fixed cost of a split.  It depends on the batch, the longest sequence and
-    the window, never on the data."""
-    n = int(_fn("gtg_attention_decode_plan")(n_seqs, n_heads, n_kv_heads, head_dim, int(max_kv_len), int(window)))
+                          window: int = 0, total_kv_len: int = 0):
+    """(n_splits, chunk_pages) for `attention_decode_bf16`: into how many thread
+    blocks the keys of the longest sequence's (sequence, key/value head) pairs are
+    split, and how many pages one split takes (a shorter sequence then takes as
+    many splits as its own pages need).  `total_kv_len` is the batch's keys
+    altogether (0: all sequences as long as the longest).  The library estimates,
+    for every chunk size, the waves of blocks on this device (its multiprocessor
+    count and the kernel's own occupancy, from the runtime) and the time the
+    memory needs, and takes the least.  The choice depends on the batch's lengths
+    and the window, never on the data."""
+    chunk = c_int(0)
+    n = int(_fn("gtg_attention_decode_plan")(n_seqs, n_heads, n_kv_heads, head_dim, int(max_kv_len),
+                                             int(total_kv_len), int(window), ctypes.byref(chunk)))
     if n < 1:
         raise KernelError(f"attention_decode_plan: {_CODES.get(n, n)}")
-    return n
+    return n, int(chunk.value)
 
 
 def attention_decode_scratch_floats(n_seqs: int, n_heads: int, head_dim: int, n_splits: int) -> int:
@@ -561,16 +567,23 @@ def attention_decode_scratch_floats(n_seqs: int, n_heads: int, head_dim: int, n_
 
 
 def attention_decode_bf16(q, out, kv, slots, positions, n_heads: int, scale: float, window: int,
-                          n_splits: int, scratch: Optional[torch.Tensor], unrotated=None) -> None:
+                          n_splits: int, scratch: Optional[torch.Tensor], unrotated=None,
+                          chunk_pages: int = 0) -> None:
     """Attention of one new token per sequence over the cache (keys split over
     `n_splits` thread blocks per head group).  Normally q is rotated and the new
     keys and values are in the cache (`rope_kv_store`).  With
     unrotated=(cos_sin, k_new, v_new, store) the kernel does that work itself: q
     and k_new come as the projection wrote them, cos_sin float32 [B, hd/2, 2] or
     None rotates them, and the new key and value are attended to and, if `store`,
-    written to the cache; k_new None for a layer that reads another's cache."""
+    written to the cache; k_new None for a layer that reads another's cache.
+    With `chunk_pages` (from `attention_decode_plan`; 0: every sequence is cut into
+    n_splits equal parts) a sequence is cut into as many equal parts as give parts
+    of about that many pages, at most n_splits: shorter sequences take fewer splits.
+    Blocks start sequence by sequence in batch order: with very unequal lengths, put
+    the long sequences first."""
     _rows2d(q, "attention: q"); _rows2d(out, "attention: out")
     B = q.shape[0]
+    _need(chunk_pages >= 0, "attention_decode_bf16: chunk_pages must not be negative")
     _need(q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and kv.k.dtype == torch.bfloat16,
           "attention_decode_bf16: bfloat16 only")
     _need(attention_bf16_supports(kv.head_dim),
@@ -595,14 +608,16 @@ def attention_decode_bf16(q, out, kv, slots, positions, n_heads: int, scale: flo
             _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(kv.k), _ptr(kv.v), kv.page_stride,
             _ptr(kv.block_table), kv.table_stride, _ptr(slots), _ptr(positions), B, n_heads, kv.n_kv_heads,
             kv.head_dim, float(scale), int(window), int(n_splits), _ptr(scratch), _ptr(cos_sin),
-            _ptr(k_new), _ptr(v_new) if k_new is not None else None, 1 if store else 0, _stream()),
+            _ptr(k_new), _ptr(v_new) if k_new is not None else None, 1 if store else 0,
+            int(chunk_pages), _stream()),
             "attention_decode_bf16")
         return
     _check(_fn("gtg_attention_decode_bf16")(_ptr(q), q.stride(0), _ptr(out), out.stride(0),
                                             _ptr(kv.k), _ptr(kv.v), kv.page_stride, _ptr(kv.block_table),
                                             kv.table_stride, _ptr(slots), _ptr(positions), B, n_heads,
                                             kv.n_kv_heads, kv.head_dim, float(scale), int(window),
-                                            int(n_splits), _ptr(scratch), _stream()), "attention_decode_bf16")
+                                            int(n_splits), _ptr(scratch), int(chunk_pages), _stream()),
+           "attention_decode_bf16")
 
 
 # ------------------------------------------------------------------------ sampling

@@ -107,6 +107,7 @@ class StepContext:
     max_q_len: int              # longest run of new tokens in the batch
     max_kv_len: int             # longest sequence after this step
     is_decode: bool             # every sequence brings exactly one token
+    total_kv_len: int = 0       # all sequences' lengths after this step, added up (0: not known)
     shared: Dict[Any, Any] = field(default_factory=dict)   # per-step values parts share (rotary tables)
     update_into: Optional["ResidualStream"] = None   # set by a block around a part's forward: see emit_update
     step: int = 0               # which step of the model this is (counted by the model; for `op_hook`)

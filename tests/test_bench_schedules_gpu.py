@@ -60,6 +60,11 @@ def decode_reference(q, k, v, n_heads, n_kv, scale):
 
 
 # ----------------------------------------------------- decode attention, 8,192 keys
+def lens_for(n_seqs):
+    """Tokens already in the cache: the new token at a page's last row, its first row, in between."""
+    return [8191, 8128, 8127, 8000][:n_seqs] + [int(x) for x in np.random.default_rng(1).integers(7000, 8192, max(0, n_seqs - 4))]
+
+
 @pytest.mark.parametrize("rotate_and_store", [False, True])
 @pytest.mark.parametrize("n_seqs", [1, 8, 64])
 @pytest.mark.parametrize("model_heads,n_heads,n_kv,hd", [((32, 32), 8, 8, 64), ((32, 8), 16, 4, 128)])
@@ -70,13 +75,13 @@ def test_decode_attention_over_8192_keys(model_heads, n_heads, n_kv, hd, n_seqs,
     8,192 keys stay small).  In every sequence one key far from the end and one in
     the middle are made to dominate some heads' queries; the new token sits at a
     page's last row, its first row, or in between."""
-    splits = ops.attention_decode_plan(n_seqs, model_heads[0], model_heads[1], hd, 8192, 0)
-    assert 1 <= splits <= 64
+    splits, chunk = ops.attention_decode_plan(n_seqs, model_heads[0], model_heads[1], hd, 8192, 0, sum(lens_for(n_seqs)) + n_seqs)
+    assert 1 <= splits <= 64 and (splits - 1) * chunk < 128 <= splits * chunk
     if n_seqs == 1:
         assert splits > 4            # one sequence alone has to be cut to fill the device
     cache = scattered_cache(n_kv, hd, n_seqs, 128)
     scale = 1.0 / math.sqrt(hd)
-    lens = [8191, 8128, 8127, 8000][:n_seqs] + [int(x) for x in np.random.default_rng(1).integers(7000, 8192, max(0, n_seqs - 4))]
+    lens = lens_for(n_seqs)
     slots = [cache.open_sequence() for _ in range(n_seqs)][::-1]
     group = n_heads // n_kv
     qs, wants, new_kv = [], [], []
@@ -108,13 +113,14 @@ def test_decode_attention_over_8192_keys(model_heads, n_heads, n_kv, hd, n_seqs,
         qkv = torch.cat([torch.stack(qs), torch.stack([a for a, _ in new_kv]), torch.stack([b for _, b in new_kv])], dim=1)
         qd, kd = n_heads * hd, n_kv * hd
         ops.attention_decode_bf16(qkv[:, :qd], out, kv, slot_t, positions, n_heads, scale, 0, splits, scratch,
-                                  unrotated=(None, qkv[:, qd:qd + kd], qkv[:, qd + kd:], True))
+                                  unrotated=(None, qkv[:, qd:qd + kd], qkv[:, qd + kd:], True), chunk_pages=chunk)
         for b, t0 in enumerate(lens):                           # and the new token is in the cache afterwards
             page = int(cache.groups[0].table_host[slots[b]][t0 // 64])
             assert torch.equal(kv.k[page, :, t0 % 64, :].reshape(-1), new_kv[b][0])
             assert torch.equal(kv.v[page, :, t0 % 64, :].reshape(-1), new_kv[b][1])
     else:
-        ops.attention_decode_bf16(torch.stack(qs), out, kv, slot_t, positions, n_heads, scale, 0, splits, scratch)
+        ops.attention_decode_bf16(torch.stack(qs), out, kv, slot_t, positions, n_heads, scale, 0, splits, scratch,
+                                  chunk_pages=chunk)
     torch.testing.assert_close(out.float(), torch.stack(wants), rtol=2e-2, atol=2e-2)
     # the engineered heads really saw their key: their output is that key's value, nearly
     for b in (0, n_seqs - 1):

@@ -516,6 +516,41 @@ def test_attention_decode_bf16(n_heads, n_kv, hd, window, splits):
     torch.testing.assert_close(out.float(), want, rtol=2e-2, atol=2e-2)
 
 
+@pytest.mark.parametrize("n_heads,n_kv,hd", [(4, 2, 16), (8, 8, 64), (6, 2, 128)])
+@pytest.mark.parametrize("window", [0, 100])
+@pytest.mark.parametrize("splits,chunk", [(4, 3), (12, 1), (2, 4), (3, 2)])
+def test_attention_decode_with_splits_sized_by_a_chunk_of_pages(n_heads, n_kv, hd, window, splits, chunk):
+    """Sequences of very unequal lengths cut into parts of about `chunk` pages: short
+    sequences leave splits without keys (the merge must pass over what those never
+    wrote: the scratch is full of NaN), and a sequence longer than splits x chunk
+    pages is cut into `splits` parts."""
+    lens_before = [0, 63, 64, 700, 129, 450]
+    cache, q, want, m, scale = attention_case(torch.bfloat16, n_heads, n_kv, hd, lens_before,
+                                              [1] * len(lens_before), window)
+    n = ops.attention_decode_scratch_floats(len(lens_before), n_heads, hd, splits)
+    out = torch.full_like(q, float("nan"))
+    scratch = torch.full((n,), float("nan"), dtype=torch.float32, device=DEV)
+    ops.attention_decode_bf16(q, out, cache.handles[0].kv, m["slots"], m["positions"], n_heads, scale,
+                              window, splits, scratch, chunk_pages=chunk)
+    torch.testing.assert_close(out.float(), want, rtol=2e-2, atol=2e-2)
+
+
+def test_the_decode_plan_follows_the_batch_not_the_data():
+    """One long sequence alone is cut into many parts; many sequences are not cut at
+    all; a batch of short sequences beside one long one gets a chunk that the short
+    ones fit into whole; a window bounds the pages whatever the length."""
+    one, chunk1 = ops.attention_decode_plan(1, 32, 32, 64, 8192, 0, 8192)
+    assert one > 4 and (one - 1) * chunk1 < 128 <= one * chunk1
+    many, _ = ops.attention_decode_plan(64, 32, 32, 64, 2048, 0, 64 * 1100)
+    assert many == 1                                      # 2,048 blocks fill the device without a cut
+    mixed, chunk = ops.attention_decode_plan(8, 32, 32, 64, 2048, 0, 8 * 1100)
+    assert mixed >= 2 and chunk >= 8                      # a sequence of 500 tokens is one block
+    windowed, wchunk = ops.attention_decode_plan(1, 32, 32, 64, 100000, 256, 100000)
+    assert windowed * wchunk <= 8                         # 256 keys touch five pages at most
+    with pytest.raises(ops.KernelError):
+        ops.attention_decode_plan(1, 32, 5, 64, 100)
+
+
 @pytest.mark.parametrize("n_heads,n_kv,hd", ATT_SHAPES + [(40, 2, 64)])
 @pytest.mark.parametrize("window", [0, 37])
 @pytest.mark.parametrize("splits", [1, 3, 16])
