@@ -668,9 +668,11 @@ GTG_API int gtg_attention_decode_plan(int B, int n_heads, int n_kv, int hd, int 
     if (mean_keys > max_kv_len) mean_keys = max_kv_len;
     const double mean_pages = (double)span(mean_keys > 1 ? mean_keys : 1);
     // measured on a B200: about 3.5 us before a block's first page is in use; a block
-    // keeps three pages in flight over that latency, 1.15 us a page; the memory's own
-    // time for all keys, once enough blocks run to saturate it
-    const double kFixedUs = 3.5, kPageUs = 1.15, kMergeUs = 3.0, kBytesPerUs = 6.0e6;
+    // keeps all but one stage of its ring in flight over that latency (three pages:
+    // 1.17 us a page; two at 128 channels); the memory's own time for all keys, once
+    // enough blocks run to saturate it
+    const double kFixedUs = 3.5, kMergeUs = 3.0, kBytesPerUs = 6.0e6;
+    const double kPageUs = kFixedUs / ((dp == 128 ? decode_stages<128>() : decode_stages<64>()) - 1);
     const double page_bytes = 2.0 * kPageTokens * dp * 2;
     const double memory_us = (double)B * mean_pages * units * page_bytes / kBytesPerUs;
     int best_chunk = max_pages;
