@@ -618,3 +618,67 @@ def test_generation_runs_a_model_that_cannot_be_captured(tmp_path):
     finally:
         unregister_architecture(arch)
         unregister_part("mixer", "decay")
+
+
+# ------------------------------------------------- layers that keep a window beside layers that keep everything
+WINDOW = 37
+
+
+def windowed_plan(cfg):
+    """Llama's plan with every odd layer attending to the last WINDOW keys only."""
+    base = llama_plan(cfg)
+    layers = [layer.replace(mixer=PartSpec(layer.part("mixer").kind, dict(layer.part("mixer").params, window=WINDOW)))
+              if i % 2 else layer for i, layer in enumerate(base.layers)]
+    return ModelPlan(base.hidden_size, base.vocab_size, base.embedding, tuple(layers), base.schedule,
+                     base.final_norm, base.head, base.stop_tokens, base.max_position)
+
+
+def plain_windowed_forward(cfg, w, tokens):
+    positions = list(range(len(tokens)))
+    inv, eps = plain.rope_inv_freq(cfg), cfg["rms_norm_eps"]
+    x = plain.embed(w["model.embed_tokens.weight"], tokens)
+    for i in range(cfg["num_hidden_layers"]):
+        p = f"model.layers.{i}."
+        n = plain.rms_norm(x, w[p + "input_layernorm.weight"], eps)
+        x = (x + plain.attention_block(n, positions, p, cfg, inv, w, window=WINDOW if i % 2 else None)).astype(np.float32)
+        n2 = plain.rms_norm(x, w[p + "post_attention_layernorm.weight"], eps)
+        x = (x + plain.swiglu_mlp(n2, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"],
+                                  w[p + "mlp.down_proj.weight"])).astype(np.float32)
+    return plain.lm_head(x, cfg, w)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_windowed_layers_beside_full_layers(model_folders, plain_models, name, dtype):
+    """Mixers differ layer by layer (every odd one sees a window of 37 keys), so the
+    cache has two groups with storage of their own; prompts longer than the window,
+    a prompt cut where the window's edge falls inside a chunk, and single tokens
+    whose window has slid past the first page."""
+    arch = register_architecture(Architecture(("ToyWindowForCausalLM",), LlamaConfig.from_json, windowed_plan))
+    try:
+        cfg, w = plain_models[name]
+        raw = dict(TINY[name], architectures=["ToyWindowForCausalLM"])
+        model = Model(arch.plan(arch.read_config(raw)), Runtime(DEV, getattr(torch, dtype))).load_tensors(
+            tensors_of(model_folders[name]))
+        cache = model.new_cache(max_tokens=64 * 6, max_slots=2)
+        n_layers = cfg["num_hidden_layers"]
+        assert len(cache.groups) == 2
+        assert sorted(g.storage.shape[0] for g in cache.groups) == sorted([(n_layers + 1) // 2, n_layers // 2])
+        assert {g.request.window for g in cache.groups} == {None, WINDOW}
+        p, q = make_prompts(name, [130, 50], seed=51)
+        want_p, want_q = plain_windowed_forward(cfg, w, p), plain_windowed_forward(cfg, w, q)
+        sp, sq = cache.open_sequence(), cache.open_sequence()
+        got = step(model, cache, [StepEntry(sp, p[:80], list(range(80))), StepEntry(sq, q, list(range(50)))])
+        got = got.float().cpu().numpy()
+        assert_close(got[:80], want_p[:80], dtype, f"{name} windowed: whole")
+        assert_close(got[80:], want_q, dtype, f"{name} windowed: second sequence")
+        cache.close_sequence(sq)
+        got = step(model, cache, [StepEntry(sp, p[80:110], list(range(30)))]).float().cpu().numpy()   # a chunk after the prompt
+        assert_close(got, want_p[80:110], dtype, f"{name} windowed: chunk")
+        rest = [step(model, cache, [StepEntry(sp, [p[t]], [0])]).float().cpu().numpy() for t in range(110, 130)]
+        assert_close(np.concatenate(rest), want_p[110:], dtype, f"{name} windowed: one by one")
+        # the window matters: without it the logits differ visibly
+        full = plain.forward(cfg, w, p)
+        assert np.abs(full[100:] - want_p[100:]).max() > 0.05 * np.abs(want_p).max()
+    finally:
+        unregister_architecture(arch)
