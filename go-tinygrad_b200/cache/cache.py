@@ -10,8 +10,10 @@ layers that keep every key and layers that keep a window do not share storage.
 Storage of a group: ``pages[entry, page, 0|1, kv_head, token(64), channel]``
 (keys at 0, values at 1).  ``block_table[slot, i]`` is the page holding tokens
 ``[64*i, 64*i+64)`` of the sequence in `slot`.  A sequence holds
-ceil(length/64) pages per group; pages and the slot return to the free lists
-when the sequence is closed, and are handed out again.
+ceil(length/64) pages per group -- a group that keeps a window gives back, as
+the sequence grows, the pages that have slid out of it -- and pages and the
+slot return to the free lists when the sequence is closed, and are handed out
+again.
 
 The reference keeps one growing slice (CPU) or one 2048-position buffer (GPU)
 per layer for its single sequence (model/llama.go:984-985,1017-1029;
@@ -86,7 +88,7 @@ class _KVGroup:
         if device.type == "cuda":
             self.table_host = self.table_host.pin_memory()
         self.table = torch.zeros((n_slots, pages_per_seq), dtype=torch.int32, device=device)
-        self.pages_of: Dict[int, List[int]] = {}
+        self.pages_of: Dict[int, List[int]] = {}     # slot -> its pages by index; -1: given back (slid out of the window)
         self.dirty: set = set()
 
     def view(self, entry: int) -> KVEntryView:
@@ -180,7 +182,7 @@ class Cache:
         if not self.slots.is_held(slot):
             raise CacheMisuse(f"slot {slot} is closed but is not open")
         for grp in self.groups:
-            grp.pool.free(grp.pages_of.pop(slot), slot)
+            grp.pool.free([p for p in grp.pages_of.pop(slot) if p >= 0], slot)
         self._length[slot] = 0
         self.slots.free(slot)
 
@@ -235,6 +237,19 @@ class Cache:
             if new_length > len(grp.pages_of[slot]) * PAGE_TOKENS:
                 raise CacheMisuse(f"slot {slot} advanced to {new_length} tokens without reserved pages")
         self._length[slot] = new_length
+        # A group that keeps a window gives back the pages no later token can see: the next
+        # token, at position new_length, reaches back to new_length - window + 1.  Their
+        # table entries stay as they are; no kernel reads a page before a window's first.
+        for grp in self.groups:
+            window = grp.request.window
+            if window is None:
+                continue
+            have = grp.pages_of[slot]
+            gone = [i for i in range(min(len(have), max(0, new_length - window + 1) // PAGE_TOKENS)) if have[i] >= 0]
+            if gone:
+                grp.pool.free([have[i] for i in gone], slot)
+                for i in gone:
+                    have[i] = -1
 
     def truncate(self, slot: int, new_length: int) -> None:
         """Forget the tokens after `new_length` (their pages stay with the sequence).
@@ -248,6 +263,12 @@ class Cache:
                               "rolled back by shortening a length; close the sequence and run it again")
         if not 0 <= new_length <= self._length[slot]:
             raise CacheMisuse(f"cannot truncate slot {slot} from {self._length[slot]} to {new_length}")
+        for grp in self.groups:
+            window = grp.request.window
+            if window is not None and any(p < 0 for p in grp.pages_of[slot][max(0, new_length - window + 1) // PAGE_TOKENS:
+                                                                         (new_length + PAGE_TOKENS - 1) // PAGE_TOKENS]):
+                raise CacheMisuse(f"slot {slot} cannot go back to {new_length} tokens: a layer that keeps a window "
+                                  f"of {window} keys has given back pages that length would need")
         self._length[slot] = new_length
 
     def flush_tables(self) -> None:
@@ -262,7 +283,8 @@ class Cache:
         """Tokens of capacity that live sequences hold (each rounded up to 64)."""
         if not self.groups:
             return 0
-        return max(sum(len(p) for p in grp.pages_of.values()) for grp in self.groups) * PAGE_TOKENS
+        return max(sum(sum(1 for p in pages if p >= 0) for pages in grp.pages_of.values())
+                   for grp in self.groups) * PAGE_TOKENS
 
     def free_pages(self) -> List[int]:
         return [grp.pool.n_free for grp in self.groups]

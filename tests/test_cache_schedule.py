@@ -214,3 +214,43 @@ def test_a_sequence_ends_on_stop_length_or_capacity():
     c.accept(3)
     assert c.finish_reason == "capacity" and len(c.tokens) == 3
     assert live([s, t, z, c, SequenceProgress(4, 1, 1, set())])[0].request == 4
+
+
+def test_a_group_that_keeps_a_window_gives_back_the_pages_that_slid_out_of_it():
+    """Two groups: all keys, and a window of 100.  As the sequence grows the windowed
+    group holds only the pages its next token can still see; the other keeps all.  No
+    page is lost, held twice or freed twice, and a released page serves another sequence."""
+    cache = Cache([[KVRequest(2, 16)], [KVRequest(1, 32, window=100)]], [None, None], max_tokens=64 * 12,
+                  max_slots=2, dtype=torch.float32, device="cpu")
+    full, win = cache.groups
+    a = cache.open_sequence()
+    cache.reserve(a, 300)                                  # a prompt: every page is needed while it runs
+    assert cache.free_pages() == [7, 7]
+    first = list(win.pages_of[a])
+    cache.advance(a, 300)
+    # the next token, at position 300, sees keys 201..300: pages 3 and 4; 0..2 went back
+    assert cache.free_pages() == [7, 10]
+    assert win.pages_of[a] == [-1, -1, -1] + first[3:] and full.pages_of[a] == full.table_host[a, :5].tolist()
+    assert cache.tokens_held() == 5 * 64
+    for length in range(301, 400):                         # one token at a time
+        cache.reserve(a, length)
+        cache.advance(a, 1)
+        lo = (length - 100 + 1) // 64
+        held = [i for i, p in enumerate(win.pages_of[a]) if p >= 0]
+        assert held == list(range(lo, (length - 1) // 64 + 1)), length
+        assert win.pool.n_free == 12 - len(held) and full.pool.n_free == 12 - ((length + 63) // 64)
+    # a page that was given back goes to another sequence, and is not this one's any more
+    b = cache.open_sequence()
+    cache.reserve(b, 64 * 5)
+    assert not set(p for p in win.pages_of[a] if p >= 0) & set(win.pages_of[b])
+    assert set(first[:3]) <= set(win.pages_of[b]) | set(win.pages_of[a])      # in use again, by b or by a itself
+    assert set(first[:3]) & set(win.pages_of[b])
+    # going back: within what is still held it works, below it is refused
+    cache.truncate(a, 390)
+    with pytest.raises(CacheMisuse, match="given back"):
+        cache.truncate(a, 200)
+    assert cache.length(a) == 390
+    cache.close_sequence(a)
+    cache.close_sequence(b)
+    assert cache.free_pages() == [12, 12] and cache.tokens_held() == 0
+    assert sorted(win.pool.alloc(12, 0)) == list(range(12))  # every page once

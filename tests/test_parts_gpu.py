@@ -653,7 +653,8 @@ def test_windowed_layers_beside_full_layers(model_folders, plain_models, name, d
     """Mixers differ layer by layer (every odd one sees a window of 37 keys), so the
     cache has two groups with storage of their own; prompts longer than the window,
     a prompt cut where the window's edge falls inside a chunk, and single tokens
-    whose window has slid past the first page."""
+    whose window has slid past the first page, which the windowed group has then
+    given back (and takes again for its third page)."""
     arch = register_architecture(Architecture(("ToyWindowForCausalLM",), LlamaConfig.from_json, windowed_plan))
     try:
         cfg, w = plain_models[name]
@@ -675,6 +676,16 @@ def test_windowed_layers_beside_full_layers(model_folders, plain_models, name, d
         cache.close_sequence(sq)
         got = step(model, cache, [StepEntry(sp, p[80:110], list(range(30)))]).float().cpu().numpy()   # a chunk after the prompt
         assert_close(got, want_p[80:110], dtype, f"{name} windowed: chunk")
+        # the windowed group has given back the first page (keys 0..63 are behind every later
+        # window); the other group keeps it.  Whatever lies in pages no sequence holds, and in
+        # the page given back once another sequence writes it, must not reach a result
+        win = next(g for g in cache.groups if g.request.window == WINDOW)
+        keeps = next(g for g in cache.groups if g.request.window is None)
+        assert win.pages_of[sp][0] == -1 and all(x >= 0 for x in win.pages_of[sp][1:]) and min(keeps.pages_of[sp]) >= 0
+        assert win.pool.n_free == keeps.pool.n_free + 1
+        held = [x for x in win.pages_of[sp] if x >= 0]
+        loose = [x for x in range(win.pool.n_pages) if x not in held]
+        win.storage[:, loose] = 3.0e4           # finite, and large enough to wreck any sum it entered
         rest = [step(model, cache, [StepEntry(sp, [p[t]], [0])]).float().cpu().numpy() for t in range(110, 130)]
         assert_close(np.concatenate(rest), want_p[110:], dtype, f"{name} windowed: one by one")
         # the window matters: without it the logits differ visibly
