@@ -97,6 +97,7 @@ class DecodeBatch:
                            step=self.model.steps_run, op_hook=self.model.op_hook)
 
     def _forward(self) -> None:
+        self.model.rt.workspace.begin_step()
         ctx = self._context()
         with ops.chained_launches(self.chained), ops.checked_access(self.model.rt.check_access):
             stream = run_layers(self.model, self.cache, ctx)
@@ -148,6 +149,10 @@ class DecodeBatch:
             DecodeBatch._side = torch.cuda.Stream()
         side = DecodeBatch._side
         side.wait_stream(main)
+        # the recording addresses the workspace's buffers: they stay alive with this object
+        # even if a later, larger step makes the workspace replace them
+        self.model.rt.workspace.begin_step()              # grown now, to what the run before asked for
+        self._workspace_held = self.model.rt.workspace.buffers()
         with torch.cuda.stream(side):
             graph.capture_begin()
             try:

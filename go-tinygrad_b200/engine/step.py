@@ -50,7 +50,7 @@ class _Staging:
         self.events = [None, None]
         self.turn = 0
 
-    def upload(self, flat: np.ndarray) -> torch.Tensor:
+    def upload(self, flat: np.ndarray, rt) -> torch.Tensor:
         n = int(flat.shape[0])
         if self.device.type != "cuda":
             return torch.from_numpy(flat).to(self.device)
@@ -62,7 +62,7 @@ class _Staging:
         if buf is None or buf.numel() < n:
             buf = self.buffers[i] = torch.empty(max(4096, 2 * n), dtype=torch.int32, pin_memory=True)
         buf[:n].numpy()[:] = flat
-        meta = torch.empty(n, dtype=torch.int32, device=self.device)
+        meta = rt.empty(n, dtype=torch.int32, lifetime="step")
         meta.copy_(buf[:n], non_blocking=True)
         ev = self.events[i] = self.events[i] or torch.cuda.Event()
         ev.record()
@@ -120,7 +120,7 @@ def build_context(model: Model, cache: Cache, entries: Sequence[StepEntry]):
     n_want = sum(int(w.shape[0]) for w in want_parts)
     flat = np.concatenate(tok_parts + pos_parts + seq_parts +
                           [np.asarray(cu), np.asarray(slots), np.asarray(start)] + want_parts).astype(np.int32)
-    meta = _staging(model).upload(flat)
+    meta = _staging(model).upload(flat, model.rt)
     o = 0
 
     def take(k):
@@ -144,9 +144,11 @@ def build_context(model: Model, cache: Cache, entries: Sequence[StepEntry]):
 
 def run_layers(model: Model, cache: Cache, ctx: StepContext) -> ResidualStream:
     """Embedding, then every schedule entry in order."""
+    workspace = model.rt.workspace
     stream = model.embedding.forward(ctx)
     for i, entry in enumerate(model.plan.schedule):
         ctx.layer = entry.layer
+        workspace.next_layer()              # what the layer before the last one allocated is free again
         model.blocks[entry.layer].forward(stream, ctx, cache.handles[i])
     ctx.layer = -1
     return stream
@@ -166,6 +168,7 @@ def step(model: Model, cache: Cache, entries: Sequence[StepEntry]) -> torch.Tens
     device, in the order of the entries and of each entry's `want`."""
     if not model.loaded:
         raise StepError("the model has no weights loaded")
+    model.rt.workspace.begin_step()         # the intermediates of the step before are dead
     ctx, rows = build_context(model, cache, entries)
     # each kernel may set itself up while its predecessor drains (kernels that take
     # no part in this are launched the plain way and order themselves fully)

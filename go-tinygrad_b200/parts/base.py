@@ -54,6 +54,82 @@ def build_part(category: str, spec: PartSpec) -> "Part":
     return cls(spec)
 
 
+class _Region:
+    """One stretch of a workspace: tensors are cut from a buffer front to back;
+    `reset` makes the whole buffer free again, grown to what the last round asked
+    for.  What does not fit is a tensor of its own."""
+    ALIGN = 256
+
+    def __init__(self, device: torch.device):
+        self.device = device
+        self.buffer: Optional[torch.Tensor] = None
+        self.offset = 0
+        self.asked = 0                      # bytes asked for since the last reset
+
+    def reset(self) -> None:
+        if self.asked > (self.buffer.numel() if self.buffer is not None else 0) and not self._recording():
+            # a quarter more than was asked for: the sizes of a step's scratch vary a little
+            self.buffer = torch.empty(self.asked + self.asked // 4, dtype=torch.uint8, device=self.device)
+        self.offset = self.asked = 0
+
+    def _recording(self) -> bool:
+        """While a CUDA graph is being recorded the buffer is not replaced: memory
+        allocated then belongs to the recording."""
+        return self.device.type == "cuda" and torch.cuda.is_current_stream_capturing()
+
+    def take(self, shape: Tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
+        n = 1
+        for d in shape:
+            n *= int(d)
+        nbytes = n * dtype.itemsize
+        padded = (nbytes + self.ALIGN - 1) // self.ALIGN * self.ALIGN
+        self.asked += padded
+        if self.buffer is None or self.offset + padded > self.buffer.numel():
+            return torch.empty(shape, dtype=dtype, device=self.device)
+        out = self.buffer[self.offset:self.offset + nbytes].view(dtype).view(shape)
+        self.offset += padded
+        return out
+
+
+class Workspace:
+    """Where the intermediate tensors of a step live, so that a step of a size
+    that has run before asks the allocator for nothing.  Three regions: one for
+    what lasts the whole step (the residual stream, the step's metadata, tables)
+    and two that take turns layer by layer -- what a layer allocates stays valid
+    until the layer after it has ended, which is as long as an update left
+    pending on the residual stream needs.  The engine calls `begin_step` and
+    `next_layer`; without those calls nothing is ever handed out twice.  A step
+    of a new size finds the regions too small, gets ordinary tensors for the
+    rest, and the regions grow at their next reset.  A buffer that is replaced
+    lives on for as long as a tensor (or a recorded graph's owner) holds it."""
+
+    def __init__(self, device: torch.device):
+        self.step_region = _Region(device)
+        self.layer_regions = (_Region(device), _Region(device))
+        self.turn = 0
+
+    def begin_step(self) -> None:
+        self.step_region.reset()
+        for r in self.layer_regions:
+            r.reset()
+        self.turn = 0
+
+    def next_layer(self) -> None:
+        self.turn ^= 1
+        self.layer_regions[self.turn].reset()
+
+    def take(self, shape: Tuple[int, ...], dtype: torch.dtype, lifetime: str) -> torch.Tensor:
+        if lifetime == "step":
+            return self.step_region.take(shape, dtype)
+        if lifetime != "layer":
+            raise ValueError(f"a workspace tensor lasts a 'layer' or a 'step', not {lifetime!r}")
+        return self.layer_regions[self.turn].take(shape, dtype)
+
+    def buffers(self) -> List[torch.Tensor]:
+        """The buffers in use now (held by whoever records a graph over them)."""
+        return [r.buffer for r in (self.step_region,) + self.layer_regions if r.buffer is not None]
+
+
 @dataclass
 class Runtime:
     """Settings of a run that parts need: where tensors live and the compute
@@ -66,6 +142,13 @@ class Runtime:
     # synchronise and are not recorded as graphs
     check_access: bool = False
     _shared: Dict[str, torch.Tensor] = field(default_factory=dict, repr=False)
+    _workspace: Optional[Workspace] = field(default=None, repr=False)
+
+    @property
+    def workspace(self) -> Workspace:
+        if self._workspace is None:
+            self._workspace = Workspace(torch.device(self.device))
+        return self._workspace
 
     def matrix(self, t: torch.Tensor, share_as: Optional[str] = None) -> torch.Tensor:
         """A weight matrix or table on the device in the compute dtype.  Parts
@@ -85,7 +168,15 @@ class Runtime:
         out = t.to(device=self.device, dtype=torch.float32).contiguous()
         return out.clone() if out.data_ptr() == t.data_ptr() else out
 
-    def empty(self, *shape: int, dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    def empty(self, *shape: int, dtype: Optional[torch.dtype] = None, lifetime: str = "layer") -> torch.Tensor:
+        """An uninitialised intermediate of the running step, from the workspace:
+        valid until the layer after the one that asked has ended (lifetime
+        "layer") or until the step ends ("step").  Nothing from here may be kept
+        across steps; what is handed to the caller of the step comes from `result`."""
+        return self.workspace.take(tuple(int(d) for d in shape), dtype or self.dtype, lifetime)
+
+    def result(self, *shape: int, dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        """An uninitialised tensor of its own, for what outlives the step."""
         return torch.empty(shape, dtype=dtype or self.dtype, device=self.device)
 
 

@@ -44,7 +44,7 @@ class TokenEmbedding(Embedding):
         self.table = rt.matrix(tensors[self.weight_name], share_as=self.weight_name)
 
     def forward(self, ctx: StepContext) -> ResidualStream:
-        residual = ctx.rt.empty(ctx.n_tokens, self.hidden, dtype=torch.float32)
+        residual = ctx.rt.empty(ctx.n_tokens, self.hidden, dtype=torch.float32, lifetime="step")
         ops.embed(ctx.tokens, self.table, residual)
         stream = ResidualStream(residual)
         if self.position:
@@ -74,6 +74,6 @@ class LMHead(Head):
         self.table = rt.matrix(tensors[self.weight_name], share_as=self.weight_name)
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
-        logits = ctx.rt.empty(x.shape[0], self.vocab, dtype=torch.float32)
+        logits = ctx.rt.result(x.shape[0], self.vocab, dtype=torch.float32)
         ops.linear(x, self.table, logits)
         return logits

@@ -80,8 +80,7 @@ class RotaryEncoding(PositionEncoding):
     def rotation(self, ctx: StepContext) -> Optional[torch.Tensor]:
         table = ctx.shared.get(self._key)
         if table is None:
-            table = torch.empty((ctx.n_tokens, self.rotary_dim // 2, 2), dtype=torch.float32,
-                                device=ctx.rt.device)
+            table = ctx.rt.empty(ctx.n_tokens, self.rotary_dim // 2, 2, dtype=torch.float32, lifetime="step")
             ops.rope_table(ctx.positions, self.inv_freq, table)
             ctx.shared[self._key] = table
         return table

@@ -254,3 +254,56 @@ def test_a_group_that_keeps_a_window_gives_back_the_pages_that_slid_out_of_it():
     cache.close_sequence(b)
     assert cache.free_pages() == [12, 12] and cache.tokens_held() == 0
     assert sorted(win.pool.alloc(12, 0)) == list(range(12))  # every page once
+
+
+def test_the_workspace_hands_out_nothing_twice_before_it_is_told_to():
+    """Scratch of a step: a region for the whole step and two that take turns layer by
+    layer.  A tensor stays untouched until the layer after its own has ended; regions
+    start empty, serve ordinary tensors meanwhile, and grow at the next reset; without
+    the engine's calls nothing is ever reused."""
+    from go_tinygrad_b200.parts.base import Runtime, Workspace
+    rt = Runtime(torch.device("cpu"), torch.float32)
+    ws = rt.workspace
+    assert isinstance(ws, Workspace) and ws.buffers() == []
+
+    def one_step(check_reuse):
+        ws.begin_step()
+        residual = rt.empty(4, 8, lifetime="step")
+        residual.fill_(7.0)
+        kept = []
+        for layer in range(5):
+            ws.next_layer()
+            a, b = rt.empty(3, 5), rt.empty(100, dtype=torch.int32)
+            assert a.dtype == torch.float32 and b.dtype == torch.int32 and a.shape == (3, 5)
+            assert a.data_ptr() % 16 == 0 and b.data_ptr() % 16 == 0      # on the device: 256, from an aligned buffer
+            a.fill_(float(layer))
+            b.fill_(layer)
+            kept.append((a, b))
+            if layer:                                      # the layer before is still whole
+                assert float(kept[layer - 1][0].min()) == float(layer - 1) and int(kept[layer - 1][1].max()) == layer - 1
+            if check_reuse and layer >= 2:                 # the one before that has been handed out again
+                assert kept[layer - 2][0].data_ptr() == a.data_ptr()
+        assert float(residual.min()) == 7.0
+        return residual, kept
+    first, kept = one_step(check_reuse=False)              # nothing to cut from at first: ordinary tensors, and
+    assert len({t.data_ptr() for pair in kept[:2] for t in pair}) == 4      # the layers' regions appear as they take turns
+    ws.begin_step()                                        # now the regions exist, as large as was asked for
+    assert len(ws.buffers()) == 3
+    held = [b.data_ptr() for b in ws.buffers()]
+    second, _ = one_step(check_reuse=True)
+    third, _ = one_step(check_reuse=True)
+    assert second.data_ptr() == third.data_ptr() and [b.data_ptr() for b in ws.buffers()] == held   # the same memory, no growth
+    # a larger step: served, and the regions have grown by the step after it
+    ws.begin_step()
+    big = rt.empty(1000, 1000, lifetime="step")
+    big.zero_()
+    assert [b.data_ptr() for b in ws.buffers()] == held
+    ws.begin_step()
+    assert ws.step_region.buffer.numel() >= 4 * 1000 * 1000
+    with pytest.raises(ValueError):
+        rt.empty(3, lifetime="forever")
+    # without the engine's calls nothing is reused
+    rt2 = Runtime(torch.device("cpu"), torch.bfloat16)
+    alive = [rt2.empty(16, 16) for _ in range(50)]
+    assert len({t.data_ptr() for t in alive}) == 50 and rt2.empty(2, 2).dtype == torch.bfloat16
+    assert rt2.result(3, 3).shape == (3, 3)

@@ -251,3 +251,36 @@ def test_the_op_hook_names_every_value_of_a_layer(model_folders, plain_models, n
     again = generate(model, [p[:9]], max_new_tokens=3, stop=[])
     assert [r.tokens for r in again] == [r.tokens for r in out] and not got
     cache.close_sequence(slot)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_step_of_a_size_that_has_run_asks_the_allocator_for_its_result_only(model_folders, plain_logits, dtype):
+    """The intermediates of a step come from the model's workspace.  Once a step of a
+    size has run, the same step again makes the allocator hand out its result and
+    nothing else, whatever the number of layers; its logits are the same bits, and
+    logits kept from an earlier step are not touched by a later one."""
+    model = Model.load(model_folders["A"], dtype=dtype, device="cuda")
+    cache = model.new_cache(max_tokens=64 * 4)
+    (p,) = make_prompts("A", [45], seed=31)
+    count = lambda: torch.cuda.memory_stats()["allocation.all.allocated"]
+
+    def prompt_then_two_tokens():
+        slot = cache.open_sequence()
+        out, asked = [], []
+        for tokens in (p[:43], p[43:44], p[44:45]):
+            before = count()
+            out.append(step(model, cache, [StepEntry(slot, tokens, [len(tokens) - 1])]))
+            asked.append(count() - before)
+        cache.close_sequence(slot)
+        return out, asked
+    first, _ = prompt_then_two_tokens()
+    kept = [t.clone() for t in first]
+    prompt_then_two_tokens()
+    again, asked = prompt_then_two_tokens()
+    assert asked == [1, 1, 1], f"allocations per step: {asked}"
+    for a, b, c in zip(first, kept, again):
+        assert torch.equal(a, b) and torch.equal(a, c)
+    assert len(model.rt.workspace.buffers()) == 3
+    want = plain_logits("A", p)
+    got = torch.cat(again).float().cpu().numpy()
+    assert_close(got, want[[42, 43, 44]], dtype, "steps from the workspace")
