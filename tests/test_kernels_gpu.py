@@ -44,7 +44,10 @@ def ref_rmsnorm(x, w, eps):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("H,N,eps", [(24, 3, 1e-5), (2048, 19, 1e-6), (1000, 4, 1e-3), (13000, 2, 1e-5), (36, 5, 1e-5),
-                                     (8192, 3, 1e-5)])
+                                     (8192, 3, 1e-5),
+                                     # many rows (a prompt)
+                                     (2048, 300, 1e-5), (1000, 257, 1e-6), (264, 1001, 1e-5), (1024, 256, 1e-5),
+                                     (1032, 260, 1e-5), (4096, 300, 1e-5), (40, 2048, 1e-5)])
 def test_add_rmsnorm(dtype, H, N, eps):
     res = rnd(N, H, scale=3.0, seed=1)
     pend = rnd(N, H, dtype=dtype, seed=2)
