@@ -521,6 +521,8 @@ attention_decode_kernel(const bf16* __restrict__ q, int ldq, bf16* __restrict__ 
     }
 }
 
+constexpr int kCombineAtOnce = 16;
+
 template <int DP>
 __global__ void attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                          bf16* __restrict__ out, int ldo, int n_heads, int hd, int n_splits) {
@@ -530,6 +532,37 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_o, const
     const int b = bh / n_heads, head = bh % n_heads;
     const int d = threadIdx.x;
     if (d >= hd) return;
+    if (n_splits <= kCombineAtOnce) {
+        // Few splits: everything this thread reads is asked for at once (one trip to the
+        // L2 instead of two in a row), then added up in the order of the loop below.
+        float ms[kCombineAtOnce], ls[kCombineAtOnce], os[kCombineAtOnce];
+#pragma unroll
+        for (int s = 0; s < kCombineAtOnce; ++s) {
+            ms[s] = -INFINITY;
+            ls[s] = os[s] = 0.f;
+            if (s < n_splits) {
+                const size_t pidx = (size_t)bh * n_splits + s;
+                const float2 ml = *reinterpret_cast<const float2*>(part_ml + pidx * 2);
+                ms[s] = ml.x;
+                ls[s] = ml.y;
+                os[s] = part_o[pidx * DP + d];
+            }
+        }
+        float M = -INFINITY;
+#pragma unroll
+        for (int s = 0; s < kCombineAtOnce; ++s) M = fmaxf(M, ms[s]);
+        const float Mu = M == -INFINITY ? 0.f : M;
+        float acc = 0.f, L = 0.f;
+#pragma unroll
+        for (int s = 0; s < kCombineAtOnce; ++s) {
+            if (ms[s] == -INFINITY) continue;      // a split without keys wrote no sums (what was read for it is not used)
+            const float f = exp2f(ms[s] - Mu);
+            acc += f * os[s];
+            L += f * ls[s];
+        }
+        out[(size_t)b * ldo + head * hd + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+        return;
+    }
     float M = -INFINITY;
     for (int s = 0; s < n_splits; ++s) M = fmaxf(M, part_ml[((size_t)bh * n_splits + s) * 2]);
     const float Mu = M == -INFINITY ? 0.f : M;

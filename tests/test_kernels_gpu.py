@@ -504,7 +504,7 @@ def test_attention_prefill_bf16(n_heads, n_kv, hd, window, lens_before, lens_new
 
 @pytest.mark.parametrize("n_heads,n_kv,hd", ATT_SHAPES)
 @pytest.mark.parametrize("window", [0, 37])
-@pytest.mark.parametrize("splits", [1, 2, 5])
+@pytest.mark.parametrize("splits", [1, 2, 5, 20])
 def test_attention_decode_bf16(n_heads, n_kv, hd, window, splits):
     lens_before = [0, 63, 64, 700, 129]
     cache, q, want, m, scale = attention_case(torch.bfloat16, n_heads, n_kv, hd, lens_before,
