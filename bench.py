@@ -353,7 +353,11 @@ def run_own(args):
         uniform in [128, 2048], ids uniform in the vocabulary (seeded)."""
         g = torch.Generator().manual_seed(1)
         lengths = torch.randint(128, 2049, (64,), generator=g).tolist()
-        return [torch.randint(0, vocab, (k,), generator=g).tolist() for k in lengths][:n]
+        prompts = [torch.randint(0, vocab, (k,), generator=g).tolist() for k in lengths]
+        if n > 64:                      # more sequences than the named points use: the same draw goes on
+            more = torch.randint(128, 2049, (n - 64,), generator=g).tolist()
+            prompts += [torch.randint(0, vocab, (k,), generator=g).tolist() for k in more]
+        return prompts[:n]
 
     if args.only == "decode":          # for profilers: the decode steps and nothing else
         r = decode_run(args.batch, args.steps, args.warmup, host=False,

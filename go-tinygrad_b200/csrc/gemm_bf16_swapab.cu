@@ -3,15 +3,15 @@
 // With this many tokens the work is still reading W once, but a CUDA-core or
 // warp-level kernel would re-read X from L2 or shared memory several times per
 // byte of W.  Here the roles of the operands are swapped on the tensor core:
-// 128 rows of W are the M dimension of tcgen05.mma and the tokens (padded to 64,
-// or to 128 for more than 64) are its N dimension, so both operands go from
-// shared memory to the tensor core once.  The accumulator [128 features x 64 or
-// 128 tokens] lives in TMEM.
+// 128 rows of W are the M dimension of tcgen05.mma and the tokens (padded to 32,
+// 48, 64, 80 or 128) are its N dimension, so both operands go from shared memory
+// to the tensor core once.  The accumulator [128 features x tokens] lives in TMEM.
 //
 // One CTA takes one (128-row tile of W, slice of k), two CTAs to an SM.  One
-// thread keeps a ring of four 24 KB stages (a 128 x 64 block of W and the 64 x 64
-// block of X under it; three stages of 32 KB with 128 tokens) full by TMA -- the weights from before the wait on the
-// kernel before, the activations after it -- one thread issues the MMAs as the
+// thread keeps a ring of stages (a 128 x 64 block of W, 16 KB, and the block of X
+// under it: five stages at up to 48 tokens, four at up to 80, three of 32 KB at
+// 128) full by TMA -- the weights from before the wait on the kernel before, the
+// activations after it -- one thread issues the MMAs as the
 // stages land, and four warps move the finished accumulator to shared memory.
 // The slices of a row tile are the CTAs of one thread-block cluster (up to
 // eight): after a cluster barrier every CTA adds up, for its share of the
@@ -31,16 +31,21 @@ constexpr int kWBytes = BR * BK * 2;
 constexpr int kThreads = 192;
 constexpr int kCtasPerSm = 2;                 // what the ring's size lets an SM hold
 constexpr int kMaxSlices = 8;                 // CTAs of a cluster (the portable limit)
-// What depends on the tokens a CTA takes (BT, the MMA's N: 64, or 128 for batches
-// of 65 to 128): the stage, the ring (about 96 KB either way, so that two CTAs
-// share an SM), the accumulator's TMEM columns.
+// What depends on the tokens a CTA takes (BT, the MMA's N: 32, 48, 64, 80 or 128, the
+// least that holds the step's rows): the stage (a 16 KB block of W and BT x 64 of X),
+// as many stages as let two CTAs share an SM, the accumulator's TMEM columns.  The
+// fewer tokens, the smaller X's share of a stage and the more stages there are.
 template <int BT> struct Tile {
-    static constexpr int kStages = BT == 64 ? 4 : 3;              // ring of k blocks
+    static_assert(BT % 16 == 0 && BT >= 32 && BT <= 128, "the MMA's N");
+    static constexpr int kStages = BT <= 48 ? 5 : BT <= 80 ? 4 : 3;   // ring of k blocks
     static constexpr int kXBytes = BT * BK * 2, kBlockBytes = kWBytes + kXBytes;
-    static constexpr int kTmemCols = BT;                          // one accumulator: 128 lanes x BT columns
+    static constexpr int kTmemCols = BT <= 32 ? 32 : BT <= 64 ? 64 : 128;   // one accumulator: 128 lanes x BT columns (a power of two is allocated)
     static constexpr int kPartFloats = BT * BR;                   // the accumulator as [token][feature], after the ring is done
     static constexpr int kSmemBytes = kStages * kBlockBytes + 1024 + 256;
     static_assert(kPartFloats * 4 <= kStages * kBlockBytes, "the partial sums reuse the ring");
+    static_assert(2 * (kSmemBytes + 1024) <= 228 * 1024, "two CTAs share an SM");
+    static_assert(kBlockBytes % 1024 == 0, "the swizzled tiles of every stage start on 1024 bytes");
+    static_assert((2 * kStages + 1) * 8 <= 192, "the barriers lie below the TMEM holder");
 };
 constexpr unsigned kSpinLimit = 1u << 22;
 // The kernels of this library exist twice: as they run, and (kTest) in the form the
@@ -111,14 +116,11 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<const uint32_t*>(&v);
 }
-__device__ __forceinline__ void tmem_ld32(uint32_t addr, uint32_t* r) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-                 "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+__device__ __forceinline__ void tmem_ld16(uint32_t addr, uint32_t* r) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
                  : "r"(addr));
 }
 
@@ -234,17 +236,17 @@ swapab_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::);
         const int feature = warp * 32 + lane;
 #pragma unroll 1
-        for (int c = 0; c < BT / 32; ++c) {
-            uint32_t v[32];
+        for (int c = 0; c < BT / 16; ++c) {
+            uint32_t v[16];
             if (use) {
-                tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(c * 32), v);
+                tmem_ld16(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(c * 16), v);
                 asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
             } else {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) v[i] = 0u;      // a slice without k blocks adds nothing
+                for (int i = 0; i < 16; ++i) v[i] = 0u;      // a slice without k blocks adds nothing
             }
 #pragma unroll
-            for (int i = 0; i < 32; ++i) part[(c * 32 + i) * BR + feature] = __uint_as_float(v[i]);
+            for (int i = 0; i < 16; ++i) part[(c * 16 + i) * BR + feature] = __uint_as_float(v[i]);
         }
         asm volatile("tcgen05.fence::before_thread_sync;\n" ::);
     }
@@ -412,7 +414,9 @@ GTG_API int gtg_gemm_bf16_swapab(const void* X, int ldx, const void* W, int ldw,
     if (K % 8 || ldx % 8 || ldw % 8 || ((uintptr_t)X % 16) || ((uintptr_t)W % 16)) return kErrUnsupported;
     int slices, kb_per;
     plan(N, K, device_sms(), &slices, &kb_per);
-    const int bt = M <= 64 ? 64 : 128;                       // tokens a CTA takes: the MMA's N
+    // tokens a CTA takes, the MMA's N: the least of these that holds the rows
+    int bt = M <= 32 ? 32 : M <= 48 ? 48 : M <= 64 ? 64 : M <= 80 ? 80 : 128;
+    if (g_test_waits) bt = M <= 64 ? 64 : 128;              // the give-up test's form exists for 64 tokens
     CUtensorMap map_w, map_x;
     int st = make_map(&map_w, W, N, K, ldw, BR);
     if (st != 0) return st;
@@ -423,7 +427,10 @@ GTG_API int gtg_gemm_bf16_swapab(const void* X, int ldx, const void* W, int ldw,
         if (bt != 64) return kErrUnsupported;
         return out_f32 ? launch<float, 64, true>(GTG_ARGS(float)) : launch<bf16, 64, true>(GTG_ARGS(bf16));
     }
+    if (bt == 32) return out_f32 ? launch<float, 32, false>(GTG_ARGS(float)) : launch<bf16, 32, false>(GTG_ARGS(bf16));
+    if (bt == 48) return out_f32 ? launch<float, 48, false>(GTG_ARGS(float)) : launch<bf16, 48, false>(GTG_ARGS(bf16));
     if (bt == 64) return out_f32 ? launch<float, 64, false>(GTG_ARGS(float)) : launch<bf16, 64, false>(GTG_ARGS(bf16));
+    if (bt == 80) return out_f32 ? launch<float, 80, false>(GTG_ARGS(float)) : launch<bf16, 80, false>(GTG_ARGS(bf16));
     return out_f32 ? launch<float, 128, false>(GTG_ARGS(float)) : launch<bf16, 128, false>(GTG_ARGS(bf16));
 #undef GTG_ARGS
 }

@@ -275,7 +275,9 @@ def test_linear_bfloat16(out_dtype, kind, M, N, K):
 
 @pytest.mark.parametrize("M,N,K", [(40, 38000, 136), (64, 19100, 520), (17, 300, 16384), (64, 2048, 2048), (33, 6144, 2048),
                                    (64, 2048, 8192), (20, 16384, 2048), (64, 130, 520), (50, 4096, 14336),
-                                   (65, 6144, 2048), (128, 2048, 8192), (97, 391, 264), (120, 16384, 2048)])
+                                   (65, 6144, 2048), (128, 2048, 8192), (97, 391, 264), (120, 16384, 2048),
+                                   (32, 6144, 2048), (24, 2048, 8192), (19, 16384, 2048), (32, 100, 64), (31, 4096, 14336),
+                                   (48, 2048, 8192), (41, 16384, 2048), (80, 2048, 2048), (72, 16384, 2048), (66, 391, 520)])
 def test_linear_swapab_slices_meet_in_a_cluster(M, N, K):
     """One CTA per (128-row tile, slice of k): more CTAs than the device holds at once
     (several waves), clusters of two, four and eight slices whose partial sums meet
@@ -327,7 +329,8 @@ def test_linear_skinny_long_rows_split_over_a_cluster(M, N, K):
 
 @pytest.mark.parametrize("kind", ["skinny", "swapab", "tcgen05"])
 @pytest.mark.parametrize("M,I,K", [(1, 8, 96), (8, 264, 96), (16, 1000, 2048), (33, 24, 8192), (64, 264, 264),
-                                   (200, 264, 96), (130, 1000, 2048), (96, 8192, 2048), (128, 264, 8192)])
+                                   (200, 264, 96), (130, 1000, 2048), (96, 8192, 2048), (128, 264, 8192),
+                                   (20, 8192, 2048), (32, 264, 96), (45, 8192, 2048), (80, 1000, 2048)])
 def test_linear_with_fused_swiglu(kind, M, I, K):
     """The product over interleaved gate/up rows writes silu(gate) * up directly."""
     if (kind == "skinny" and M > ops.WARP_LEVEL_MAX_ROWS) or (kind == "swapab" and M > ops.SKINNY_MAX_ROWS):
