@@ -122,6 +122,9 @@ class Cache:
             self.max_sequence = min(self.max_sequence, int(max_position))
         self.slots = SlotTable(self.n_slots)
         self._length = [0] * self.n_slots
+        # what users of the cache keep with it and want gone when it goes (the generation
+        # loop: its recorded decode steps); the cache itself never looks inside
+        self.attachments: Dict[str, object] = {}
 
         # group the KV requests
         keys: List[KVRequest] = []

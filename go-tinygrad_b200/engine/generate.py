@@ -14,7 +14,7 @@ The reference's loop: model/llama.go:1047-1474 (one sequence, exactly
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import List, Optional, Sequence, Union
+from typing import Dict, List, Optional, Sequence, Tuple, Union
 
 import torch
 
@@ -50,7 +50,9 @@ def generate(model: Model, prompts: Sequence[Sequence[int]],
     needs, up to `max_batch` requests at a time, default 64).  `max_sequence`
     caps a sequence's length (prompt and new tokens) below the model's own longest
     position: a request that reaches it ends with "capacity".  Decode steps of a
-    batch whose membership does not change are replayed as a CUDA graph unless
+    batch whose membership does not change are replayed as a CUDA graph (one
+    recording per batch size, kept with a `cache` the caller passes, so that
+    later calls with the same cache, temperature and seed record nothing) unless
     `use_graph` is False or the model cannot be captured (a part of it talks to
     the host in its forward, or a diagnostic hook is set: `Model.capturable`)."""
     n = len(prompts)
@@ -66,6 +68,7 @@ def generate(model: Model, prompts: Sequence[Sequence[int]],
     if cache is not None:
         max_seq = cache.max_sequence if max_seq is None else min(max_seq, cache.max_sequence)
     lengths = [len(p) for p in prompts]
+    own_cache = cache is None
     if cache is None:
         max_batch = max_batch or 64
         if max_tokens is None:
@@ -79,7 +82,11 @@ def generate(model: Model, prompts: Sequence[Sequence[int]],
                            max_sequence=max_seq)
     sampler = Sampler(temperature, seed)
     results: List[Optional[GenerationResult]] = [None] * n
-    decoders = {}                       # batch size -> DecodeBatch
+    # batch size (and what else a recording fixes) -> DecodeBatch
+    # A caller who keeps a cache over several calls keeps, with it, the decode batches made
+    # for it, so that a later call records nothing anew; they go when the cache goes.
+    kept = {} if own_cache else cache.attachments.setdefault("decode_batches", {})
+    key = lambda size: (id(model), size, sampler.temperature, sampler.seed, bool(use_graph))
 
     for batch in batches:
         seqs = [SequenceProgress(i, lengths[i], limits[i], stop_set, max_seq) for i in batch]
@@ -108,10 +115,11 @@ def generate(model: Model, prompts: Sequence[Sequence[int]],
                     break
                 now = tuple(s.request for s in running)
                 if now != members:          # the batch shrank: another fixed set of sequences
-                    decode = decoders.get(len(now))
-                    if decode is None:      # one recorded step per batch size serves every set of that size
-                        decode = decoders[len(now)] = DecodeBatch(model, cache, [slots[r] for r in now], now,
-                                                                  sampler, use_graph=use_graph)
+                    decode = kept.get(key(len(now)))
+                    if decode is None or decode.model is not model:
+                        # one recorded step per batch size serves every set of that size
+                        decode = kept[key(len(now))] = DecodeBatch(model, cache, [slots[r] for r in now], now,
+                                                                   sampler, use_graph=use_graph)
                     else:
                         decode.rebind([slots[r] for r in now], now)
                     members = now

@@ -135,6 +135,35 @@ def test_batch_after_batch_through_a_small_cache(model_folders):
     assert cache.open_slots() == [] and cache.free_pages() == [4]
 
 
+def test_a_cache_kept_over_calls_keeps_its_recorded_decode_steps(model_folders, monkeypatch):
+    """The decode batches a call of `generate` makes stay with a cache the caller owns: a
+    second call with that cache builds none, whatever its prompts, and gives what a call
+    on a cache of its own gives; another temperature is another recording."""
+    from go_tinygrad_b200.engine import generate as generate_module
+    name = "A"
+    model = get_model(model_folders, name, "bfloat16")
+    made = []
+    real = generate_module.DecodeBatch
+
+    def counting(*args, **kwargs):
+        made.append(1)
+        return real(*args, **kwargs)
+    monkeypatch.setattr(generate_module, "DecodeBatch", counting)
+    cache = model.new_cache(max_tokens=64 * 8, max_slots=3)
+    first_prompts = make_prompts(name, [40, 9, 70], seed=51)
+    second_prompts = make_prompts(name, [5, 120, 33], seed=52)
+    limits = [12, 5, 9]                                       # sizes 3, 2 and 1 each get a recording
+    lib.generate(model, first_prompts, limits, stop=[], cache=cache)
+    assert len(made) == 3 and len(cache.attachments["decode_batches"]) == 3
+    second = lib.generate(model, second_prompts, limits, stop=[], cache=cache)
+    assert len(made) == 3, "the second call made decode batches of its own"
+    fresh = lib.generate(model, second_prompts, limits, stop=[])
+    assert [r.tokens for r in second] == [r.tokens for r in fresh]
+    lib.generate(model, second_prompts, limits, stop=[], cache=cache, temperature=0.5, seed=1)
+    assert len(made) == 6 + 3                                 # the call on its own cache, and the other temperature
+    assert cache.open_slots() == []
+
+
 def test_command_line(model_folders, plain_models):
     name = "A"
     cfg, w = plain_models[name]
