@@ -219,11 +219,13 @@ attention_prefill_kernel(const bf16* __restrict__ q, int ldq, bf16* __restrict__
 }
 
 // ============================================================== decode
-// Pages in the ring of a decode block.  What the kernel reaches is set by the bytes in
-// flight per SM: four stages of 16 KB pages let three blocks share an SM (heads up to 64
-// channels); pages of 128 channels take 32 KB, and three stages keep two blocks on an SM
-// where four would leave one.
-template <int DP> __host__ __device__ constexpr int decode_stages() { return DP == 128 ? 3 : 4; }
+// Pages in the ring of a decode block: three (two in flight while one is worked on).
+// What the kernel reaches is set by how many blocks share an SM more than by how deep
+// each one's ring is: with 16 KB pages (heads up to 64 channels) three stages let four
+// blocks share an SM, and that beat three blocks of four stages at every batch size
+// measured (and two blocks of six by far); pages of 128 channels take 32 KB, three
+// stages keep two blocks on an SM, and two stages with three blocks were slower.
+template <int DP> __host__ __device__ constexpr int decode_stages() { return 3; }
 // Shared memory of a decode block: the queries, then the page ring (reused for the merge).
 template <int DP>
 constexpr int decode_smem_bytes() {
@@ -701,9 +703,9 @@ GTG_API int gtg_attention_decode_plan(int B, int n_heads, int n_kv, int hd, int 
     if (mean_keys > max_kv_len) mean_keys = max_kv_len;
     const double mean_pages = (double)span(mean_keys > 1 ? mean_keys : 1);
     // measured on a B200: about 3.5 us before a block's first page is in use; a block
-    // keeps all but one stage of its ring in flight over that latency (three pages:
-    // 1.17 us a page; two at 128 channels); the memory's own time for all keys, once
-    // enough blocks run to saturate it
+    // keeps all but one stage of its ring in flight over that latency (two pages:
+    // 1.75 us a page); the memory's own time for all keys, once enough blocks run to
+    // saturate it
     const double kFixedUs = 3.5, kMergeUs = 3.0, kBytesPerUs = 6.0e6;
     const double kPageUs = kFixedUs / ((dp == 128 ? decode_stages<128>() : decode_stages<64>()) - 1);
     const double page_bytes = 2.0 * kPageTokens * dp * 2;
