@@ -219,17 +219,20 @@ attention_prefill_kernel(const bf16* __restrict__ q, int ldq, bf16* __restrict__
 }
 
 // ============================================================== decode
-// Pages in the ring of a decode block: three (two in flight while one is worked on).
-// What the kernel reaches is set by how many blocks share an SM more than by how deep
-// each one's ring is: with 16 KB pages (heads up to 64 channels) three stages let four
-// blocks share an SM, and that beat three blocks of four stages at every batch size
-// measured (and two blocks of six by far); pages of 128 channels take 32 KB, three
-// stages keep two blocks on an SM, and two stages with three blocks were slower.
-template <int DP> __host__ __device__ constexpr int decode_stages() { return 3; }
+// Pages in the ring of a decode block: three (two in flight while one is worked on) or
+// four.  What the kernel reaches is set by how many blocks share an SM more than by how
+// deep each one's ring is: with 16 KB pages (heads up to 64 channels) three stages let
+// four blocks share an SM, and that beat three blocks of four stages at most batch
+// sizes measured (and two blocks of six by far).  The exception is a batch that brings
+// about one block per slot without any split: then the longest sequence's one block
+// is what the step waits for, and the block with three pages in flight is the faster
+// (`gtg_attention_decode_plan` picks).  Pages of 128 channels take 32 KB: three stages
+// keep two blocks on an SM; two stages with three blocks were slower.
+constexpr int kRingDefault = 3, kRingDeep = 4;
 // Shared memory of a decode block: the queries, then the page ring (reused for the merge).
-template <int DP>
+template <int DP, int STAGES>
 constexpr int decode_smem_bytes() {
-    constexpr int ring = decode_stages<DP>() * 2 * 64 * DP * 2;
+    constexpr int ring = STAGES * 2 * 64 * DP * 2;
     constexpr int merge = (4 * 16 * DP + 128) * 4;
     return 16 * DP * 2 + (ring > merge ? ring : merge);
 }
@@ -258,7 +261,7 @@ __device__ __forceinline__ void rotate_pair(float a, float b, float2 cs, bf16& r
 
 // Partials: for each (sequence, query head, split): DP floats of unnormalised
 // output, then the running max (log2 domain) and the running sum.
-template <int DP>
+template <int DP, int STAGES>
 __global__ void __launch_bounds__(128)
 attention_decode_kernel(const bf16* __restrict__ q, int ldq, bf16* __restrict__ out, int ldo,
                         const bf16* __restrict__ kc, const bf16* __restrict__ vc, long long page_stride,
@@ -268,7 +271,7 @@ attention_decode_kernel(const bf16* __restrict__ q, int ldq, bf16* __restrict__ 
                         int n_splits, float* __restrict__ part_o, float* __restrict__ part_ml,
                         const DecodeRope rope, int chunk_pages) {
     chain_release();
-    constexpr int kDecodeStages = decode_stages<DP>();
+    constexpr int kDecodeStages = STAGES;
     constexpr int CPR = DP / 8;
     constexpr int TILE_BYTES = 64 * DP * 2;
     constexpr int STAGE_BYTES = 2 * TILE_BYTES;
@@ -608,28 +611,46 @@ int launch_prefill(const bf16* q, int ldq, bf16* out, int ldo, const bf16* kc, c
     return launch_status();
 }
 
-template <int DP>
-int launch_decode(const bf16* q, int ldq, bf16* out, int ldo, const bf16* kc, const bf16* vc,
-                  long long page_stride, const int* block_table, int table_stride,
-                  const int* slots, const int* positions, int B, int n_heads, int n_kv, int hd,
-                  float scale, int window, int n_splits, float* part_o, float* part_ml,
-                  cudaStream_t stream, const DecodeRope rope = DecodeRope{}, int chunk_pages = 0) {
+template <int DP, int STAGES>
+int launch_decode_ring(const bf16* q, int ldq, bf16* out, int ldo, const bf16* kc, const bf16* vc,
+                       long long page_stride, const int* block_table, int table_stride,
+                       const int* slots, const int* positions, int B, int n_heads, int n_kv, int hd,
+                       float scale, int window, int n_splits, float* part_o, float* part_ml,
+                       cudaStream_t stream, const DecodeRope rope, int chunk_pages) {
     static bool configured = false;
-    const int smem = decode_smem_bytes<DP>();
+    const int smem = decode_smem_bytes<DP, STAGES>();
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<DP>,
+        cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<DP, STAGES>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
     const int group = n_heads / n_kv;
     dim3 grid(n_splits, n_kv * ((group + 15) / 16), B);
-    int st = launch_chained(attention_decode_kernel<DP>, grid, dim3(128), smem, stream, q, ldq, out, ldo, kc, vc,
+    int st = launch_chained(attention_decode_kernel<DP, STAGES>, grid, dim3(128), smem, stream, q, ldq, out, ldo, kc, vc,
                             page_stride, block_table, table_stride, slots, positions, n_heads, n_kv, hd, scale,
                             window, n_splits, part_o, part_ml, rope, n_splits > 1 ? chunk_pages : 0);
     if (st != 0 || n_splits == 1) return st;
     return launch_chained(attention_combine_kernel<DP>, dim3(B * n_heads), dim3(DP), 0, stream,
                           (const float*)part_o, (const float*)part_ml, out, ldo, n_heads, hd, n_splits);
+}
+
+// ring_pages: kRingDeep where the plan asked for it (heads up to 64 channels), else the default.
+template <int DP>
+int launch_decode(const bf16* q, int ldq, bf16* out, int ldo, const bf16* kc, const bf16* vc,
+                  long long page_stride, const int* block_table, int table_stride,
+                  const int* slots, const int* positions, int B, int n_heads, int n_kv, int hd,
+                  float scale, int window, int n_splits, float* part_o, float* part_ml,
+                  cudaStream_t stream, const DecodeRope rope, int chunk_pages, int ring_pages) {
+    if constexpr (DP <= 64) {
+        if (ring_pages == kRingDeep)
+            return launch_decode_ring<DP, kRingDeep>(q, ldq, out, ldo, kc, vc, page_stride, block_table, table_stride, slots,
+                                                     positions, B, n_heads, n_kv, hd, scale, window, n_splits, part_o,
+                                                     part_ml, stream, rope, chunk_pages);
+    }
+    return launch_decode_ring<DP, kRingDefault>(q, ldq, out, ldo, kc, vc, page_stride, block_table, table_stride, slots,
+                                                positions, B, n_heads, n_kv, hd, scale, window, n_splits, part_o, part_ml,
+                                                stream, rope, chunk_pages);
 }
 }  // namespace
 
@@ -640,16 +661,16 @@ GTG_API int gtg_attention_bf16_supports(int hd) { return padded_head_dim(hd) != 
 // How many decode blocks the current device holds at once: what the occupancy
 // calculator says for this kernel's registers and shared memory, times the
 // device's multiprocessors.  Asked once per (device, head size).
-template <int DP>
+template <int DP, int STAGES>
 static int decode_block_slots() {
     static int cached[64] = {};
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
     if (cached[dev] == 0) {
-        constexpr int smem = decode_smem_bytes<DP>();
+        constexpr int smem = decode_smem_bytes<DP, STAGES>();
         int per_sm = 0, sms = 0;
-        if (cudaFuncSetAttribute(attention_decode_kernel<DP>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess ||
-            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attention_decode_kernel<DP>, 128, smem) != cudaSuccess ||
+        if (cudaFuncSetAttribute(attention_decode_kernel<DP, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess ||
+            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attention_decode_kernel<DP, STAGES>, 128, smem) != cudaSuccess ||
             cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
             (void)cudaGetLastError();
             return 0;
@@ -676,20 +697,34 @@ static int decode_block_slots() {
 // splits x chunk pages (a recorded step replayed while its sequences grow) is cut
 // into `splits` parts of more pages each: the plan is a matter of speed only.
 GTG_API int gtg_attention_decode_plan(int B, int n_heads, int n_kv, int hd, int max_kv_len, long long total_kv_len,
-                                      int window, int* chunk_pages) {
+                                      int window, int* chunk_pages, int* ring_pages) {
     if (chunk_pages) *chunk_pages = 0;
+    if (ring_pages) *ring_pages = kRingDefault;
     if (B <= 0 || n_heads <= 0 || n_kv <= 0 || n_heads % n_kv != 0) return kErrBadArgument;
-    int slots = 0;
+    int slots = 0, slots_deep = 0;
     const int dp = padded_head_dim(hd);
     switch (dp) {
-        case 16: slots = decode_block_slots<16>(); break;
-        case 32: slots = decode_block_slots<32>(); break;
-        case 64: slots = decode_block_slots<64>(); break;
-        case 128: slots = decode_block_slots<128>(); break;
+        case 16: slots = decode_block_slots<16, kRingDefault>(); slots_deep = decode_block_slots<16, kRingDeep>(); break;
+        case 32: slots = decode_block_slots<32, kRingDefault>(); slots_deep = decode_block_slots<32, kRingDeep>(); break;
+        case 64: slots = decode_block_slots<64, kRingDefault>(); slots_deep = decode_block_slots<64, kRingDeep>(); break;
+        case 128: slots = decode_block_slots<128, kRingDefault>(); break;
         default: return kErrUnsupported;
     }
     if (slots <= 0) return 1;
     const long long units = (long long)n_kv * ((n_heads / n_kv + 15) / 16);      // blocks per split of one sequence
+    // The deeper ring, for the batch that fills the device about once with one block per
+    // (sequence, head group): more blocks than the deep form's slots (below that, cutting
+    // the sequences finer over the default form's many slots wins) and up to a fifth
+    // more than the default form's (beyond, the blocks queue and their number per SM
+    // counts again).  Measured at 32 head groups over prompts of 128 to 2,048 tokens:
+    // the default form wins at 4, 12, 24, 32 and 48 sequences by 1 to 7 %, the deep
+    // form at 16 and 20 by 6 %.
+    int ring = kRingDefault;
+    if (slots_deep > 0 && (long long)B * units > slots_deep && (long long)B * units <= slots + slots / 5) {
+        ring = kRingDeep;
+        slots = slots_deep;
+    }
+    if (ring_pages) *ring_pages = ring;
     auto span = [&](long long keys) {                                              // pages that hold `keys` keys
         long long pages = (keys + kPageTokens - 1) / kPageTokens;
         if (window > 0 && window < keys) {
@@ -704,10 +739,10 @@ GTG_API int gtg_attention_decode_plan(int B, int n_heads, int n_kv, int hd, int 
     const double mean_pages = (double)span(mean_keys > 1 ? mean_keys : 1);
     // measured on a B200: about 3.5 us before a block's first page is in use; a block
     // keeps all but one stage of its ring in flight over that latency (two pages:
-    // 1.75 us a page); the memory's own time for all keys, once enough blocks run to
-    // saturate it
+    // 1.75 us a page; three: 1.17); the memory's own time for all keys, once enough
+    // blocks run to saturate it
     const double kFixedUs = 3.5, kMergeUs = 3.0, kBytesPerUs = 6.0e6;
-    const double kPageUs = kFixedUs / ((dp == 128 ? decode_stages<128>() : decode_stages<64>()) - 1);
+    const double kPageUs = kFixedUs / (ring - 1);
     const double page_bytes = 2.0 * kPageTokens * dp * 2;
     const double memory_us = (double)B * mean_pages * units * page_bytes / kBytesPerUs;
     int best_chunk = max_pages;
@@ -789,7 +824,7 @@ GTG_API int gtg_attention_decode_rope_bf16(const void* q, int ldq, void* out, in
                                            int B, int n_heads, int n_kv, int hd, float scale, int window,
                                            int n_splits, float* scratch, const float* cos_sin,
                                            const void* k_new, const void* v_new, int store,
-                                           int chunk_pages, cudaStream_t stream) {
+                                           int chunk_pages, int ring_pages, cudaStream_t stream) {
     if (B <= 0) return 0;
     if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv != 0 || ldq % 8 != 0 || n_splits < 1) return kErrBadArgument;
     if (k_new != nullptr && v_new == nullptr) return kErrBadArgument;
@@ -805,7 +840,7 @@ GTG_API int gtg_attention_decode_rope_bf16(const void* q, int ldq, void* out, in
     if (k_new != nullptr && store) { rope.kc_w = (bf16*)kc; rope.vc_w = (bf16*)vc; }
 #define GTG_ARGS (const bf16*)q, ldq, (bf16*)out, ldo, (const bf16*)kc, (const bf16*)vc, page_stride, \
         block_table, table_stride, slots, positions, B, n_heads, n_kv, hd, scale, window, n_splits, part_o, part_ml, \
-        stream, rope, chunk_pages
+        stream, rope, chunk_pages, ring_pages
     switch (dp) {
         case 16: return launch_decode<16>(GTG_ARGS);
         case 32: return launch_decode<32>(GTG_ARGS);
@@ -821,7 +856,8 @@ GTG_API int gtg_attention_decode_bf16(const void* q, int ldq, void* out, int ldo
                                       const int* block_table, int table_stride,
                                       const int* slots, const int* positions,
                                       int B, int n_heads, int n_kv, int hd, float scale, int window,
-                                      int n_splits, float* scratch, int chunk_pages, cudaStream_t stream) {
+                                      int n_splits, float* scratch, int chunk_pages, int ring_pages,
+                                      cudaStream_t stream) {
     if (B <= 0) return 0;
     if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv != 0 || ldq % 8 != 0 || n_splits < 1) return kErrBadArgument;
     const int dp = padded_head_dim(hd);
@@ -831,7 +867,7 @@ GTG_API int gtg_attention_decode_bf16(const void* q, int ldq, void* out, int ldo
     float* part_ml = scratch ? scratch + (size_t)B * n_heads * n_splits * dp : nullptr;
 #define GTG_ARGS (const bf16*)q, ldq, (bf16*)out, ldo, (const bf16*)kc, (const bf16*)vc, page_stride, \
         block_table, table_stride, slots, positions, B, n_heads, n_kv, hd, scale, window, n_splits, part_o, part_ml, stream, \
-        DecodeRope{}, chunk_pages
+        DecodeRope{}, chunk_pages, ring_pages
     switch (dp) {
         case 16: return launch_decode<16>(GTG_ARGS);
         case 32: return launch_decode<32>(GTG_ARGS);

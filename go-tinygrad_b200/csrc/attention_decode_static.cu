@@ -57,5 +57,5 @@ GTG_API int gtg_attention_decode_bf16_static(const void* q, int ldq, void* out, 
     }
     return gtg_attention_decode_bf16(q, ldq, out, ldo, kc, vc, page_stride, block_table, table_stride,
                                      slots, positions, n_seqs, n_heads, n_kv, head_dim, scale, window,
-                                     n_splits, scratch, 0, stream);
+                                     n_splits, scratch, 0, 0, stream);
 }

@@ -48,13 +48,13 @@ _SIGNATURES = {
                                                   _I, _I, _I, _I, _F, _I, _P]),
     "gtg_attention_bf16_supports": ("attention_bf16", [_I]),
     "gtg_attention_decode_scratch_floats": ("attention_bf16", [_I, _I, _I, _I]),
-    "gtg_attention_decode_plan": ("attention_bf16", [_I, _I, _I, _I, _I, _L, _I, _P]),
+    "gtg_attention_decode_plan": ("attention_bf16", [_I, _I, _I, _I, _I, _L, _I, _P, _P]),
     "gtg_attention_prefill_bf16": ("attention_bf16", [_P, _I, _P, _I, _P, _P, _L, _P, _I, _P, _P, _P,
                                                       _I, _I, _I, _I, _I, _F, _I, _P]),
     "gtg_attention_decode_rope_bf16": ("attention_bf16", [_P, _I, _P, _I, _P, _P, _L, _P, _I, _P, _P,
-                                                          _I, _I, _I, _I, _F, _I, _I, _P, _P, _P, _P, _I, _I, _P]),
+                                                          _I, _I, _I, _I, _F, _I, _I, _P, _P, _P, _P, _I, _I, _I, _P]),
     "gtg_attention_decode_bf16": ("attention_bf16", [_P, _I, _P, _I, _P, _P, _L, _P, _I, _P, _P,
-                                                     _I, _I, _I, _I, _F, _I, _I, _P, _I, _P]),
+                                                     _I, _I, _I, _I, _F, _I, _I, _P, _I, _I, _P]),
     "gtg_attention_tcgen05_supports": ("attention_tcgen05", [_I]),
     "gtg_attention_tcgen05_status": ("attention_tcgen05", []),
     "gtg_attention_prefill_tcgen05": ("attention_tcgen05", [_P, _I, _I, _P, _I, _P, _P, _L, _I, _P, _I, _P, _P, _P,
@@ -545,21 +545,24 @@ def attention_prefill_tcgen05(q, out, kv, cu_seqlens, slots, start_pos, n_seqs: 
 
 def attention_decode_plan(n_seqs: int, n_heads: int, n_kv_heads: int, head_dim: int, max_kv_len: int,
                           window: int = 0, total_kv_len: int = 0):
-    """(n_splits, chunk_pages) for `attention_decode_bf16`: into how many thread
-    blocks the keys of the longest sequence's (sequence, key/value head) pairs are
-    split, and how many pages one split takes (a shorter sequence then takes as
-    many splits as its own pages need).  `total_kv_len` is the batch's keys
-    altogether (0: all sequences as long as the longest).  The library estimates,
-    for every chunk size, the waves of blocks on this device (its multiprocessor
-    count and the kernel's own occupancy, from the runtime) and the time the
-    memory needs, and takes the least.  The choice depends on the batch's lengths
-    and the window, never on the data."""
-    chunk = c_int(0)
+    """(n_splits, chunk_pages, ring_pages) for `attention_decode_bf16`: into how
+    many thread blocks the keys of the longest sequence's (sequence, key/value
+    head) pairs are split, how many pages one split takes (a shorter sequence
+    then takes as many splits as its own pages need), and which form of the
+    kernel runs: the one with three pages in its ring and more blocks to an SM,
+    or, for a batch that brings about one block per place on the device, the one
+    with four.  `total_kv_len` is the batch's keys altogether (0: all sequences
+    as long as the longest).  The library estimates, for every chunk size, the
+    waves of blocks on this device (its multiprocessor count and the kernel's
+    own occupancy, from the runtime) and the time the memory needs, and takes
+    the least.  The choice depends on the batch's lengths and the window, never
+    on the data."""
+    chunk, ring = c_int(0), c_int(0)
     n = int(_fn("gtg_attention_decode_plan")(n_seqs, n_heads, n_kv_heads, head_dim, int(max_kv_len),
-                                             int(total_kv_len), int(window), ctypes.byref(chunk)))
+                                             int(total_kv_len), int(window), ctypes.byref(chunk), ctypes.byref(ring)))
     if n < 1:
         raise KernelError(f"attention_decode_plan: {_CODES.get(n, n)}")
-    return n, int(chunk.value)
+    return n, int(chunk.value), int(ring.value)
 
 
 def attention_decode_scratch_floats(n_seqs: int, n_heads: int, head_dim: int, n_splits: int) -> int:
@@ -568,7 +571,7 @@ def attention_decode_scratch_floats(n_seqs: int, n_heads: int, head_dim: int, n_
 
 def attention_decode_bf16(q, out, kv, slots, positions, n_heads: int, scale: float, window: int,
                           n_splits: int, scratch: Optional[torch.Tensor], unrotated=None,
-                          chunk_pages: int = 0) -> None:
+                          chunk_pages: int = 0, ring_pages: int = 0) -> None:
     """Attention of one new token per sequence over the cache (keys split over
     `n_splits` thread blocks per head group).  Normally q is rotated and the new
     keys and values are in the cache (`rope_kv_store`).  With
@@ -580,7 +583,8 @@ def attention_decode_bf16(q, out, kv, slots, positions, n_heads: int, scale: flo
     n_splits equal parts) a sequence is cut into as many equal parts as give parts
     of about that many pages, at most n_splits: shorter sequences take fewer splits.
     Blocks start sequence by sequence in batch order: with very unequal lengths, put
-    the long sequences first."""
+    the long sequences first.  `ring_pages` (from the plan; 0: the default) picks
+    the form of the kernel; the result does not depend on it."""
     _rows2d(q, "attention: q"); _rows2d(out, "attention: out")
     B = q.shape[0]
     _need(chunk_pages >= 0, "attention_decode_bf16: chunk_pages must not be negative")
@@ -609,14 +613,15 @@ def attention_decode_bf16(q, out, kv, slots, positions, n_heads: int, scale: flo
             _ptr(kv.block_table), kv.table_stride, _ptr(slots), _ptr(positions), B, n_heads, kv.n_kv_heads,
             kv.head_dim, float(scale), int(window), int(n_splits), _ptr(scratch), _ptr(cos_sin),
             _ptr(k_new), _ptr(v_new) if k_new is not None else None, 1 if store else 0,
-            int(chunk_pages), _stream()),
+            int(chunk_pages), int(ring_pages), _stream()),
             "attention_decode_bf16")
         return
     _check(_fn("gtg_attention_decode_bf16")(_ptr(q), q.stride(0), _ptr(out), out.stride(0),
                                             _ptr(kv.k), _ptr(kv.v), kv.page_stride, _ptr(kv.block_table),
                                             kv.table_stride, _ptr(slots), _ptr(positions), B, n_heads,
                                             kv.n_kv_heads, kv.head_dim, float(scale), int(window),
-                                            int(n_splits), _ptr(scratch), int(chunk_pages), _stream()),
+                                            int(n_splits), _ptr(scratch), int(chunk_pages), int(ring_pages),
+                                            _stream()),
            "attention_decode_bf16")
 
 

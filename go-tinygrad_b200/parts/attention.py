@@ -112,7 +112,7 @@ class GQAttention(Mixer):
             if ctx.is_decode:
                 new_k = qkv[:, self.q_dim: self.q_dim + self.kv_dim] if store else None
                 new_v = qkv[:, self.q_dim + self.kv_dim:] if store else None
-                splits, chunk = ops.attention_decode_plan(n, self.n_heads, self.n_kv, self.head_dim,
+                splits, chunk, ring = ops.attention_decode_plan(n, self.n_heads, self.n_kv, self.head_dim,
                                                           ctx.max_kv_len, window, ctx.total_kv_len)
                 scratch = None
                 if splits > 1:
@@ -121,7 +121,7 @@ class GQAttention(Mixer):
                 ops.attention_decode_bf16(q, mixed, kv, ctx.slots, ctx.positions, self.n_heads,
                                           self.scale, window, splits, scratch,
                                           unrotated=(rotation, new_k, new_v, True) if in_attention else None,
-                                          chunk_pages=chunk)
+                                          chunk_pages=chunk, ring_pages=ring)
             elif ops.attention_tcgen05_supports(kv) and qkv.stride(0) % 8 == 0:
                 ops.attention_prefill_tcgen05(q, mixed, kv, ctx.cu_seqlens, ctx.slots, ctx.start_pos,
                                               ctx.n_seqs, ctx.max_q_len, self.n_heads, self.scale, window)

@@ -69,13 +69,13 @@ def lens_for(n_seqs):
 @pytest.mark.parametrize("n_seqs", [1, 8, 64])
 @pytest.mark.parametrize("model_heads,n_heads,n_kv,hd", [((32, 32), 8, 8, 64), ((32, 8), 16, 4, 128)])
 def test_decode_attention_over_8192_keys(model_heads, n_heads, n_kv, hd, n_seqs, rotate_and_store):
-    """128 pages per sequence, the ring of four (three) pages wrapping dozens of
+    """128 pages per sequence, the ring of three (or four) pages wrapping dozens of
     times, at the split count the library chooses for this many sequences of the
     model's head counts (the test itself runs fewer heads so that 64 sequences of
     8,192 keys stay small).  In every sequence one key far from the end and one in
     the middle are made to dominate some heads' queries; the new token sits at a
     page's last row, its first row, or in between."""
-    splits, chunk = ops.attention_decode_plan(n_seqs, model_heads[0], model_heads[1], hd, 8192, 0, sum(lens_for(n_seqs)) + n_seqs)
+    splits, chunk, ring = ops.attention_decode_plan(n_seqs, model_heads[0], model_heads[1], hd, 8192, 0, sum(lens_for(n_seqs)) + n_seqs)
     assert 1 <= splits <= 64 and (splits - 1) * chunk < 128 <= splits * chunk
     if n_seqs == 1:
         assert splits > 4            # one sequence alone has to be cut to fill the device
@@ -113,14 +113,15 @@ def test_decode_attention_over_8192_keys(model_heads, n_heads, n_kv, hd, n_seqs,
         qkv = torch.cat([torch.stack(qs), torch.stack([a for a, _ in new_kv]), torch.stack([b for _, b in new_kv])], dim=1)
         qd, kd = n_heads * hd, n_kv * hd
         ops.attention_decode_bf16(qkv[:, :qd], out, kv, slot_t, positions, n_heads, scale, 0, splits, scratch,
-                                  unrotated=(None, qkv[:, qd:qd + kd], qkv[:, qd + kd:], True), chunk_pages=chunk)
+                                  unrotated=(None, qkv[:, qd:qd + kd], qkv[:, qd + kd:], True), chunk_pages=chunk,
+                                  ring_pages=ring)
         for b, t0 in enumerate(lens):                           # and the new token is in the cache afterwards
             page = int(cache.groups[0].table_host[slots[b]][t0 // 64])
             assert torch.equal(kv.k[page, :, t0 % 64, :].reshape(-1), new_kv[b][0])
             assert torch.equal(kv.v[page, :, t0 % 64, :].reshape(-1), new_kv[b][1])
     else:
         ops.attention_decode_bf16(torch.stack(qs), out, kv, slot_t, positions, n_heads, scale, 0, splits, scratch,
-                                  chunk_pages=chunk)
+                                  chunk_pages=chunk, ring_pages=ring)
     torch.testing.assert_close(out.float(), torch.stack(wants), rtol=2e-2, atol=2e-2)
     # the engineered heads really saw their key: their output is that key's value, nearly
     for b in (0, n_seqs - 1):

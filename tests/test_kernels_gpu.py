@@ -539,20 +539,28 @@ def test_attention_decode_with_splits_sized_by_a_chunk_of_pages(n_heads, n_kv, h
     ops.attention_decode_bf16(q, out, cache.handles[0].kv, m["slots"], m["positions"], n_heads, scale,
                               window, splits, scratch, chunk_pages=chunk)
     torch.testing.assert_close(out.float(), want, rtol=2e-2, atol=2e-2)
+    deep = torch.full_like(q, float("nan"))               # the form with four pages in its ring: the same bits
+    scratch.fill_(float("nan"))
+    ops.attention_decode_bf16(q, deep, cache.handles[0].kv, m["slots"], m["positions"], n_heads, scale,
+                              window, splits, scratch, chunk_pages=chunk, ring_pages=4)
+    assert torch.equal(deep, out)
 
 
 def test_the_decode_plan_follows_the_batch_not_the_data():
     """One long sequence alone is cut into many parts; many sequences are not cut at
     all; a batch of short sequences beside one long one gets a chunk that the short
     ones fit into whole; a window bounds the pages whatever the length."""
-    one, chunk1 = ops.attention_decode_plan(1, 32, 32, 64, 8192, 0, 8192)
-    assert one > 4 and (one - 1) * chunk1 < 128 <= one * chunk1
-    many, _ = ops.attention_decode_plan(64, 32, 32, 64, 2048, 0, 64 * 1100)
-    assert many == 1                                      # 2,048 blocks fill the device without a cut
-    mixed, chunk = ops.attention_decode_plan(8, 32, 32, 64, 2048, 0, 8 * 1100)
+    one, chunk1, ring1 = ops.attention_decode_plan(1, 32, 32, 64, 8192, 0, 8192)
+    assert one > 4 and (one - 1) * chunk1 < 128 <= one * chunk1 and ring1 == 3
+    many, _, ring_many = ops.attention_decode_plan(64, 32, 32, 64, 2048, 0, 64 * 1100)
+    assert many == 1 and ring_many == 3                   # 2,048 blocks fill the device without a cut
+    mixed, chunk, _ = ops.attention_decode_plan(8, 32, 32, 64, 2048, 0, 8 * 1100)
     assert mixed >= 2 and chunk >= 8                      # a sequence of 500 tokens is one block
-    windowed, wchunk = ops.attention_decode_plan(1, 32, 32, 64, 100000, 256, 100000)
+    windowed, wchunk, _ = ops.attention_decode_plan(1, 32, 32, 64, 100000, 256, 100000)
     assert windowed * wchunk <= 8                         # 256 keys touch five pages at most
+    # about one block per place on the device, uncut: the form with the deeper ring (up to 64 channels only)
+    assert ops.attention_decode_plan(16, 32, 32, 64, 2048, 0, 16 * 1100)[2] == 4
+    assert ops.attention_decode_plan(16, 32, 8, 128, 2048, 0, 16 * 1100)[2] == 3
     with pytest.raises(ops.KernelError):
         ops.attention_decode_plan(1, 32, 5, 64, 100)
 
