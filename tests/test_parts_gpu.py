@@ -693,3 +693,42 @@ def test_windowed_layers_beside_full_layers(model_folders, plain_models, name, d
         assert np.abs(full[100:] - want_p[100:]).max() > 0.05 * np.abs(want_p).max()
     finally:
         unregister_architecture(arch)
+
+
+@pytest.mark.parametrize("use_graph", [True, False])
+def test_generation_through_windowed_layers_gives_pages_back_under_recorded_steps(model_folders, plain_models, use_graph):
+    """Greedy generation (float32) far past the window through the toy model above: the
+    windowed group gives pages back while decode steps are replayed from a recording,
+    sequences of unequal lengths end at different times, and every token is the plain
+    implementation's choice from the same prefix; the cache ends empty."""
+    name = "A"
+    arch = register_architecture(Architecture(("ToyWindowForCausalLM",), LlamaConfig.from_json, windowed_plan))
+    try:
+        cfg, w = plain_models[name]
+        raw = dict(TINY[name], architectures=["ToyWindowForCausalLM"])
+        model = Model(arch.plan(arch.read_config(raw)), Runtime(DEV, torch.float32)).load_tensors(
+            tensors_of(model_folders[name]))
+        prompts = make_prompts(name, [70, 9, 131], seed=61)
+        limits = [150, 40, 90]
+        cache = model.new_cache(max_tokens=64 * 12, max_slots=3)
+        released = []
+        real_advance = cache.advance
+
+        def watching(slot, n):
+            real_advance(slot, n)
+            win = next(g for g in cache.groups if g.request.window == WINDOW)
+            released.append(sum(1 for p in win.pages_of[slot] if p < 0))
+        cache.advance = watching
+        out = lib.generate(model, prompts, limits, stop=[], cache=cache, use_graph=use_graph)
+        assert max(released) >= 2                      # pages did go back while the batch ran
+        for p, r, n in zip(prompts, out, limits):
+            assert len(r.tokens) == n
+            # one pass of the plain implementation over prompt and answer: at every place the
+            # token that was chosen must be the maximum there (or within rounding of it)
+            logits = plain_windowed_forward(cfg, w, list(p) + r.tokens[:-1]).astype(np.float64)
+            for t, tok in enumerate(r.tokens):
+                row = logits[len(p) - 1 + t]
+                assert row[tok] >= row.max() - 1e-4 * max(1.0, np.abs(row).max()), (len(p), t, tok, int(row.argmax()))
+        assert cache.open_slots() == [] and all(f == cache.n_pages for f in cache.free_pages())
+    finally:
+        unregister_architecture(arch)
