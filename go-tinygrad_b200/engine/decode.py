@@ -24,6 +24,7 @@ serves every set of as many sequences.
 """
 from __future__ import annotations
 
+import gc
 from typing import List, Optional, Sequence
 
 import torch
@@ -68,6 +69,8 @@ class DecodeBatch:
         self._runs = 0
         self._planned_len = 0                             # the longest sequence the recording was made for
         self._planned_total = 0                           # ... and all sequences' lengths together
+        self._open_first = False                          # the next step runs in the open before one is recorded again
+        self._failed_recordings = 0
 
     def rebind(self, slots: Sequence[int], requests: Sequence[int]) -> None:
         """The same number of sequences, other slots and request ids: the
@@ -119,17 +122,32 @@ class DecodeBatch:
         if self.graph is None or not self.use_graph:
             self._planned_len, self._planned_total = longest, sum(lengths)
         elif longest > self._planned_len * 1.17 or longest * 2 < self._planned_len:
-            self.graph = None                             # outgrown (or far too long a plan): record again
+            self.graph = None                             # outgrown (or far too long a plan): record again,
+            self._open_first = True                       # after one step in the open with the new plan
             self._planned_len, self._planned_total = longest, sum(lengths)
         if not self.use_graph:
             self._forward()
         elif self.graph is not None:
             self.graph.replay()
-        elif self._runs == 0:
+        elif self._runs == 0 or self._open_first:
+            self._open_first = False
             self._forward()
         else:
-            self.graph = self._record()
-            self.graph.replay()
+            try:
+                self.graph = self._record()
+            except (ops.KernelError, RuntimeError):
+                # A recording may not do what a first launch of something does (load a kernel,
+                # size its resources); the open steps before it are there to have that done,
+                # but a plan that changes between two steps can still bring something new.
+                # Nothing of a failed recording has run: the step runs in the open instead,
+                # and the next one is tried again (three failures: this batch stays in the open).
+                self.graph = None
+                self._failed_recordings += 1
+                if self._failed_recordings >= 3:
+                    self.use_graph = False
+                self._forward()
+            else:
+                self.graph.replay()
         self._finish_step()
 
     def _finish_step(self) -> None:
@@ -153,13 +171,29 @@ class DecodeBatch:
         # even if a later, larger step makes the workspace replace them
         self.model.rt.workspace.begin_step()              # grown now, to what the run before asked for
         self._workspace_held = self.model.rt.workspace.buffers()
-        with torch.cuda.stream(side):
-            graph.capture_begin()
-            try:
-                self._forward()
-            finally:
+        # While a recording runs, nothing else may talk to the device: a graph or a tensor
+        # that the cyclic collector happens to finalise in the middle of it (garbage of
+        # earlier work, of this library's or of the caller's) frees device memory and
+        # invalidates the recording.  So the collector rests meanwhile (it is not run first,
+        # as torch.cuda.graph does: that costs more than the recording).
+        collecting = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.stream(side):
+                graph.capture_begin()
+                try:
+                    self._forward()
+                except BaseException:
+                    try:
+                        graph.capture_end()               # leaves the recording mode; reports the failure once more
+                    except RuntimeError:
+                        pass
+                    raise
                 graph.capture_end()
-        main.wait_stream(side)
+        finally:
+            if collecting:
+                gc.enable()
+            main.wait_stream(side)
         return graph
 
     _side: Optional["torch.cuda.Stream"] = None

@@ -13,6 +13,7 @@ The reference's loop: model/llama.go:1047-1474 (one sequence, exactly
 """
 from __future__ import annotations
 
+import weakref
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence, Tuple, Union
 
@@ -118,8 +119,11 @@ def generate(model: Model, prompts: Sequence[Sequence[int]],
                     decode = kept.get(key(len(now)))
                     if decode is None or decode.model is not model:
                         # one recorded step per batch size serves every set of that size
-                        decode = kept[key(len(now))] = DecodeBatch(model, cache, [slots[r] for r in now], now,
-                                                                   sampler, use_graph=use_graph)
+                        # (a batch that is kept with the caller's cache refers to it weakly: the two
+                        # go together when the caller lets go of the cache, without the collector's help)
+                        decode = kept[key(len(now))] = DecodeBatch(model, cache if own_cache else weakref.proxy(cache),
+                                                                   [slots[r] for r in now], now, sampler,
+                                                                   use_graph=use_graph)
                     else:
                         decode.rebind([slots[r] for r in now], now)
                     members = now

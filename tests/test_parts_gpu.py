@@ -695,9 +695,11 @@ def test_windowed_layers_beside_full_layers(model_folders, plain_models, name, d
         unregister_architecture(arch)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("use_graph", [True, False])
-def test_generation_through_windowed_layers_gives_pages_back_under_recorded_steps(model_folders, plain_models, use_graph):
-    """Greedy generation (float32) far past the window through the toy model above: the
+def test_generation_through_windowed_layers_gives_pages_back_under_recorded_steps(model_folders, plain_models, use_graph,
+                                                                                   dtype):
+    """Greedy generation far past the window through the toy model above: the
     windowed group gives pages back while decode steps are replayed from a recording,
     sequences of unequal lengths end at different times, and every token is the plain
     implementation's choice from the same prefix; the cache ends empty."""
@@ -706,7 +708,7 @@ def test_generation_through_windowed_layers_gives_pages_back_under_recorded_step
     try:
         cfg, w = plain_models[name]
         raw = dict(TINY[name], architectures=["ToyWindowForCausalLM"])
-        model = Model(arch.plan(arch.read_config(raw)), Runtime(DEV, torch.float32)).load_tensors(
+        model = Model(arch.plan(arch.read_config(raw)), Runtime(DEV, getattr(torch, dtype))).load_tensors(
             tensors_of(model_folders[name]))
         prompts = make_prompts(name, [70, 9, 131], seed=61)
         limits = [150, 40, 90]
@@ -728,7 +730,8 @@ def test_generation_through_windowed_layers_gives_pages_back_under_recorded_step
             logits = plain_windowed_forward(cfg, w, list(p) + r.tokens[:-1]).astype(np.float64)
             for t, tok in enumerate(r.tokens):
                 row = logits[len(p) - 1 + t]
-                assert row[tok] >= row.max() - 1e-4 * max(1.0, np.abs(row).max()), (len(p), t, tok, int(row.argmax()))
+                slack = (1e-4 if dtype == "float32" else 5e-2) * max(1.0, np.abs(row).max())
+                assert row[tok] >= row.max() - slack, (len(p), t, tok, int(row.argmax()))
         assert cache.open_slots() == [] and all(f == cache.n_pages for f in cache.free_pages())
     finally:
         unregister_architecture(arch)
