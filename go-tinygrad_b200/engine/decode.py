@@ -70,7 +70,6 @@ class DecodeBatch:
         self._planned_len = 0                             # the longest sequence the recording was made for
         self._planned_total = 0                           # ... and all sequences' lengths together
         self._open_first = False                          # the next step runs in the open before one is recorded again
-        self._failed_recordings = 0
 
     def rebind(self, slots: Sequence[int], requests: Sequence[int]) -> None:
         """The same number of sequences, other slots and request ids: the
@@ -133,21 +132,8 @@ class DecodeBatch:
             self._open_first = False
             self._forward()
         else:
-            try:
-                self.graph = self._record()
-            except (ops.KernelError, RuntimeError):
-                # A recording may not do what a first launch of something does (load a kernel,
-                # size its resources); the open steps before it are there to have that done,
-                # but a plan that changes between two steps can still bring something new.
-                # Nothing of a failed recording has run: the step runs in the open instead,
-                # and the next one is tried again (three failures: this batch stays in the open).
-                self.graph = None
-                self._failed_recordings += 1
-                if self._failed_recordings >= 3:
-                    self.use_graph = False
-                self._forward()
-            else:
-                self.graph.replay()
+            self.graph = self._record()
+            self.graph.replay()
         self._finish_step()
 
     def _finish_step(self) -> None:
@@ -183,13 +169,8 @@ class DecodeBatch:
                 graph.capture_begin()
                 try:
                     self._forward()
-                except BaseException:
-                    try:
-                        graph.capture_end()               # leaves the recording mode; reports the failure once more
-                    except RuntimeError:
-                        pass
-                    raise
-                graph.capture_end()
+                finally:
+                    graph.capture_end()
         finally:
             if collecting:
                 gc.enable()

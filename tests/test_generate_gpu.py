@@ -179,38 +179,3 @@ def test_command_line(model_folders, plain_models):
     bad = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "llmgen"), "-model", model_folders[name],
                           "-tokens", "-1"], capture_output=True, text=True, timeout=300)
     assert bad.returncode == 1 and "non-negative" in bad.stderr
-
-
-def test_a_recording_that_fails_is_run_in_the_open_and_tried_again(model_folders, monkeypatch):
-    """Something the host does in the middle of a recording that a recording does not allow
-    (here: waiting for the device) spoils it.  Nothing of a spoilt recording has run: the step
-    runs in the open, the next one is recorded again, and the tokens are those of a generation
-    that records nothing at all; after three failures the batch stays in the open."""
-    import torch
-    from go_tinygrad_b200.engine import decode as decode_module
-    name = "A"
-    model = get_model(model_folders, name, "bfloat16")
-    prompts = make_prompts(name, [33, 12], seed=71)
-    plain = lib.generate(model, prompts, 20, stop=[], use_graph=False)
-    real = decode_module.DecodeBatch._forward
-    spoil = {"left": 2, "seen": 0}
-
-    def forward(self):
-        if torch.cuda.is_current_stream_capturing() and spoil["left"] > 0:
-            spoil["left"] -= 1
-            spoil["seen"] += 1
-            torch.cuda.current_stream().synchronize()         # not allowed while recording: raises
-        real(self)
-    monkeypatch.setattr(decode_module.DecodeBatch, "_forward", forward)
-    cache = model.new_cache(max_tokens=64 * 4, max_slots=2)
-    out = lib.generate(model, prompts, 20, stop=[], cache=cache)
-    assert spoil["seen"] == 2
-    assert [r.tokens for r in out] == [r.tokens for r in plain]
-    batch = next(iter(cache.attachments["decode_batches"].values()))
-    assert batch.graph is not None and batch.use_graph           # the third recording held
-    spoil["left"] = 100
-    cache2 = model.new_cache(max_tokens=64 * 4, max_slots=2)
-    out = lib.generate(model, prompts, 20, stop=[], cache=cache2)
-    assert [r.tokens for r in out] == [r.tokens for r in plain]
-    batch = next(iter(cache2.attachments["decode_batches"].values()))
-    assert batch.graph is None and not batch.use_graph           # given up after three
