@@ -7,7 +7,7 @@
 //   attention_decode: one query per sequence.  One CTA per (split, key/value
 //     head, sequence) serves the whole group of query heads that share the
 //     key/value head (rows of one 16-row MMA tile), streams its share of the
-//     pages through a four-stage cp.async ring and writes either the final
+//     pages through a cp.async ring of three pages (or four) and writes either the final
 //     output or a partial (max, sum, accumulator) that attention_combine merges
 //     in a fixed order.
 //
